@@ -1,0 +1,339 @@
+"""ctypes binding of include/backend_cuda.h.
+
+Method names and argument meaning follow the C entry points one for one
+(apus_cuda_moe_route -> Backend.moe_route, ...), which in turn mirror the
+reference engine's operator surface (c/moe.h, c/layer.h, c/backend_metal.h).
+Host-pointer methods take and return numpy arrays of uint16 BF16 codes;
+``*_dev`` methods take raw device addresses (ints) and a CUDA stream handle.
+
+The library must exist: importing never builds, and every compute call raises
+``BackendError`` when the CUDA library reports failure (there is no CPU path).
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libapus_cuda.so")
+
+u16p = C.POINTER(C.c_uint16)
+i32p = C.POINTER(C.c_int32)
+f32p = C.POINTER(C.c_float)
+sz = C.c_size_t
+vp = C.c_void_p
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+class MoeCfg(C.Structure):
+    """ApusCudaMoeCfg"""
+    _fields_ = [("hidden", sz), ("experts", sz), ("moe_inter", sz),
+                ("shared_inter", sz), ("top_k", sz)]
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["hidden"], d["experts"], d["moe_inter"],
+                   d["shared_inter"], d["top_k"])
+
+
+class MoeW(C.Structure):
+    """ApusCudaMoeW"""
+    _fields_ = [(k, vp) for k in ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u",
+                                  "sh_d", "sh_gate")]
+
+
+class MoeTrace(C.Structure):
+    """ApusCudaMoeTrace"""
+    _fields_ = [(k, vp) for k in ("rtr_idx", "rtr_w", "moe_routed",
+                                  "moe_shared", "moe_out")]
+
+
+# every symbol include/backend_cuda.h declares
+SYMBOLS = [
+    "apus_cuda_enable", "apus_cuda_disable", "apus_cuda_is_enabled",
+    "apus_cuda_bytes_resident", "apus_cuda_bytes_uploaded",
+    "apus_cuda_launches", "apus_cuda_last_error", "apus_cuda_bf16_gemv",
+    "apus_cuda_bf16_gemm", "apus_cuda_bf16_matvec_f32", "apus_cuda_moe_route",
+    "apus_cuda_moe_route_topn", "apus_cuda_moe_dispatch",
+    "apus_cuda_moe_block", "apus_cuda_block_hooks", "apus_cuda_layer_create",
+    "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
+    "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
+    "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
+    "apus_cuda_route_dev", "apus_cuda_dispatch_dev", "apus_cuda_rmsnorm_dev",
+    "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
+]
+
+TENSOR_IDS = dict(rtr_w=1, exp_gu=2, exp_d=3, sh_g=4, sh_u=5, sh_d=6, sh_gate=7)
+
+
+def _ptr(a, t=vp):
+    if a is None:
+        return None
+    if isinstance(a, int):
+        return C.cast(a, t) if t is not vp else a
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(t) if t is not vp else a.ctypes.data
+
+
+def _u16(a):
+    return np.ascontiguousarray(a, dtype=np.uint16)
+
+
+class Backend:
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise BackendError(
+                f"{path} is missing: build it first (build.build()); "
+                "there is no CPU fallback")
+        self.lib = L = C.CDLL(path)
+        L.apus_cuda_last_error.restype = C.c_char_p
+        L.apus_cuda_enable.argtypes = [C.c_char_p, sz]
+        for n in ("bytes_resident", "bytes_uploaded", "launches"):
+            getattr(L, "apus_cuda_" + n).restype = C.c_uint64
+        L.apus_cuda_bf16_gemv.argtypes = [u16p, u16p, u16p, sz, sz]
+        L.apus_cuda_bf16_gemm.argtypes = [u16p, u16p, u16p, sz, sz, sz]
+        L.apus_cuda_bf16_matvec_f32.argtypes = [u16p, u16p, f32p, sz, sz]
+        L.apus_cuda_moe_route.argtypes = [u16p, u16p, i32p, u16p, u16p, sz, sz,
+                                          sz, sz]
+        L.apus_cuda_moe_route_topn.argtypes = [u16p, u16p, i32p, sz, sz, sz]
+        L.apus_cuda_moe_dispatch.argtypes = [i32p, sz, sz, sz, i32p, i32p, i32p]
+        L.apus_cuda_moe_block.argtypes = [C.POINTER(MoeCfg), C.POINTER(MoeW),
+                                          u16p, u16p, sz, C.POINTER(MoeTrace)]
+        L.apus_cuda_layer_create.argtypes = [C.POINTER(MoeCfg),
+                                             C.POINTER(MoeW), sz, sz,
+                                             C.POINTER(vp)]
+        L.apus_cuda_layer_destroy.argtypes = [vp]
+        L.apus_cuda_layer_destroy.restype = None
+        L.apus_cuda_layer_tensor.argtypes = [vp, C.c_int, C.POINTER(sz)]
+        L.apus_cuda_layer_tensor.restype = vp
+        L.apus_cuda_layer_refresh.argtypes = [vp]
+        L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
+                                              C.POINTER(MoeTrace), vp]
+        L.apus_cuda_reserve.argtypes = [C.POINTER(MoeCfg), sz]
+        L.apus_cuda_route_dev.argtypes = [vp, vp, sz, vp, vp, vp]
+        L.apus_cuda_dispatch_dev.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
+        L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
+        L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
+        L.apus_synth_fill_host.argtypes = [u16p, sz, C.c_uint64, C.c_uint32,
+                                           C.c_uint32, C.c_uint64, C.c_double]
+        L.apus_synth_fill_host.restype = None
+        L.apus_synth_fill_dev.argtypes = [vp, sz, C.c_uint64, C.c_uint32,
+                                          C.c_uint32, C.c_uint64, C.c_double,
+                                          vp]
+
+    # ---- errors -----------------------------------------------------------
+    def last_error(self):
+        return self.lib.apus_cuda_last_error().decode()
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise BackendError(f"{what} failed (rc={rc}): {self.last_error()}")
+
+    # ---- lifecycle ----------------------------------------------------------
+    def enable(self):
+        buf = C.create_string_buffer(512)
+        rc = self.lib.apus_cuda_enable(buf, 512)
+        if rc != 0:
+            raise BackendError("apus_cuda_enable: " + buf.value.decode())
+
+    def disable(self):
+        self.lib.apus_cuda_disable()
+
+    def is_enabled(self):
+        return bool(self.lib.apus_cuda_is_enabled())
+
+    def bytes_resident(self):
+        return int(self.lib.apus_cuda_bytes_resident())
+
+    def bytes_uploaded(self):
+        return int(self.lib.apus_cuda_bytes_uploaded())
+
+    def launches(self):
+        return int(self.lib.apus_cuda_launches())
+
+    # ---- per-matmul entry points (host arrays) -----------------------------
+    def bf16_gemv(self, w, x):
+        w, x = _u16(w), _u16(x)
+        O, K = w.shape
+        y = np.zeros(O, np.uint16)
+        rc = self.lib.apus_cuda_bf16_gemv(_ptr(w, u16p), _ptr(x, u16p),
+                                          _ptr(y, u16p), O, K)
+        self._check(rc, "apus_cuda_bf16_gemv")
+        return y
+
+    def bf16_gemm(self, w, x):
+        w, x = _u16(w), _u16(x)
+        O, K = w.shape
+        M = x.shape[0]
+        y = np.zeros((M, O), np.uint16)
+        rc = self.lib.apus_cuda_bf16_gemm(_ptr(w, u16p), _ptr(x, u16p),
+                                          _ptr(y, u16p), M, O, K)
+        self._check(rc, "apus_cuda_bf16_gemm")
+        return y
+
+    def bf16_matvec_f32(self, w, x):
+        w, x = _u16(w), _u16(x)
+        O, K = w.shape
+        y = np.zeros(O, np.float32)
+        rc = self.lib.apus_cuda_bf16_matvec_f32(_ptr(w, u16p), _ptr(x, u16p),
+                                                _ptr(y, f32p), O, K)
+        self._check(rc, "apus_cuda_bf16_matvec_f32")
+        return y
+
+    # ---- router / dispatch (host arrays) -----------------------------------
+    def moe_route(self, x, wg, topk, want_logits=False):
+        x, wg = _u16(x), _u16(wg)
+        if x.ndim == 1:
+            x = x[None, :]
+        T, K = x.shape
+        E = wg.shape[0]
+        idx = np.zeros((T, topk), np.int32)
+        w = np.zeros((T, topk), np.uint16)
+        lg = np.zeros((T, E), np.uint16) if want_logits else None
+        rc = self.lib.apus_cuda_moe_route(_ptr(x, u16p), _ptr(wg, u16p),
+                                          _ptr(idx, i32p), _ptr(w, u16p),
+                                          _ptr(lg, u16p), T, E, K, topk)
+        self._check(rc, "apus_cuda_moe_route")
+        return (idx, w, lg) if want_logits else (idx, w)
+
+    def moe_route_topn(self, x, wg, n):
+        x, wg = _u16(x), _u16(wg)
+        E, K = wg.shape
+        idx = np.zeros(n, np.int32)
+        rc = self.lib.apus_cuda_moe_route_topn(_ptr(x, u16p), _ptr(wg, u16p),
+                                               _ptr(idx, i32p), n, E, K)
+        self._check(rc, "apus_cuda_moe_route_topn")
+        return idx
+
+    def moe_dispatch(self, idx, E):
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        T, TK = idx.shape
+        counts = np.zeros(E, np.int32)
+        offsets = np.zeros(E + 1, np.int32)
+        perm = np.zeros(T * TK, np.int32)
+        rc = self.lib.apus_cuda_moe_dispatch(_ptr(idx, i32p), T, TK, E,
+                                             _ptr(counts, i32p),
+                                             _ptr(offsets, i32p),
+                                             _ptr(perm, i32p))
+        self._check(rc, "apus_cuda_moe_dispatch")
+        return counts, offsets, perm
+
+    # ---- the block, host arrays ---------------------------------------------
+    def moe_block(self, cfg, W, ln2, trace=True):
+        """cfg: dict; W: dict of uint16 arrays (kept alive by the caller: the
+        rtr_w address is the residency key); ln2 [T,H].  Returns dict(out,
+        idx, w, routed, shared)."""
+        ln2 = _u16(ln2)
+        T, H = ln2.shape
+        TK = cfg["top_k"]
+        c = MoeCfg.from_dict(cfg)
+        w = MoeW(*[W[k].ctypes.data for k in
+                   ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u", "sh_d",
+                    "sh_gate")])
+        out = np.zeros((T, H), np.uint16)
+        res = dict(out=out)
+        tr = None
+        if trace:
+            res["idx"] = np.zeros((T, TK), np.int32)
+            res["w"] = np.zeros((T, TK), np.uint16)
+            res["routed"] = np.zeros((T, H), np.uint16)
+            res["shared"] = np.zeros((T, H), np.uint16)
+            tr = MoeTrace(res["idx"].ctypes.data, res["w"].ctypes.data,
+                          res["routed"].ctypes.data, res["shared"].ctypes.data,
+                          None)
+        rc = self.lib.apus_cuda_moe_block(C.byref(c), C.byref(w),
+                                          _ptr(ln2, u16p), _ptr(out, u16p), T,
+                                          C.byref(tr) if tr else None)
+        self._check(rc, "apus_cuda_moe_block")
+        return res
+
+    # ---- device-resident form -------------------------------------------------
+    def layer_create(self, cfg, W=None, expert_begin=0, expert_end=None):
+        c = MoeCfg.from_dict(cfg)
+        if expert_end is None:
+            expert_end = cfg["experts"]
+        w = None
+        if W is not None:
+            w = MoeW(*[W[k].ctypes.data for k in
+                       ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u", "sh_d",
+                        "sh_gate")])
+        h = vp()
+        rc = self.lib.apus_cuda_layer_create(C.byref(c),
+                                             C.byref(w) if w else None,
+                                             expert_begin, expert_end,
+                                             C.byref(h))
+        self._check(rc, "apus_cuda_layer_create")
+        return h.value
+
+    def layer_destroy(self, layer):
+        self.lib.apus_cuda_layer_destroy(layer)
+
+    def layer_tensor(self, layer, name):
+        n = sz()
+        p = self.lib.apus_cuda_layer_tensor(layer, TENSOR_IDS[name],
+                                            C.byref(n))
+        return p, int(n.value)
+
+    def layer_refresh(self, layer):
+        self._check(self.lib.apus_cuda_layer_refresh(layer),
+                    "apus_cuda_layer_refresh")
+
+    def reserve(self, cfg, T):
+        c = MoeCfg.from_dict(cfg)
+        self._check(self.lib.apus_cuda_reserve(C.byref(c), T),
+                    "apus_cuda_reserve")
+
+    def moe_block_dev(self, layer, d_ln2, d_out, T, stream=None, d_trace=None):
+        tr = None
+        if d_trace:
+            tr = MoeTrace(d_trace.get("idx"), d_trace.get("w"),
+                          d_trace.get("routed"), d_trace.get("shared"),
+                          d_trace.get("out"))
+        rc = self.lib.apus_cuda_moe_block_dev(layer, d_ln2, d_out, T,
+                                              C.byref(tr) if tr else None,
+                                              stream)
+        self._check(rc, "apus_cuda_moe_block_dev")
+
+    def last_block_launches(self):
+        return int(self.lib.apus_cuda_last_block_launches())
+
+    def last_block_status(self):
+        return int(self.lib.apus_cuda_last_block_status())
+
+    def route_dev(self, layer, d_x, T, d_idx, d_w, stream=None):
+        self._check(self.lib.apus_cuda_route_dev(layer, d_x, T, d_idx, d_w,
+                                                 stream),
+                    "apus_cuda_route_dev")
+
+    def dispatch_dev(self, d_idx, T, topk, E, d_counts, d_offsets, d_perm,
+                     stream=None):
+        self._check(self.lib.apus_cuda_dispatch_dev(d_idx, T, topk, E,
+                                                    d_counts, d_offsets,
+                                                    d_perm, stream),
+                    "apus_cuda_dispatch_dev")
+
+    def rmsnorm_dev(self, d_x, d_w, d_y, T, N, stream=None):
+        self._check(self.lib.apus_cuda_rmsnorm_dev(d_x, d_w, d_y, T, N,
+                                                   stream),
+                    "apus_cuda_rmsnorm_dev")
+
+    def resadd_dev(self, d_a, d_b, d_out, n, stream=None):
+        self._check(self.lib.apus_cuda_resadd_dev(d_a, d_b, d_out, n, stream),
+                    "apus_cuda_resadd_dev")
+
+    # ---- synthetic tensors -------------------------------------------------------
+    def synth_fill_host(self, n, seed, layer, tensor_id, sigma, first=0):
+        out = np.empty(n, np.uint16)
+        self.lib.apus_synth_fill_host(_ptr(out, u16p), n, seed, layer,
+                                      tensor_id, first, sigma)
+        return out
+
+    def synth_fill_dev(self, d_dst, n, seed, layer, tensor_id, sigma, first=0,
+                       stream=None):
+        self._check(self.lib.apus_synth_fill_dev(d_dst, n, seed, layer,
+                                                 tensor_id, first, sigma,
+                                                 stream),
+                    "apus_synth_fill_dev")

@@ -1,0 +1,1016 @@
+/*
+ * backend_cuda.cu — C-ABI implementation of include/backend_cuda.h.
+ *
+ * Host side of the CUDA backend: context, HBM weight residency (the CPU
+ * engine's NVMe expert cache, c/cache.h, has no counterpart here — a 67 GiB
+ * checkpoint fits in one B200's 180 GB), workspace arena, kernel launches.
+ * Shaped after c/backend_metal.mm: one process-wide context, one op mutex,
+ * pointer-keyed weight cache, env-var knobs read at enable time, 0 / nonzero
+ * return convention.  There is no CPU path in this file: without a usable
+ * device every compute entry point fails.
+ */
+#include "../../include/backend_cuda.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+#include "decode_gemv.cuh"
+#include "dispatch.cuh"
+#include "misc_kernels.cuh"
+#include "prefill_gemm.cuh"
+#include "router.cuh"
+
+using namespace apus;
+
+/* ------------------------------------------------------------------------ */
+/* context                                                                   */
+/* ------------------------------------------------------------------------ */
+
+struct DevBuf {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct Arena {
+    char *base = nullptr;
+    size_t cap = 0;
+    size_t off = 0;
+    void reset() { off = 0; }
+    void *take(size_t bytes) {
+        size_t o = (off + 255) & ~(size_t)255;
+        if (o + bytes > cap) return nullptr;
+        off = o + bytes;
+        return base + o;
+    }
+};
+
+struct ApusCudaLayer {
+    ApusCudaMoeCfg cfg;
+    size_t e_begin = 0, e_end = 0;
+    uint16_t *rtr_w = nullptr, *exp_gu = nullptr, *exp_d = nullptr;
+    uint16_t *sh_g = nullptr, *sh_u = nullptr, *sh_d = nullptr,
+             *sh_gate = nullptr;
+    float wmin = 0.0f;          /* smallest nonzero |rtr_w| (0 = unknown) */
+    size_t bytes = 0;
+    PrefillMaps *maps = nullptr; /* tensor maps for the tcgen05 path */
+};
+
+struct Ctx {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    std::unordered_map<const void *, DevBuf> wcache;
+    std::unordered_map<const void *, ApusCudaLayer *> layers;  /* host-ptr key */
+    uint64_t budget = ~0ull;
+    uint64_t bytes_resident = 0, bytes_uploaded = 0, launches = 0;
+    Arena ws;      /* block workspace */
+    Arena io;      /* host-pointer staging */
+    int *d_status = nullptr;
+    unsigned int *d_scratch_u32 = nullptr;
+    int decode_max_t = 64;
+    int last_block_launches = 0;
+    bool hooks_filled = false;
+};
+
+static Ctx *g_ctx = nullptr;
+static std::recursive_mutex g_mu;
+static char g_err[512] = "";
+
+ApusCudaBlockHooks apus_cuda_block_hooks = {nullptr};
+
+/* The engine's three-slot table (c/backend_metal.h:79-88), when the engine is
+ * linked into this process; absent (NULL address) otherwise. */
+extern "C" {
+typedef struct {
+    int (*bf16_gemv)(const uint16_t *, const uint16_t *, uint16_t *, size_t,
+                     size_t);
+    int (*bf16_gemm)(const uint16_t *, const uint16_t *, uint16_t *, size_t,
+                     size_t, size_t);
+    int (*bf16_matvec_f32)(const uint16_t *, const uint16_t *, float *, size_t,
+                           size_t);
+} ApusBackendHooksView;
+extern ApusBackendHooksView apus_backend_hooks __attribute__((weak));
+}
+
+static int fail(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return 1;
+}
+#define CU_OK(call)                                                        \
+    do {                                                                   \
+        cudaError_t e_ = (call);                                           \
+        if (e_ != cudaSuccess)                                             \
+            return fail("%s: %s (%s:%d)", #call, cudaGetErrorString(e_),   \
+                        __FILE__, __LINE__);                               \
+    } while (0)
+
+static long env_long(const char *name, long dflt) {
+    const char *e = getenv(name);
+    return (e && *e) ? atol(e) : dflt;
+}
+
+static int ctx_init() {
+    if (g_ctx) return 0;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0)
+        return fail("no CUDA device (%s)", cudaGetErrorString(e));
+    int dev = (int)env_long("APUS_CUDA_DEVICE", -1);
+    if (dev < 0) {
+        /* one process per GPU under a multi-rank launcher */
+        dev = (int)env_long("LOCAL_RANK", 0);
+        if (dev >= n) dev = dev % n;
+    }
+    if (dev >= n) return fail("APUS_CUDA_DEVICE=%d but %d device(s)", dev, n);
+    CU_OK(cudaSetDevice(dev));
+    cudaDeviceProp prop;
+    CU_OK(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+        return fail("device %d is sm_%d%d; this backend is built for sm_100a",
+                    dev, prop.major, prop.minor);
+    Ctx *c = new Ctx();
+    c->device = dev;
+    c->sm_count = prop.multiProcessorCount;
+    c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    CU_OK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CU_OK(cudaMalloc(&c->d_status, 256));
+    CU_OK(cudaMemset(c->d_status, 0, 256));
+    c->d_scratch_u32 = reinterpret_cast<unsigned int *>(c->d_status) + 16;
+    long mb = env_long("APUS_CUDA_DENSE_MB", -1);
+    c->budget = mb < 0 ? ~0ull : (uint64_t)mb << 20;
+    c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 64);
+    g_ctx = c;
+    return 0;
+}
+
+static int arena_reserve(Arena &a, size_t bytes) {
+    if (a.cap >= bytes) return 0;
+    CU_OK(cudaDeviceSynchronize());
+    if (a.base) CU_OK(cudaFree(a.base));
+    a.base = nullptr;
+    a.cap = 0;
+    size_t want = bytes + (bytes >> 3) + (1u << 20);
+    CU_OK(cudaMalloc((void **)&a.base, want));
+    a.cap = want;
+    a.off = 0;
+    return 0;
+}
+
+#define LAUNCHED()                                                         \
+    do {                                                                   \
+        g_ctx->launches++;                                                 \
+        g_ctx->last_block_launches++;                                      \
+        cudaError_t e_ = cudaGetLastError();                               \
+        if (e_ != cudaSuccess)                                             \
+            return fail("kernel launch: %s (%s:%d)", cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                               \
+    } while (0)
+
+/* ------------------------------------------------------------------------ */
+/* lifecycle                                                                 */
+/* ------------------------------------------------------------------------ */
+
+static int hook_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y,
+                     size_t O, size_t K) {
+    return apus_cuda_bf16_gemv(w, x, y, O, K);
+}
+static int hook_gemm(const uint16_t *w, const uint16_t *x, uint16_t *y,
+                     size_t M, size_t O, size_t K) {
+    return apus_cuda_bf16_gemm(w, x, y, M, O, K);
+}
+static int hook_matvec(const uint16_t *w, const uint16_t *x, float *y,
+                       size_t O, size_t K) {
+    return apus_cuda_bf16_matvec_f32(w, x, y, O, K);
+}
+
+extern "C" int apus_cuda_enable(char *err, size_t errcap) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) {
+        if (err && errcap) snprintf(err, errcap, "%s", g_err);
+        return -1;
+    }
+    if (&apus_backend_hooks) {
+        apus_backend_hooks.bf16_gemv =
+            getenv("APUS_CUDA_NO_GEMV") ? nullptr : hook_gemv;
+        apus_backend_hooks.bf16_gemm =
+            getenv("APUS_CUDA_NO_GEMM") ? nullptr : hook_gemm;
+        apus_backend_hooks.bf16_matvec_f32 =
+            getenv("APUS_CUDA_NO_MATVEC") ? nullptr : hook_matvec;
+    }
+    apus_cuda_block_hooks.moe_block =
+        getenv("APUS_CUDA_NO_MOE") ? nullptr : apus_cuda_moe_block;
+    g_ctx->hooks_filled = true;
+    return 0;
+}
+
+static void layer_free(ApusCudaLayer *L) {
+    if (!L) return;
+    void *ptrs[] = {L->rtr_w, L->exp_gu, L->exp_d, L->sh_g,
+                    L->sh_u,  L->sh_d,   L->sh_gate};
+    for (void *p : ptrs)
+        if (p) cudaFree(p);
+    if (L->maps) prefill_maps_free(L->maps);
+    if (g_ctx && g_ctx->bytes_resident >= L->bytes)
+        g_ctx->bytes_resident -= L->bytes;
+    delete L;
+}
+
+extern "C" void apus_cuda_disable(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (&apus_backend_hooks)
+        memset(&apus_backend_hooks, 0, sizeof apus_backend_hooks);
+    apus_cuda_block_hooks.moe_block = nullptr;
+    Ctx *c = g_ctx;
+    if (!c) return;
+    cudaDeviceSynchronize();
+    for (auto &kv : c->wcache) cudaFree(kv.second.ptr);
+    for (auto &kv : c->layers) layer_free(kv.second);
+    if (c->ws.base) cudaFree(c->ws.base);
+    if (c->io.base) cudaFree(c->io.base);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    g_ctx = nullptr;
+    delete c;
+}
+
+extern "C" int apus_cuda_is_enabled(void) {
+    return g_ctx && g_ctx->hooks_filled;
+}
+extern "C" uint64_t apus_cuda_bytes_resident(void) {
+    return g_ctx ? g_ctx->bytes_resident : 0;
+}
+extern "C" uint64_t apus_cuda_bytes_uploaded(void) {
+    return g_ctx ? g_ctx->bytes_uploaded : 0;
+}
+extern "C" uint64_t apus_cuda_launches(void) {
+    return g_ctx ? g_ctx->launches : 0;
+}
+extern "C" const char *apus_cuda_last_error(void) { return g_err; }
+
+/* ------------------------------------------------------------------------ */
+/* per-matmul entry points (host pointers)                                   */
+/* ------------------------------------------------------------------------ */
+
+static void *weight_buf(Ctx *c, const void *ptr, size_t bytes) {
+    auto it = c->wcache.find(ptr);
+    if (it != c->wcache.end()) {
+        if (it->second.bytes >= bytes) return it->second.ptr;
+        /* same key, larger view: replace the copy */
+        cudaFree(it->second.ptr);
+        c->bytes_resident -= it->second.bytes;
+        c->wcache.erase(it);
+    }
+    if (c->bytes_resident + bytes > c->budget) {
+        fail("weight budget exhausted (APUS_CUDA_DENSE_MB)");
+        return nullptr;
+    }
+    void *d = nullptr;
+    if (cudaMalloc(&d, bytes) != cudaSuccess) {
+        fail("cudaMalloc(%zu) for a weight failed", bytes);
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (cudaMemcpy(d, ptr, bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        fail("weight upload failed");
+        cudaFree(d);
+        return nullptr;
+    }
+    c->bytes_resident += bytes;
+    c->bytes_uploaded += bytes;
+    c->wcache.emplace(ptr, DevBuf{d, bytes});
+    return d;
+}
+
+static int dense_op(const uint16_t *w, const uint16_t *x, void *y, size_t M,
+                    size_t O, size_t K, bool f32_out) {
+    if (!M || !O || !K) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    const uint16_t *dw = (const uint16_t *)weight_buf(c, w, O * K * 2);
+    if (!dw) return 1;
+    size_t xb = M * K * 2, yb = M * O * (f32_out ? 4 : 2);
+    if (arena_reserve(c->io, xb + yb + 1024)) return 1;
+    c->io.reset();
+    uint16_t *dx = (uint16_t *)c->io.take(xb);
+    void *dy = c->io.take(yb);
+    CU_OK(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, c->stream));
+    long total = (long)(M * O);
+    int blocks = (int)((total + 127) / 128);
+    if (blocks > c->sm_count * 16) blocks = c->sm_count * 16;
+    if (f32_out)
+        exact_matvec_f32_kernel<<<blocks, 128, 0, c->stream>>>(
+            dw, dx, (float *)dy, (long)O, (int)K);
+    else
+        exact_gemm_kernel<<<blocks, 128, 0, c->stream>>>(
+            dw, dx, (uint16_t *)dy, (long)M, (long)O, (int)K);
+    LAUNCHED();
+    CU_OK(cudaMemcpyAsync(y, dy, yb, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int apus_cuda_bf16_gemv(const uint16_t *w, const uint16_t *x,
+                                   uint16_t *y, size_t O, size_t K) {
+    return dense_op(w, x, y, 1, O, K, false);
+}
+extern "C" int apus_cuda_bf16_gemm(const uint16_t *w, const uint16_t *x,
+                                   uint16_t *y, size_t M, size_t O, size_t K) {
+    return dense_op(w, x, y, M, O, K, false);
+}
+extern "C" int apus_cuda_bf16_matvec_f32(const uint16_t *w, const uint16_t *x,
+                                         float *y, size_t O, size_t K) {
+    return dense_op(w, x, y, 1, O, K, true);
+}
+
+/* ------------------------------------------------------------------------ */
+/* router / dispatch launches                                                */
+/* ------------------------------------------------------------------------ */
+
+template <int TT>
+static int launch_router_tt(Ctx *c, const uint16_t *dx, const uint16_t *dwr,
+                            int T, int E, int K, int topk, float wmin,
+                            int32_t *didx, uint16_t *dw, uint16_t *dlogits,
+                            const uint16_t *extra_row, uint16_t *extra_out,
+                            cudaStream_t st) {
+    size_t smem = ((size_t)TT * K + (size_t)TT * E) * sizeof(float);
+    if (smem > (size_t)c->smem_optin)
+        return fail("router tile does not fit shared memory (K=%d E=%d)", K, E);
+    CU_OK(cudaFuncSetAttribute(router_topk_kernel<TT>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem));
+    int grid = (T + TT - 1) / TT;
+    router_topk_kernel<TT><<<grid, ROUTER_THREADS, smem, st>>>(
+        dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row, extra_out);
+    LAUNCHED();
+    return 0;
+}
+
+static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
+                         int E, int K, int topk, float wmin, int32_t *didx,
+                         uint16_t *dw, uint16_t *dlogits,
+                         const uint16_t *extra_row, uint16_t *extra_out,
+                         cudaStream_t st) {
+    if (E < 1 || E > 1024 || topk < 1 || topk > 32 || topk > E || K < 1)
+        return fail("router: unsupported E=%d topk=%d K=%d", E, topk, K);
+    /* small T: one token per CTA keeps the chain latency at its floor;
+     * large T: eight chains per thread amortise the weight reads */
+    if (T <= 2 * c->sm_count)
+        return launch_router_tt<1>(c, dx, dwr, T, E, K, topk, wmin, didx, dw,
+                                   dlogits, extra_row, extra_out, st);
+    size_t smem8 = ((size_t)8 * K + (size_t)8 * E) * sizeof(float);
+    if (smem8 <= (size_t)c->smem_optin)
+        return launch_router_tt<8>(c, dx, dwr, T, E, K, topk, wmin, didx, dw,
+                                   dlogits, extra_row, extra_out, st);
+    return launch_router_tt<1>(c, dx, dwr, T, E, K, topk, wmin, didx, dw,
+                               dlogits, extra_row, extra_out, st);
+}
+
+static size_t dispatch_scratch_bytes(size_t A, size_t E) {
+    size_t units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
+    return units * E * sizeof(int32_t);
+}
+
+static int launch_dispatch(Ctx *c, const int32_t *didx, int A, int E,
+                           DispatchOut o, int32_t *unit_hist,
+                           cudaStream_t st) {
+    if (E < 1 || E > 1024) return fail("dispatch: unsupported E=%d", E);
+    if (A <= 4096) {
+        dispatch_small_kernel<<<1, 256, 2 * E * sizeof(int), st>>>(
+            didx, A, E, o, c->d_status);
+        LAUNCHED();
+        return 0;
+    }
+    int units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
+    int blocks = (units + DISPATCH_WARPS - 1) / DISPATCH_WARPS;
+    size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);
+    dispatch_hist_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
+        didx, A, E, unit_hist, c->d_status);
+    LAUNCHED();
+    dispatch_scan_kernel<<<1, 1024, 0, st>>>(unit_hist, units, E, o);
+    LAUNCHED();
+    dispatch_permute_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
+        didx, A, E, unit_hist, o);
+    LAUNCHED();
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* router / dispatch, host pointers                                          */
+/* ------------------------------------------------------------------------ */
+
+static int min_nonzero(Ctx *c, const uint16_t *d, size_t n, float *out,
+                       cudaStream_t st) {
+    unsigned int inf = 0x7f800000u;
+    CU_OK(cudaMemcpyAsync(c->d_scratch_u32, &inf, 4, cudaMemcpyHostToDevice, st));
+    bf16_min_nonzero_kernel<<<c->sm_count * 2, 256, 0, st>>>(d, n,
+                                                             c->d_scratch_u32);
+    LAUNCHED();
+    unsigned int bits = 0;
+    CU_OK(cudaMemcpyAsync(&bits, c->d_scratch_u32, 4, cudaMemcpyDeviceToHost, st));
+    CU_OK(cudaStreamSynchronize(st));
+    float f;
+    memcpy(&f, &bits, 4);
+    *out = (bits >= 0x7f800000u) ? 0.0f : f;
+    return 0;
+}
+
+static int route_host(const uint16_t *x, const uint16_t *wg, int32_t *idx,
+                      uint16_t *w, uint16_t *logits, size_t T, size_t E,
+                      size_t K, size_t topk) {
+    if (!T || !E || !K || !topk) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    size_t need = T * K * 2 + E * K * 2 + T * topk * 6 + T * E * 2 + 4096;
+    if (arena_reserve(c->io, need)) return 1;
+    c->io.reset();
+    uint16_t *dx = (uint16_t *)c->io.take(T * K * 2);
+    uint16_t *dwr = (uint16_t *)c->io.take(E * K * 2);
+    int32_t *didx = (int32_t *)c->io.take(T * topk * 4);
+    uint16_t *dw = (uint16_t *)c->io.take(T * topk * 2);
+    uint16_t *dl = logits ? (uint16_t *)c->io.take(T * E * 2) : nullptr;
+    CU_OK(cudaMemcpyAsync(dx, x, T * K * 2, cudaMemcpyHostToDevice, c->stream));
+    CU_OK(cudaMemcpyAsync(dwr, wg, E * K * 2, cudaMemcpyHostToDevice, c->stream));
+    float wmin = 0.0f;
+    if (min_nonzero(c, dwr, E * K, &wmin, c->stream)) return 1;
+    if (launch_router(c, dx, dwr, (int)T, (int)E, (int)K, (int)topk, wmin, didx,
+                      w ? dw : nullptr, dl, nullptr, nullptr, c->stream))
+        return 1;
+    CU_OK(cudaMemcpyAsync(idx, didx, T * topk * 4, cudaMemcpyDeviceToHost,
+                          c->stream));
+    if (w)
+        CU_OK(cudaMemcpyAsync(w, dw, T * topk * 2, cudaMemcpyDeviceToHost,
+                              c->stream));
+    if (logits)
+        CU_OK(cudaMemcpyAsync(logits, dl, T * E * 2, cudaMemcpyDeviceToHost,
+                              c->stream));
+    CU_OK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int apus_cuda_moe_route(const uint16_t *x, const uint16_t *wg,
+                                   int32_t *idx, uint16_t *w, uint16_t *logits,
+                                   size_t T, size_t E, size_t K, size_t topk) {
+    return route_host(x, wg, idx, w, logits, T, E, K, topk);
+}
+extern "C" int apus_cuda_moe_route_topn(const uint16_t *x, const uint16_t *wg,
+                                        int32_t *idx, size_t n, size_t E,
+                                        size_t K) {
+    return route_host(x, wg, idx, nullptr, nullptr, 1, E, K, n);
+}
+
+extern "C" int apus_cuda_moe_dispatch(const int32_t *idx, size_t T, size_t topk,
+                                      size_t E, int32_t *counts,
+                                      int32_t *offsets, int32_t *perm) {
+    size_t A = T * topk;
+    if (!A || !E) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    size_t need = A * 8 + (2 * E + 1) * 4 + dispatch_scratch_bytes(A, E) + 4096;
+    if (arena_reserve(c->io, need)) return 1;
+    c->io.reset();
+    int32_t *didx = (int32_t *)c->io.take(A * 4);
+    DispatchOut o;
+    memset(&o, 0, sizeof o);
+    o.counts = (int32_t *)c->io.take(E * 4);
+    o.offsets = (int32_t *)c->io.take((E + 1) * 4);
+    o.perm = (int32_t *)c->io.take(A * 4);
+    int32_t *uh = (int32_t *)c->io.take(dispatch_scratch_bytes(A, E));
+    CU_OK(cudaMemcpyAsync(didx, idx, A * 4, cudaMemcpyHostToDevice, c->stream));
+    CU_OK(cudaMemsetAsync(c->d_status, 0, 4, c->stream));
+    if (launch_dispatch(c, didx, (int)A, (int)E, o, uh, c->stream)) return 1;
+    CU_OK(cudaMemcpyAsync(counts, o.counts, E * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(cudaMemcpyAsync(offsets, o.offsets, (E + 1) * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(cudaMemcpyAsync(perm, o.perm, A * 4, cudaMemcpyDeviceToHost, c->stream));
+    int st = 0;
+    CU_OK(cudaMemcpyAsync(&st, c->d_status, 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(cudaStreamSynchronize(c->stream));
+    if (st) return fail("dispatch: expert id out of range (status %d)", st);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* layers                                                                    */
+/* ------------------------------------------------------------------------ */
+
+static int cfg_check(const ApusCudaMoeCfg *c) {
+    if (!c) return fail("null config");
+    if (!c->hidden || !c->experts || !c->moe_inter || !c->shared_inter ||
+        !c->top_k)
+        return fail("zero dimension in MoE config");
+    if (c->hidden % 8 || c->moe_inter % 8 || c->shared_inter % 8)
+        return fail("hidden, moe_inter and shared_inter must be multiples of 8");
+    if (c->experts > 1024 || c->top_k > 32 || c->top_k > c->experts)
+        return fail("unsupported experts=%zu top_k=%zu", c->experts, c->top_k);
+    return 0;
+}
+
+extern "C" int apus_cuda_layer_create(const ApusCudaMoeCfg *cfg,
+                                      const ApusCudaMoeW *w,
+                                      size_t expert_begin, size_t expert_end,
+                                      ApusCudaLayer **out) {
+    if (!out) return fail("null out");
+    *out = nullptr;
+    if (cfg_check(cfg)) return 1;
+    if (expert_begin > expert_end || expert_end > cfg->experts)
+        return fail("bad expert range [%zu,%zu)", expert_begin, expert_end);
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    const size_t H = cfg->hidden, E = cfg->experts, I = cfg->moe_inter,
+                 Is = cfg->shared_inter;
+    const size_t ne = expert_end - expert_begin;
+    ApusCudaLayer *L = new ApusCudaLayer();
+    L->cfg = *cfg;
+    L->e_begin = expert_begin;
+    L->e_end = expert_end;
+    struct Item { uint16_t **dst; size_t elems; const uint16_t *src; };
+    Item items[] = {
+        {&L->rtr_w, E * H, w ? w->rtr_w : nullptr},
+        {&L->exp_gu, ne * 2 * I * H,
+         w && w->exp_gu ? w->exp_gu + expert_begin * 2 * I * H : nullptr},
+        {&L->exp_d, ne * H * I,
+         w && w->exp_d ? w->exp_d + expert_begin * H * I : nullptr},
+        {&L->sh_g, Is * H, w ? w->sh_g : nullptr},
+        {&L->sh_u, Is * H, w ? w->sh_u : nullptr},
+        {&L->sh_d, H * Is, w ? w->sh_d : nullptr},
+        {&L->sh_gate, H, w ? w->sh_gate : nullptr},
+    };
+    for (auto &it : items) {
+        size_t bytes = it.elems * 2;
+        if (!bytes) continue;
+        if (c->bytes_resident + L->bytes + bytes > c->budget) {
+            layer_free(L);
+            return fail("weight budget exhausted (APUS_CUDA_DENSE_MB)");
+        }
+        if (cudaMalloc((void **)it.dst, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            layer_free(L);
+            return fail("cudaMalloc(%zu) for layer weights failed", bytes);
+        }
+        L->bytes += bytes;
+        if (it.src) {
+            if (cudaMemcpy(*it.dst, it.src, bytes, cudaMemcpyHostToDevice) !=
+                cudaSuccess) {
+                layer_free(L);
+                return fail("layer weight upload failed");
+            }
+            c->bytes_uploaded += bytes;
+        }
+    }
+    c->bytes_resident += L->bytes;
+    L->maps = nullptr;
+    if (w && w->rtr_w) {
+        if (min_nonzero(c, L->rtr_w, E * H, &L->wmin, c->stream)) {
+            layer_free(L);
+            return 1;
+        }
+    }
+    *out = L;
+    return 0;
+}
+
+extern "C" void apus_cuda_layer_destroy(ApusCudaLayer *layer) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (g_ctx) cudaDeviceSynchronize();
+    layer_free(layer);
+}
+
+extern "C" void *apus_cuda_layer_tensor(ApusCudaLayer *L, int which,
+                                        size_t *elems) {
+    if (!L) return nullptr;
+    const size_t H = L->cfg.hidden, E = L->cfg.experts, I = L->cfg.moe_inter,
+                 Is = L->cfg.shared_inter, ne = L->e_end - L->e_begin;
+    void *p = nullptr;
+    size_t n = 0;
+    switch (which) {
+        case 1: p = L->rtr_w; n = E * H; break;
+        case 2: p = L->exp_gu; n = ne * 2 * I * H; break;
+        case 3: p = L->exp_d; n = ne * H * I; break;
+        case 4: p = L->sh_g; n = Is * H; break;
+        case 5: p = L->sh_u; n = Is * H; break;
+        case 6: p = L->sh_d; n = H * Is; break;
+        case 7: p = L->sh_gate; n = H; break;
+        default: break;
+    }
+    if (elems) *elems = n;
+    return p;
+}
+
+extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
+    if (!L) return fail("null layer");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    return min_nonzero(g_ctx, L->rtr_w, L->cfg.experts * L->cfg.hidden,
+                       &L->wmin, g_ctx->stream);
+}
+
+/* ------------------------------------------------------------------------ */
+/* the block                                                                 */
+/* ------------------------------------------------------------------------ */
+
+struct BlockBufs {
+    int32_t *idx;
+    uint16_t *rw, *sgl;
+    DispatchOut d;
+    int32_t *unit_hist;
+    uint16_t *act, *sa, *eo, *sy, *xg;
+    int32_t *tiles;        /* prefill tile list */
+    size_t total;
+};
+
+static size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
+
+/* carve (or just size, when a.base == NULL) the block's workspace */
+static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
+                        BlockBufs *b, bool prefill) {
+    const size_t H = c.hidden, E = c.experts, I = c.moe_inter,
+                 Is = c.shared_inter, TK = c.top_k, A = T * TK;
+    size_t sz[] = {
+        A * 4,                         /* idx */
+        A * 2,                         /* rw */
+        T * 2,                         /* sgl */
+        E * 4, (E + 1) * 4, A * 4, A * 4,            /* counts offsets perm pos */
+        (A + E) * 4, (A + E) * 4, (A + E) * 4, 256,  /* groups, n_groups */
+        dispatch_scratch_bytes(A, E),  /* unit_hist */
+        A * I * 2, T * Is * 2, A * H * 2, T * H * 2, /* act sa eo sy */
+        prefill ? A * H * 2 : 0,       /* xg */
+        prefill ? prefill_tile_list_bytes(A, T, E) : 0,
+    };
+    size_t total = 0;
+    for (size_t s : sz) total += al256(s) + 256;
+    b->total = total;
+    if (!a) return 0;
+    a->reset();
+    void *p[sizeof sz / sizeof sz[0]];
+    for (size_t i = 0; i < sizeof sz / sizeof sz[0]; i++) {
+        p[i] = sz[i] ? a->take(sz[i]) : nullptr;
+        if (sz[i] && !p[i]) return fail("workspace arena too small");
+    }
+    b->idx = (int32_t *)p[0];
+    b->rw = (uint16_t *)p[1];
+    b->sgl = (uint16_t *)p[2];
+    b->d.counts = (int32_t *)p[3];
+    b->d.offsets = (int32_t *)p[4];
+    b->d.perm = (int32_t *)p[5];
+    b->d.pos = (int32_t *)p[6];
+    b->d.grp_expert = (int32_t *)p[7];
+    b->d.grp_first = (int32_t *)p[8];
+    b->d.grp_n = (int32_t *)p[9];
+    b->d.n_groups = (int32_t *)p[10];
+    b->unit_hist = (int32_t *)p[11];
+    b->act = (uint16_t *)p[12];
+    b->sa = (uint16_t *)p[13];
+    b->eo = (uint16_t *)p[14];
+    b->sy = (uint16_t *)p[15];
+    b->xg = (uint16_t *)p[16];
+    b->tiles = (int32_t *)p[17];
+    return 0;
+}
+
+extern "C" int apus_cuda_reserve(const ApusCudaMoeCfg *cfg, size_t T) {
+    if (cfg_check(cfg) || !T) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    BlockBufs b;
+    block_layout(*cfg, T, nullptr, &b, true);
+    return arena_reserve(g_ctx->ws, b.total);
+}
+
+static int decode_smem_bytes(const ApusCudaMoeCfg &c, bool down) {
+    size_t H = c.hidden, Imax = c.moe_inter > c.shared_inter ? c.moe_inter
+                                                             : c.shared_inter;
+    size_t stage = down ? DOWN_ROWS * Imax : 2 * H;
+    size_t xrow = down ? Imax : H;
+    return (int)((DEC_WARPS * DEC_STAGES * stage + GROUP_TOKENS * xrow) * 2 +
+                 DEC_WARPS * DEC_STAGES * 8 + 128);
+}
+
+/* routed + shared experts through the grouped-GEMV kernels */
+static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
+                              int T, BlockBufs &b, bool do_shared,
+                              cudaStream_t st) {
+    const ApusCudaMoeCfg &cfg = L->cfg;
+    DecodeArgs a;
+    memset(&a, 0, sizeof a);
+    a.T = T;
+    a.H = (int)cfg.hidden;
+    a.I = (int)cfg.moe_inter;
+    a.Is = (int)cfg.shared_inter;
+    a.TK = (int)cfg.top_k;
+    a.expert_begin = (int)L->e_begin;
+    a.x = dx;
+    a.exp_gu = L->exp_gu;
+    a.exp_d = L->exp_d;
+    a.sh_g = L->sh_g;
+    a.sh_u = L->sh_u;
+    a.sh_d = L->sh_d;
+    a.perm = b.d.perm;
+    a.grp_expert = b.d.grp_expert;
+    a.grp_first = b.d.grp_first;
+    a.grp_n = b.d.grp_n;
+    a.n_groups = b.d.n_groups;
+    a.act = b.act;
+    a.sa = b.sa;
+    a.eo = b.eo;
+    a.sy = b.sy;
+    a.do_shared = do_shared ? 1 : 0;
+    a.status = c->d_status;
+    int s1 = decode_smem_bytes(cfg, false), s2 = decode_smem_bytes(cfg, true);
+    if (s1 > c->smem_optin || s2 > c->smem_optin)
+        return fail("decode kernels need %d/%d B shared memory (> %d)", s1, s2,
+                    c->smem_optin);
+    if (cfg.hidden % DOWN_ROWS) return fail("hidden must be a multiple of 8");
+    CU_OK(cudaFuncSetAttribute(decode_gate_up_kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, s1));
+    CU_OK(cudaFuncSetAttribute(decode_down_kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
+    decode_gate_up_kernel<<<c->sm_count, DEC_THREADS, s1, st>>>(a);
+    LAUNCHED();
+    decode_down_kernel<<<c->sm_count, DEC_THREADS, s2, st>>>(a);
+    LAUNCHED();
+    return 0;
+}
+
+static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T, BlockBufs &b,
+                        uint16_t *d_out, const ApusCudaMoeTrace *tr,
+                        bool with_shared, cudaStream_t st) {
+    FinalizeArgs f;
+    memset(&f, 0, sizeof f);
+    f.T = T;
+    f.H = (int)cfg.hidden;
+    f.TK = (int)cfg.top_k;
+    f.eo = b.eo;
+    f.rw = b.rw;
+    f.sy = with_shared ? b.sy : nullptr;
+    f.sgl = b.sgl;
+    f.out = d_out;
+    f.tr_routed = tr ? tr->moe_routed : nullptr;
+    f.tr_shared = tr ? tr->moe_shared : nullptr;
+    f.tr_out = tr ? tr->moe_out : nullptr;
+    long total = (long)T * (cfg.hidden / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > c->sm_count * 8) blocks = c->sm_count * 8;
+    moe_finalize_kernel<<<blocks, 256, 0, st>>>(f);
+    LAUNCHED();
+    return 0;
+}
+
+static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
+                            uint16_t *d_out, size_t T,
+                            const ApusCudaMoeTrace *d_tr, cudaStream_t st) {
+    Ctx *c = g_ctx;
+    const ApusCudaMoeCfg &cfg = L->cfg;
+    if (L->e_begin != 0 || L->e_end != cfg.experts)
+        return fail("moe_block needs all experts resident; use the "
+                    "expert-parallel entry points for a partial layer");
+    c->last_block_launches = 0;
+    const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
+    BlockBufs b;
+    block_layout(cfg, T, nullptr, &b, prefill);
+    if (arena_reserve(c->ws, b.total)) return 1;
+    if (block_layout(cfg, T, &c->ws, &b, prefill)) return 1;
+    const int Ti = (int)T, E = (int)cfg.experts, H = (int)cfg.hidden,
+              TK = (int)cfg.top_k;
+    if (launch_router(c, d_ln2, L->rtr_w, Ti, E, H, TK, L->wmin, b.idx, b.rw,
+                      nullptr, L->sh_gate, b.sgl, st))
+        return 1;
+    if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
+    if (prefill) {
+        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
+                                L->exp_gu, L->exp_d, L->sh_g, L->sh_u, L->sh_d,
+                                d_ln2, Ti, b.d, b.xg, b.act, b.sa, b.eo, b.sy,
+                                b.tiles, c->d_status, st,
+                                &c->last_block_launches))
+            return fail("%s", prefill_last_error());
+        c->launches += 0;   /* counted inside */
+    } else {
+        if (run_decode_experts(c, L, d_ln2, Ti, b, true, st)) return 1;
+    }
+    if (run_finalize(c, cfg, Ti, b, d_out, d_tr, true, st)) return 1;
+    if (d_tr && d_tr->rtr_idx)
+        CU_OK(cudaMemcpyAsync(d_tr->rtr_idx, b.idx, T * TK * 4,
+                              cudaMemcpyDeviceToDevice, st));
+    if (d_tr && d_tr->rtr_w)
+        CU_OK(cudaMemcpyAsync(d_tr->rtr_w, b.rw, T * TK * 2,
+                              cudaMemcpyDeviceToDevice, st));
+    return 0;
+}
+
+extern "C" int apus_cuda_moe_block_dev(ApusCudaLayer *layer,
+                                       const uint16_t *d_ln2, uint16_t *d_out,
+                                       size_t T, const ApusCudaMoeTrace *d_tr,
+                                       void *stream) {
+    if (!layer || !d_ln2 || !d_out || !T) return fail("moe_block_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    if (layer->maps == nullptr && prefill_supported(layer->cfg) &&
+        (int)T > g_ctx->decode_max_t) {
+        layer->maps = prefill_maps_create(layer->cfg, layer->exp_gu,
+                                          layer->exp_d, layer->sh_g,
+                                          layer->sh_u, layer->sh_d,
+                                          layer->e_end - layer->e_begin);
+        if (!layer->maps) return fail("%s", prefill_last_error());
+    }
+    return block_dev_locked(layer, d_ln2, d_out, T, d_tr, st);
+}
+
+extern "C" int apus_cuda_last_block_launches(void) {
+    return g_ctx ? g_ctx->last_block_launches : 0;
+}
+extern "C" int apus_cuda_last_block_status(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_ctx) return -1;
+    int st = -1;
+    if (cudaMemcpy(&st, g_ctx->d_status, 4, cudaMemcpyDeviceToHost) !=
+        cudaSuccess)
+        return -1;
+    if (st) cudaMemset(g_ctx->d_status, 0, 4);
+    return st;
+}
+
+extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
+                                   const ApusCudaMoeW *w, const uint16_t *ln2,
+                                   uint16_t *moe_out, size_t T,
+                                   const ApusCudaMoeTrace *tr) {
+    if (cfg_check(cfg)) return 1;
+    if (!w || !w->rtr_w || !w->exp_gu || !w->exp_d || !w->sh_g || !w->sh_u ||
+        !w->sh_d || !w->sh_gate || !ln2 || !moe_out || !T)
+        return fail("moe_block: null argument or T == 0");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    ApusCudaLayer *L = nullptr;
+    auto it = c->layers.find(w->rtr_w);
+    if (it != c->layers.end()) {
+        L = it->second;
+        if (memcmp(&L->cfg, cfg, sizeof *cfg) != 0)
+            return fail("moe_block: layer key reused with a different shape");
+    } else {
+        if (apus_cuda_layer_create(cfg, w, 0, cfg->experts, &L)) return 1;
+        c->layers.emplace(w->rtr_w, L);
+    }
+    const size_t H = cfg->hidden, TK = cfg->top_k;
+    size_t need = 2 * T * H * 2 + T * TK * 6 + 3 * T * H * 2 + 8192;
+    if (arena_reserve(c->io, need)) return 1;
+    c->io.reset();
+    uint16_t *dx = (uint16_t *)c->io.take(T * H * 2);
+    uint16_t *dout = (uint16_t *)c->io.take(T * H * 2);
+    ApusCudaMoeTrace dtr;
+    memset(&dtr, 0, sizeof dtr);
+    if (tr) {
+        if (tr->rtr_idx) dtr.rtr_idx = (int32_t *)c->io.take(T * TK * 4);
+        if (tr->rtr_w) dtr.rtr_w = (uint16_t *)c->io.take(T * TK * 2);
+        if (tr->moe_routed) dtr.moe_routed = (uint16_t *)c->io.take(T * H * 2);
+        if (tr->moe_shared) dtr.moe_shared = (uint16_t *)c->io.take(T * H * 2);
+    }
+    CU_OK(cudaMemcpyAsync(dx, ln2, T * H * 2, cudaMemcpyHostToDevice, c->stream));
+    if (apus_cuda_moe_block_dev(L, dx, dout, T, tr ? &dtr : nullptr, c->stream))
+        return 1;
+    CU_OK(cudaMemcpyAsync(moe_out, dout, T * H * 2, cudaMemcpyDeviceToHost,
+                          c->stream));
+    if (tr) {
+        if (tr->rtr_idx)
+            CU_OK(cudaMemcpyAsync(tr->rtr_idx, dtr.rtr_idx, T * TK * 4,
+                                  cudaMemcpyDeviceToHost, c->stream));
+        if (tr->rtr_w)
+            CU_OK(cudaMemcpyAsync(tr->rtr_w, dtr.rtr_w, T * TK * 2,
+                                  cudaMemcpyDeviceToHost, c->stream));
+        if (tr->moe_routed)
+            CU_OK(cudaMemcpyAsync(tr->moe_routed, dtr.moe_routed, T * H * 2,
+                                  cudaMemcpyDeviceToHost, c->stream));
+        if (tr->moe_shared)
+            CU_OK(cudaMemcpyAsync(tr->moe_shared, dtr.moe_shared, T * H * 2,
+                                  cudaMemcpyDeviceToHost, c->stream));
+    }
+    int st = 0;
+    CU_OK(cudaMemcpyAsync(&st, c->d_status, 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(cudaStreamSynchronize(c->stream));
+    if (tr && tr->moe_out) memcpy(tr->moe_out, moe_out, T * H * 2);
+    if (st) {
+        cudaMemset(c->d_status, 0, 4);
+        return fail("moe_block: device status %d (a bounded wait gave up or "
+                    "an index was out of range)", st);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* stages on device pointers                                                 */
+/* ------------------------------------------------------------------------ */
+
+extern "C" int apus_cuda_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
+                                   size_t T, int32_t *d_idx, uint16_t *d_w,
+                                   void *stream) {
+    if (!L || !d_x || !d_idx || !T) return fail("route_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    g_ctx->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    return launch_router(g_ctx, d_x, L->rtr_w, (int)T, (int)L->cfg.experts,
+                         (int)L->cfg.hidden, (int)L->cfg.top_k, L->wmin, d_idx,
+                         d_w, nullptr, nullptr, nullptr, st);
+}
+
+extern "C" int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T,
+                                      size_t topk, size_t E, int32_t *d_counts,
+                                      int32_t *d_offsets, int32_t *d_perm,
+                                      void *stream) {
+    size_t A = T * topk;
+    if (!d_idx || !A || !E) return fail("dispatch_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    size_t need = dispatch_scratch_bytes(A, E) + 1024;
+    if (arena_reserve(c->io, need)) return 1;
+    c->io.reset();
+    DispatchOut o;
+    memset(&o, 0, sizeof o);
+    o.counts = d_counts;
+    o.offsets = d_offsets;
+    o.perm = d_perm;
+    int32_t *uh = (int32_t *)c->io.take(dispatch_scratch_bytes(A, E));
+    return launch_dispatch(c, d_idx, (int)A, (int)E, o, uh, st);
+}
+
+extern "C" int apus_cuda_rmsnorm_dev(const uint16_t *d_x, const uint16_t *d_w,
+                                     uint16_t *d_y, size_t T, size_t N,
+                                     void *stream) {
+    if (!d_x || !d_y || !T || !N) return fail("rmsnorm_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    size_t smem = 4 * N * sizeof(float);
+    if (smem > 48 * 1024) {
+        if (smem > (size_t)g_ctx->smem_optin) return fail("rmsnorm: N too large");
+        CU_OK(cudaFuncSetAttribute(rmsnorm_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    }
+    rmsnorm_kernel<<<(unsigned)((T + 3) / 4), 128, smem, st>>>(d_x, d_w, d_y,
+                                                               (int)T, (int)N);
+    LAUNCHED();
+    return 0;
+}
+
+extern "C" int apus_cuda_resadd_dev(const uint16_t *d_a, const uint16_t *d_b,
+                                    uint16_t *d_out, size_t n, void *stream) {
+    if (!d_a || !d_b || !d_out || !n) return fail("resadd_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    size_t blocks = (n + 255) / 256;
+    if (blocks > (size_t)g_ctx->sm_count * 16) blocks = g_ctx->sm_count * 16;
+    resadd_kernel<<<(unsigned)blocks, 256, 0, st>>>(d_a, d_b, d_out, n);
+    LAUNCHED();
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* synthetic tensors                                                         */
+/* ------------------------------------------------------------------------ */
+
+extern "C" void apus_synth_fill_host(uint16_t *dst, size_t n, uint64_t seed,
+                                     uint32_t layer, uint32_t tensor_id,
+                                     uint64_t first, double sigma) {
+    const uint64_t key = apus_synth_key(seed, layer, tensor_id);
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)n; i++)
+        dst[i] = apus_synth_bf16(key, first + (uint64_t)i, sigma);
+}
+
+extern "C" int apus_synth_fill_dev(uint16_t *d_dst, size_t n, uint64_t seed,
+                                   uint32_t layer, uint32_t tensor_id,
+                                   uint64_t first, double sigma, void *stream) {
+    if (!d_dst || !n) return fail("synth_fill_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    const uint64_t key = apus_synth_key(seed, layer, tensor_id);
+    size_t blocks = (n + 255) / 256;
+    if (blocks > (size_t)g_ctx->sm_count * 32) blocks = g_ctx->sm_count * 32;
+    synth_fill_kernel<<<(unsigned)blocks, 256, 0, st>>>(d_dst, n, key, first,
+                                                        sigma);
+    LAUNCHED();
+    return 0;
+}

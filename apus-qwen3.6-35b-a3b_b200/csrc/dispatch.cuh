@@ -1,0 +1,234 @@
+/*
+ * dispatch.cuh — token-to-expert dispatch: histogram, prefix sum, STABLE
+ * permutation.
+ *
+ * The CPU engine never materialises a permutation; its batched body scans all
+ * assignments once per expert (c/layer.h:599-606) and scatters results back
+ * with a second scan (c/layer.h:614-620).  The order those loops imply is:
+ * experts ascending; inside an expert, tokens ascending, then slots
+ * ascending — i.e. a stable counting sort of the flat assignment index
+ * a = t*topk + j by expert id.  These kernels produce exactly that order
+ * (atomics are used for counts only, never for placement):
+ *
+ *   counts[e], offsets[e] (exclusive, offsets[E] = T*topk),
+ *   perm[p]  = flat assignment sitting at sorted position p,
+ *   pos[a]   = sorted position of flat assignment a (inverse of perm).
+ *
+ * Work unit = 256 consecutive assignments handled by one warp in 8 ordered
+ * steps of 32; __match_any_sync ranks equal keys inside a step by lane, a
+ * per-warp cursor carries the rank across steps, and a scan over
+ * (expert, unit) gives every unit its base — so placement is deterministic
+ * and stable at any grid size.
+ *
+ * The same pass also emits the token groups the decode kernels iterate:
+ * every expert's rows cut into groups of at most GROUP_TOKENS.
+ */
+#pragma once
+#include "common.cuh"
+
+namespace apus {
+
+constexpr int DISPATCH_UNIT = 256;      /* assignments per warp */
+constexpr int DISPATCH_WARPS = 8;       /* warps per block */
+constexpr int GROUP_TOKENS = 4;         /* rows per decode token group */
+
+struct DispatchOut {
+    int32_t *counts;     /* [E] */
+    int32_t *offsets;    /* [E+1] */
+    int32_t *perm;       /* [A] */
+    int32_t *pos;        /* [A]  (may be NULL) */
+    int32_t *grp_expert; /* [<= A] expert of each token group (may be NULL) */
+    int32_t *grp_first;  /* [<= A] first sorted position of the group */
+    int32_t *grp_n;      /* [<= A] rows in the group (1..GROUP_TOKENS) */
+    int32_t *n_groups;   /* [1] */
+};
+
+/* ---- small problems: one block does everything -------------------------- */
+/* A <= 4096, E <= 1024.  Shared: hist[E] + cursor[E] + scratch. */
+__global__ void __launch_bounds__(256)
+dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
+                      DispatchOut o, int *status) {
+    extern __shared__ int sm[];
+    int *hist = sm;            /* [E] */
+    int *cursor = sm + E;      /* [E] */
+    __shared__ int warp_tot[8];
+    __shared__ int s_ngroups;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < E; e += 256) hist[e] = 0;
+    if (tid == 0) s_ngroups = 0;
+    __syncthreads();
+    for (int a = tid; a < A; a += 256) {
+        int k = idx[a];
+        if (k < 0 || k >= E) { set_status(status, ST_BAD_INDEX); continue; }
+        atomicAdd(&hist[k], 1);
+    }
+    __syncthreads();
+    /* exclusive scan over experts: thread t owns bins [t*per, (t+1)*per) */
+    const int per = (E + 255) / 256;
+    int local = 0;
+    for (int j = 0; j < per; j++) {
+        int e = tid * per + j;
+        if (e < E) local += hist[e];
+    }
+    int inc = local;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += v;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; w++) base += warp_tot[w];
+    int run = base + inc - local;
+    for (int j = 0; j < per; j++) {
+        int e = tid * per + j;
+        if (e < E) {
+            int c = hist[e];
+            o.counts[e] = c;
+            o.offsets[e] = run;
+            cursor[e] = run;
+            if (o.grp_expert && c > 0) {
+                int ng = (c + GROUP_TOKENS - 1) / GROUP_TOKENS;
+                int g0 = atomicAdd(&s_ngroups, ng);
+                /* group order is irrelevant to results; record and move on */
+                for (int g = 0; g < ng; g++) {
+                    o.grp_expert[g0 + g] = e;
+                    o.grp_first[g0 + g] = run + g * GROUP_TOKENS;
+                    int left = c - g * GROUP_TOKENS;
+                    o.grp_n[g0 + g] = left < GROUP_TOKENS ? left : GROUP_TOKENS;
+                }
+            }
+            run += c;
+        }
+    }
+    if (tid == 255) o.offsets[E] = base + inc;   /* == number of valid keys */
+    __syncthreads();
+    if (tid == 0 && o.n_groups) *o.n_groups = s_ngroups;
+    /* stable placement: warp 0 walks the assignments in order */
+    if (warp == 0) {
+        for (int a0 = 0; a0 < A; a0 += 32) {
+            int a = a0 + lane;
+            int k = (a < A) ? idx[a] : -1;
+            bool ok = (k >= 0 && k < E);
+            unsigned act = __ballot_sync(0xffffffffu, ok);
+            if (ok) {
+                unsigned peers = __match_any_sync(act, k);
+                int rank = __popc(peers & ((1u << lane) - 1u));
+                int dst = cursor[k] + rank;
+                o.perm[dst] = a;
+                if (o.pos) o.pos[a] = dst;
+                __syncwarp(act);
+                if (rank == 0) cursor[k] += __popc(peers);
+            }
+            __syncwarp();
+        }
+    }
+}
+
+/* ---- large problems: three passes ---------------------------------------- */
+/* pass 1: per-unit histograms, unit_hist[unit][e] */
+__global__ void __launch_bounds__(DISPATCH_WARPS * 32)
+dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
+                     int32_t *__restrict__ unit_hist, int *status) {
+    extern __shared__ int sm[];   /* [DISPATCH_WARPS][E] */
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int unit = blockIdx.x * DISPATCH_WARPS + warp;
+    int *h = sm + warp * E;
+    for (int e = lane; e < E; e += 32) h[e] = 0;
+    __syncwarp();
+    const int a_lo = unit * DISPATCH_UNIT;
+    if (a_lo < A) {
+        const int a_hi = min(A, a_lo + DISPATCH_UNIT);
+        for (int a = a_lo + lane; a < a_hi; a += 32) {
+            int k = idx[a];
+            if (k < 0 || k >= E) { set_status(status, ST_BAD_INDEX); continue; }
+            atomicAdd(&h[k], 1);
+        }
+        __syncwarp();
+        for (int e = lane; e < E; e += 32)
+            unit_hist[(size_t)unit * E + e] = h[e];
+    }
+}
+
+/* pass 2: one block.  For each expert, exclusive prefix over units (in
+ * place), totals -> counts; exclusive scan over experts -> offsets; token
+ * groups. */
+__global__ void __launch_bounds__(1024)
+dispatch_scan_kernel(int32_t *__restrict__ unit_hist, int n_units, int E,
+                     DispatchOut o) {
+    __shared__ int warp_tot[32];
+    __shared__ int s_ngroups;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_ngroups = 0;
+    int total = 0;
+    if (tid < E) {
+        for (int u = 0; u < n_units; u++) {
+            int v = unit_hist[(size_t)u * E + tid];
+            unit_hist[(size_t)u * E + tid] = total;
+            total += v;
+        }
+    }
+    int inc = total;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += v;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; w++) base += warp_tot[w];
+    const int off = base + inc - total;
+    if (tid < E) {
+        o.counts[tid] = total;
+        o.offsets[tid] = off;
+        if (o.grp_expert && total > 0) {
+            int ng = (total + GROUP_TOKENS - 1) / GROUP_TOKENS;
+            int g0 = atomicAdd(&s_ngroups, ng);
+            for (int g = 0; g < ng; g++) {
+                o.grp_expert[g0 + g] = tid;
+                o.grp_first[g0 + g] = off + g * GROUP_TOKENS;
+                int left = total - g * GROUP_TOKENS;
+                o.grp_n[g0 + g] = left < GROUP_TOKENS ? left : GROUP_TOKENS;
+            }
+        }
+    }
+    if (tid == 1023) o.offsets[E] = base + inc;
+    __syncthreads();
+    if (tid == 0 && o.n_groups) *o.n_groups = s_ngroups;
+}
+
+/* pass 3: stable placement inside each unit */
+__global__ void __launch_bounds__(DISPATCH_WARPS * 32)
+dispatch_permute_kernel(const int32_t *__restrict__ idx, int A, int E,
+                        const int32_t *__restrict__ unit_hist, DispatchOut o) {
+    extern __shared__ int sm[];   /* [DISPATCH_WARPS][E] cursors */
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int unit = blockIdx.x * DISPATCH_WARPS + warp;
+    const int a_lo = unit * DISPATCH_UNIT;
+    if (a_lo >= A) return;
+    int *cursor = sm + warp * E;
+    for (int e = lane; e < E; e += 32)
+        cursor[e] = o.offsets[e] + unit_hist[(size_t)unit * E + e];
+    __syncwarp();
+    const int a_hi = min(A, a_lo + DISPATCH_UNIT);
+    for (int a0 = a_lo; a0 < a_hi; a0 += 32) {
+        int a = a0 + lane;
+        int k = (a < a_hi) ? idx[a] : -1;
+        bool ok = (k >= 0 && k < E);
+        unsigned act = __ballot_sync(0xffffffffu, ok);
+        if (ok) {
+            unsigned peers = __match_any_sync(act, k);
+            int rank = __popc(peers & ((1u << lane) - 1u));
+            int dst = cursor[k] + rank;
+            o.perm[dst] = a;
+            if (o.pos) o.pos[a] = dst;
+            __syncwarp(act);
+            if (rank == 0) cursor[k] += __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace apus

@@ -1,0 +1,235 @@
+/*
+ * router.cuh — fused router: BF16 logits -> fp32 softmax -> top-k (lowest
+ * index wins ties) -> renormalised BF16 weights, for a tile of tokens per CTA.
+ *
+ * Replaces apus_moe_route (c/moe.h:357-371) and its helpers
+ * apus_moe_router_probs (c/moe.h:321-335) / apus_moe_router_select
+ * (c/moe.h:339-355).  Selected ids must be bit-identical to the CPU engine's,
+ * and the engine rounds its logits to BF16 before the softmax, so one fp32
+ * ulp in a logit can flip a BF16 code and with it a selection.  The logit of
+ * (token, expert) is therefore accumulated exactly as the CPU anchor does it
+ * (c/bf16.h:285-294): one chain per (token, expert), k strictly ascending,
+ * one rounding for the product and one for the add.
+ *
+ * Fast path: a product of two BF16 values has at most 16 significant bits,
+ * so it is exact in fp32 whenever it does not underflow below 2^-133; then
+ * rn(w*x) == w*x and fma(w, x, acc) == rn(rn(w*x) + acc) bit for bit.  The CTA
+ * checks (smallest nonzero |w| of the router matrix, supplied by the host) x
+ * (smallest nonzero |x| of its token tile) >= 2^-120 and takes the FMA chain;
+ * otherwise it runs the literal multiply-then-add chain.
+ *
+ * Softmax: max by value; q_e = exp(l_e - m) evaluated in fp64 and rounded to
+ * fp32 (glibc's expf is correctly rounded in all but vanishingly rare cases,
+ * so this tracks it; a last-bit difference can only move a weight, never a
+ * selection, because distinct BF16 logits give probabilities many ulps
+ * apart and equal logits give equal probabilities on both sides); the
+ * denominator is the ascending sequential fp32 sum; p_e = q_e / s; selection
+ * on p with strict '>' from -inf; renormalisation sum in selection order.
+ */
+#pragma once
+#include "common.cuh"
+
+namespace apus {
+
+constexpr int ROUTER_THREADS = 288;   /* 256 expert chains + a warp for the extra row */
+
+template <int TT, bool FMA>
+__device__ __forceinline__ void router_chains(const uint16_t *__restrict__ wrow,
+                                              const float *__restrict__ xs,
+                                              int K, float (&acc)[TT]) {
+    /* wrow: this thread's expert row; xs: [TT][K] fp32 in shared memory */
+    const bool vec = ((K & 7) == 0) && ((((uintptr_t)wrow) & 15) == 0);
+    int k = 0;
+    if (vec) {
+#pragma unroll 2
+        for (; k < K; k += 8) {
+            uint4 wv = ldg16(wrow + k);
+            float wf[8];
+            wf[0] = bf16lo(wv.x); wf[1] = bf16hi(wv.x);
+            wf[2] = bf16lo(wv.y); wf[3] = bf16hi(wv.y);
+            wf[4] = bf16lo(wv.z); wf[5] = bf16hi(wv.z);
+            wf[6] = bf16lo(wv.w); wf[7] = bf16hi(wv.w);
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                const float4 xa =
+                    *reinterpret_cast<const float4 *>(xs + (size_t)t * K + k);
+                const float4 xb = *reinterpret_cast<const float4 *>(
+                    xs + (size_t)t * K + k + 4);
+                const float xf[8] = {xa.x, xa.y, xa.z, xa.w,
+                                     xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (FMA)
+                        acc[t] = __fmaf_rn(wf[j], xf[j], acc[t]);
+                    else
+                        acc[t] = __fadd_rn(acc[t], __fmul_rn(wf[j], xf[j]));
+                }
+            }
+        }
+    } else {
+        for (; k < K; k++) {
+            float wf = bf16_f32(__ldg(wrow + k));
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                float xf = xs[(size_t)t * K + k];
+                if (FMA)
+                    acc[t] = __fmaf_rn(wf, xf, acc[t]);
+                else
+                    acc[t] = __fadd_rn(acc[t], __fmul_rn(wf, xf));
+            }
+        }
+    }
+}
+
+/*
+ * grid = ceil(T / TT); block = 256.  Dynamic shared memory:
+ *   xs   float [TT][K]
+ *   ps   float [TT][E]      logits, then exps, then probabilities
+ * wmin = smallest nonzero |w| over the router matrix (0 = unknown: always
+ * take the literal multiply-then-add chain).  topk == 0 is not allowed;
+ * w_out may be NULL (ids only, c/moe.h:373-383); logits_out may be NULL.
+ * extra_row [K] (optional) is one more weight row scored against every token
+ * with the same exact chain, its BF16 result written to extra_out[t]: the
+ * block uses it for the shared expert's gate logit (c/layer.h:355), which
+ * then costs no launch and no extra latency.
+ */
+template <int TT>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_topk_kernel(const uint16_t *__restrict__ x,
+                   const uint16_t *__restrict__ wr, int T, int E, int K,
+                   int topk, float wmin, int32_t *__restrict__ idx_out,
+                   uint16_t *__restrict__ w_out,
+                   uint16_t *__restrict__ logits_out,
+                   const uint16_t *__restrict__ extra_row,
+                   uint16_t *__restrict__ extra_out) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *xs = reinterpret_cast<float *>(smem_raw);
+    float *ps = xs + (size_t)TT * K;
+    __shared__ unsigned int s_xmin;
+
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * TT;
+    if (tid == 0) s_xmin = 0x7f800000u;
+    __syncthreads();
+
+    /* stage the token tile as fp32; track the smallest nonzero |x| */
+    unsigned int xmin = 0x7f800000u;
+    for (int i = tid; i < TT * K; i += ROUTER_THREADS) {
+        int t = i / K, k = i - t * K;
+        float v = 0.0f;
+        if (t0 + t < T) {
+            uint16_t c = x[(size_t)(t0 + t) * K + k];
+            v = bf16_f32(c);
+            unsigned int a = ((unsigned int)c << 16) & 0x7fffffffu;
+            if (a != 0 && a < xmin) xmin = a;
+        }
+        xs[i] = v;
+    }
+    atomicMin(&s_xmin, xmin);
+    __syncthreads();
+    const double prod_floor = 7.52316384526264e-37;   /* 2^-120 */
+    const bool use_fma =
+        (wmin > 0.0f) &&
+        ((double)wmin * (double)__uint_as_float(s_xmin) >= prod_floor);
+
+    /* one chain per (token, expert) */
+    const int rows = E + (extra_row ? 1 : 0);
+    for (int e = tid; e < rows; e += ROUTER_THREADS) {
+        float acc[TT];
+#pragma unroll
+        for (int t = 0; t < TT; t++) acc[t] = 0.0f;
+        if (e == E) {
+            router_chains<TT, false>(extra_row, xs, K, acc);
+#pragma unroll
+            for (int t = 0; t < TT; t++)
+                if (t0 + t < T) extra_out[t0 + t] = bf16_bits(acc[t]);
+            continue;
+        }
+        const uint16_t *wrow = wr + (size_t)e * K;
+        if (use_fma)
+            router_chains<TT, true>(wrow, xs, K, acc);
+        else
+            router_chains<TT, false>(wrow, xs, K, acc);
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            uint16_t code = bf16_bits(acc[t]);
+            ps[(size_t)t * E + e] = bf16_f32(code);
+            if (logits_out && t0 + t < T)
+                logits_out[(size_t)(t0 + t) * E + e] = code;
+        }
+    }
+    __syncthreads();
+
+    /* one warp per token: softmax, selection, renormalisation */
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int t = warp; t < TT; t += ROUTER_THREADS / 32) {
+        if (t0 + t >= T) break;
+        float *p = ps + (size_t)t * E;
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, p[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        for (int e = lane; e < E; e += 32)
+            p[e] = (float)exp((double)__fsub_rn(p[e], m));
+        __syncwarp();
+        float s = 0.0f;
+        if (lane == 0)
+            for (int e = 0; e < E; e++) s = __fadd_rn(s, p[e]);
+        s = __shfl_sync(0xffffffffu, s, 0);
+        for (int e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], s);
+        __syncwarp();
+
+        int my_e = 0;
+        float my_p = 0.0f;
+        for (int i = 0; i < topk; i++) {
+            float bv = -INFINITY;
+            int be = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                float v = p[e];
+                if (v > bv) { bv = v; be = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            if (be == 0x7fffffff) {   /* nothing left above -inf: the CPU
+                                       * loop leaves best = 0 */
+                be = 0;
+                bv = p[0];
+            }
+            if (lane == i) { my_e = be; my_p = bv; }
+            if (lane == (be & 31)) p[be] = -INFINITY;
+            __syncwarp();
+        }
+        if (w_out) {
+            float sw = 0.0f;
+            for (int i = 0; i < topk; i++)
+                sw = __fadd_rn(sw, __shfl_sync(0xffffffffu, my_p, i));
+            if (lane < topk)
+                w_out[(size_t)(t0 + t) * topk + lane] =
+                    bf16_bits(__fdiv_rn(my_p, sw));
+        }
+        if (lane < topk) idx_out[(size_t)(t0 + t) * topk + lane] = my_e;
+    }
+}
+
+/* smallest nonzero |w| over n BF16 codes, as fp32 bits (min-reduced into
+ * *out, which the host initialises to +inf bits). */
+__global__ void bf16_min_nonzero_kernel(const uint16_t *__restrict__ w,
+                                        size_t n, unsigned int *out) {
+    unsigned int m = 0x7f800000u;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        unsigned int a = ((unsigned int)w[i] << 16) & 0x7fffffffu;
+        if (a != 0 && a < m) m = a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMin(out, m);
+}
+
+}  // namespace apus

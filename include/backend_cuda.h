@@ -1,0 +1,239 @@
+/*
+ * backend_cuda.h — CUDA (NVIDIA B200, sm_100a) backend for the MoE block of
+ * the apus-qwen engine.  Pure C11 interface; the implementation is
+ * backend_cuda.cu.  It sits beside the engine's c/backend_metal.h and keeps
+ * that header's conventions: plain pointers and sizes, BF16 as uint16_t
+ * codes, row-major tensors, `0` = "produced the result", nonzero =
+ * "unsupported / failed" (c/backend_metal.h:65-67), host buffers owned by the
+ * caller, weights never written or freed by the backend.
+ *
+ * Two layers of entry points:
+ *
+ *  1. The engine's three per-matmul hooks (c/backend_metal.h:79-86), host
+ *     pointers, synchronous.  Their kernels accumulate in the engine's
+ *     normative order (ascending k, one fp32 rounding per step), so a taken
+ *     hook is bit-identical to the engine's x86 CPU dispatch.
+ *
+ *  2. The MoE block as ONE operator (router -> top-k -> dispatch -> routed
+ *     SwiGLU experts + shared expert -> weighted combine), which is what
+ *     c/layer.h:333-370 (one token) and c/layer.h:570-651 (T tokens) assemble
+ *     from 21 separate matmul calls.  Host-pointer form for the drop-in,
+ *     device-pointer form (weights resident in HBM) for serving and
+ *     benchmarks.
+ *
+ * Numerics of the block operator: router logits, softmax, selection and
+ * renormalisation follow c/moe.h:321-371 exactly (selected expert ids and the
+ * dispatch permutation are bit-exact); expert products accumulate in fp32 in
+ * a different order than the CPU anchor and keep every BF16 rounding point of
+ * c/moe.h:25-55 and c/layer.h:356-361, so outputs agree to BF16 tolerance
+ * (max-abs 2e-2, relative L2 1e-2), not bitwise.
+ *
+ * There is no CPU fallback inside this library: if no usable GPU is present
+ * every compute entry point returns nonzero and apus_cuda_enable fails.
+ *
+ * Threading: entry points serialise on one mutex per process (the engine may
+ * call hooks from its forward thread and its prefetch-prediction thread at
+ * the same time, c/backend_metal.mm:202-207).
+ */
+#ifndef APUS_BACKEND_CUDA_H
+#define APUS_BACKEND_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------
+ * Lifecycle and counters — mirror apus_metal_enable / _disable / _is_enabled
+ * and the three counters (c/backend_metal.h:95-104).
+ * ---------------------------------------------------------------------- */
+
+/* Initialise the device (APUS_CUDA_DEVICE, default 0), create the stream and
+ * the weight-residency table, and, when the engine's hook table
+ * `apus_backend_hooks` is linked into the process, fill its three slots
+ * (APUS_CUDA_NO_GEMV / _NO_GEMM / _NO_MATVEC leave a slot NULL, as
+ * c/backend_metal.mm:490-495 does for Metal).  Also fills
+ * apus_cuda_block_hooks unless APUS_CUDA_NO_MOE is set.  Returns 0 on
+ * success; -1 with a message in err otherwise.  Idempotent. */
+int  apus_cuda_enable(char *err, size_t errcap);
+/* Zero the hook tables and release every device allocation (weight cache,
+ * registered layers created through the host-pointer path, workspaces).
+ * Call before freeing model weights. */
+void apus_cuda_disable(void);
+int  apus_cuda_is_enabled(void);
+
+/* Weight bytes resident in HBM / copied host->device so far / kernels
+ * launched so far.  (Metal's "wrapped" zero-copy counter has no CUDA
+ * counterpart: every weight is a copy in HBM.) */
+uint64_t apus_cuda_bytes_resident(void);
+uint64_t apus_cuda_bytes_uploaded(void);
+uint64_t apus_cuda_launches(void);
+/* Text of the last error recorded by any entry point ("" if none). */
+const char *apus_cuda_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Per-matmul entry points — same signatures and layouts as the hook slots
+ * (c/backend_metal.h:80-85) and as the direct entry points
+ * apus_metal_bf16_gemv / _gemm / _matvec_f32 (c/backend_metal.h:109-114).
+ * w [O,K], x [M,K], y [M,O]; HOST pointers; synchronous.  The weight pointer
+ * is the residency key: first sight uploads O*K*2 bytes, later calls reuse
+ * the copy (stable-pointer rule, c/backend_metal.h:42-48).  Budget:
+ * APUS_CUDA_DENSE_MB (default: unlimited); past it the call returns 1.
+ * Zero dimensions return 1 (c/backend_metal.mm:323).
+ * ---------------------------------------------------------------------- */
+int apus_cuda_bf16_gemv(const uint16_t *w, const uint16_t *x, uint16_t *y,
+                        size_t O, size_t K);
+int apus_cuda_bf16_gemm(const uint16_t *w, const uint16_t *x, uint16_t *y,
+                        size_t M, size_t O, size_t K);
+int apus_cuda_bf16_matvec_f32(const uint16_t *w, const uint16_t *x, float *y,
+                              size_t O, size_t K);
+
+/* ------------------------------------------------------------------------
+ * Router and dispatch on their own (host pointers; for kernel-level tests
+ * and for the engine's second caller of the router, c/pilot.h:282-288).
+ * ---------------------------------------------------------------------- */
+
+/* apus_moe_route (c/moe.h:357-371) over T tokens: x [T,K], wg [E,K] ->
+ * idx [T,topk] (selection order), w [T,topk] BF16.  logits [T,E] BF16 is
+ * optional (NULL to skip).  E <= 1024, topk <= 32, topk <= E. */
+int apus_cuda_moe_route(const uint16_t *x, const uint16_t *wg, int32_t *idx,
+                        uint16_t *w, uint16_t *logits, size_t T, size_t E,
+                        size_t K, size_t topk);
+/* apus_moe_route_topn (c/moe.h:373-383): first n ids, no weights. */
+int apus_cuda_moe_route_topn(const uint16_t *x, const uint16_t *wg,
+                             int32_t *idx, size_t n, size_t E, size_t K);
+/* The dispatch order c/layer.h:599-606,614-620 implies: stable counting sort
+ * of the flat assignments a = t*topk + j by expert id.  idx [T*topk] ->
+ * counts [E], offsets [E+1], perm [T*topk]. */
+int apus_cuda_moe_dispatch(const int32_t *idx, size_t T, size_t topk,
+                           size_t E, int32_t *counts, int32_t *offsets,
+                           int32_t *perm);
+
+/* ------------------------------------------------------------------------
+ * The MoE block operator.
+ * ---------------------------------------------------------------------- */
+
+/* MoE fields of ApusLayerCfg (c/layer.h:115,129-130). */
+typedef struct {
+    size_t hidden;        /* H  (2048) */
+    size_t experts;       /* E  (256)  */
+    size_t moe_inter;     /* I  (512)  */
+    size_t shared_inter;  /* Is (512)  */
+    size_t top_k;         /* 8 */
+} ApusCudaMoeCfg;
+
+/* MoE fields of ApusLayerW (c/layer.h:150-156). */
+typedef struct {
+    const uint16_t *rtr_w;    /* [E, H] */
+    const uint16_t *exp_gu;   /* [E, 2I, H] fused gate|up */
+    const uint16_t *exp_d;    /* [E, H, I] */
+    const uint16_t *sh_g;     /* [Is, H] */
+    const uint16_t *sh_u;     /* [Is, H] */
+    const uint16_t *sh_d;     /* [H, Is] */
+    const uint16_t *sh_gate;  /* [1, H] */
+} ApusCudaMoeW;
+
+/* MoE fields of ApusLayerTrace (c/layer.h:186-188); every member optional. */
+typedef struct {
+    int32_t  *rtr_idx;      /* [T, top_k] */
+    uint16_t *rtr_w;        /* [T, top_k] */
+    uint16_t *moe_routed;   /* [T, H] */
+    uint16_t *moe_shared;   /* [T, H] */
+    uint16_t *moe_out;      /* [T, H] */
+} ApusCudaMoeTrace;
+
+/* Host-pointer block operator: argument meaning identical to
+ * apus_layer_moe_batch (c/layer.h:570-573).  The layer's weights are uploaded
+ * on first sight of w->rtr_w (the residency key) and stay in HBM until
+ * apus_cuda_disable.  Synchronous: moe_out and the trace rows are complete on
+ * return.  Returns 0, or nonzero with apus_cuda_last_error() set. */
+int apus_cuda_moe_block(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
+                        const uint16_t *ln2, uint16_t *moe_out, size_t T,
+                        const ApusCudaMoeTrace *tr);
+
+/* Second hook table, for the block operator.  Kept apart from the engine's
+ * three-slot table so that table's layout is untouched.  The engine-side
+ * glue tests `apus_cuda_block_hooks.moe_block` at the top of apus_layer_moe
+ * and apus_layer_moe_batch. */
+typedef struct {
+    int (*moe_block)(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
+                     const uint16_t *ln2, uint16_t *moe_out, size_t T,
+                     const ApusCudaMoeTrace *tr);
+} ApusCudaBlockHooks;
+extern ApusCudaBlockHooks apus_cuda_block_hooks;
+
+/* ---- device-resident form ------------------------------------------------ */
+
+typedef struct ApusCudaLayer ApusCudaLayer;   /* one layer's MoE weights in HBM */
+
+/* Allocate HBM for one layer's MoE weights and, if w is not NULL, upload
+ * them.  Experts [expert_begin, expert_end) are made resident (pass 0, E for
+ * all of them); router, shared expert and shared gate always are.  With
+ * w == NULL the tensors are left uninitialised for apus_cuda_layer_tensor +
+ * a device-side fill. */
+int apus_cuda_layer_create(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
+                           size_t expert_begin, size_t expert_end,
+                           ApusCudaLayer **out);
+void apus_cuda_layer_destroy(ApusCudaLayer *layer);
+/* Device pointer and element count of one tensor of the layer: which = 1
+ * rtr_w, 2 exp_gu (first resident expert), 3 exp_d, 4 sh_g, 5 sh_u, 6 sh_d,
+ * 7 sh_gate. */
+void *apus_cuda_layer_tensor(ApusCudaLayer *layer, int which, size_t *elems);
+/* Call after writing rtr_w through apus_cuda_layer_tensor: rescans the
+ * router weights for the magnitude bound the router kernel's fast path
+ * depends on. */
+int apus_cuda_layer_refresh(ApusCudaLayer *layer);
+
+/* The block on device pointers: d_ln2 [T,H] -> d_out [T,H]; d_tr members are
+ * device pointers (or NULL).  Enqueued on `stream` (a cudaStream_t, NULL =
+ * the backend's own stream); does not synchronise.  Workspace comes from a
+ * per-process arena that grows on demand (growth synchronises; call
+ * apus_cuda_reserve first to avoid that inside a timed region or a stream
+ * capture).  Path selection: T <= APUS_CUDA_DECODE_MAX_T (default 64) takes
+ * the bandwidth-bound grouped-GEMV kernels, larger T the tcgen05 grouped
+ * GEMM. */
+int apus_cuda_moe_block_dev(ApusCudaLayer *layer, const uint16_t *d_ln2,
+                            uint16_t *d_out, size_t T,
+                            const ApusCudaMoeTrace *d_tr, void *stream);
+/* Grow the workspace arena for blocks of up to T tokens of this shape. */
+int apus_cuda_reserve(const ApusCudaMoeCfg *c, size_t T);
+/* Kernels one apus_cuda_moe_block_dev call launched last time (for the
+ * benchmark's launch count). */
+int apus_cuda_last_block_launches(void);
+/* Device-side status word of the last block call: 0 = ok; nonzero = a
+ * bounded wait inside a kernel gave up (the context stays usable). */
+int apus_cuda_last_block_status(void);
+
+/* ---- stages of the block, device pointers (kernel-level tests) ---------- */
+int apus_cuda_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
+                        int32_t *d_idx, uint16_t *d_w, void *stream);
+int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T, size_t topk,
+                           size_t E, int32_t *d_counts, int32_t *d_offsets,
+                           int32_t *d_perm, void *stream);
+
+/* ---- the two steps either side of the block (c/layer.h:386,388) --------- */
+/* y = rmsnorm(x, gain 1+w) per row (c/attn.h:175-186; w NULL = zero gain
+ * offset); out = rnd(a + b) (c/layer.h:230-234).  Device pointers. */
+int apus_cuda_rmsnorm_dev(const uint16_t *d_x, const uint16_t *d_w,
+                          uint16_t *d_y, size_t T, size_t N, void *stream);
+int apus_cuda_resadd_dev(const uint16_t *d_a, const uint16_t *d_b,
+                         uint16_t *d_out, size_t n, void *stream);
+
+/* ---- synthetic tensors (benchmarks and tests) ---------------------------- */
+/* Fill n BF16 elements with the counter-based approximately-normal stream
+ * (seed, layer, tensor_id), element index starting at first, scaled by
+ * sigma.  Host and device versions produce identical bits. */
+void apus_synth_fill_host(uint16_t *dst, size_t n, uint64_t seed,
+                          uint32_t layer, uint32_t tensor_id, uint64_t first,
+                          double sigma);
+int apus_synth_fill_dev(uint16_t *d_dst, size_t n, uint64_t seed,
+                        uint32_t layer, uint32_t tensor_id, uint64_t first,
+                        double sigma, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* APUS_BACKEND_CUDA_H */
