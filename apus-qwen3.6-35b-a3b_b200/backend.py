@@ -62,10 +62,12 @@ SYMBOLS = [
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
     "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
+    "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
 ]
 
+STAGES = ("router", "dispatch", "gather", "gate_up", "down", "finalize")
 TENSOR_IDS = dict(rtr_w=1, exp_gu=2, exp_d=3, sh_g=4, sh_u=5, sh_d=6, sh_gate=7)
 
 
@@ -113,6 +115,7 @@ class Backend:
         L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
                                               C.POINTER(MoeTrace), vp]
         L.apus_cuda_reserve.argtypes = [C.POINTER(MoeCfg), sz]
+        L.apus_cuda_last_stage_ms.argtypes = [C.POINTER(C.c_float), C.c_int]
         L.apus_cuda_route_dev.argtypes = [vp, vp, sz, vp, vp, vp]
         L.apus_cuda_dispatch_dev.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
@@ -296,6 +299,17 @@ class Backend:
                                               C.byref(tr) if tr else None,
                                               stream)
         self._check(rc, "apus_cuda_moe_block_dev")
+
+    def stage_timing(self, enable):
+        self._check(self.lib.apus_cuda_stage_timing(1 if enable else 0),
+                    "apus_cuda_stage_timing")
+
+    def last_stage_ms(self):
+        ms = (C.c_float * len(STAGES))()
+        n = self.lib.apus_cuda_last_stage_ms(ms, len(STAGES))
+        if n < 0:
+            raise BackendError("apus_cuda_last_stage_ms failed")
+        return dict(zip(STAGES, (float(v) for v in ms)))
 
     def last_block_launches(self):
         return int(self.lib.apus_cuda_last_block_launches())

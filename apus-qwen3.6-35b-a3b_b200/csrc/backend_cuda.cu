@@ -79,6 +79,11 @@ struct Ctx {
     int decode_max_t = 64;
     int last_block_launches = 0;
     bool hooks_filled = false;
+    /* optional per-stage CUDA events inside the block (benchmarks) */
+    bool stage_timing = false;
+    cudaEvent_t ev[16] = {};
+    int n_ev = 0;
+    int ev_stage[16] = {};
 };
 
 static Ctx *g_ctx = nullptr;
@@ -177,6 +182,15 @@ static int arena_reserve(Arena &a, size_t bytes) {
             return fail("kernel launch: %s (%s:%d)", cudaGetErrorString(e_), \
                         __FILE__, __LINE__);                               \
     } while (0)
+
+/* stage marks: an event before the first stage and after every stage */
+static void stage_mark(Ctx *c, int stage, cudaStream_t st) {
+    if (!c->stage_timing || c->n_ev >= 16) return;
+    if (!c->ev[c->n_ev]) cudaEventCreate(&c->ev[c->n_ev]);
+    cudaEventRecord(c->ev[c->n_ev], st);
+    c->ev_stage[c->n_ev] = stage;
+    c->n_ev++;
+}
 
 /* ------------------------------------------------------------------------ */
 /* lifecycle                                                                 */
@@ -744,8 +758,10 @@ static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
     decode_gate_up_kernel<<<c->sm_count, DEC_THREADS, s1, st>>>(a);
     LAUNCHED();
+    stage_mark(c, APUS_CUDA_STAGE_GATE_UP, st);
     decode_down_kernel<<<c->sm_count, DEC_THREADS, s2, st>>>(a);
     LAUNCHED();
+    stage_mark(c, APUS_CUDA_STAGE_DOWN, st);
     return 0;
 }
 
@@ -789,10 +805,14 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     if (block_layout(cfg, T, &c->ws, &b, prefill)) return 1;
     const int Ti = (int)T, E = (int)cfg.experts, H = (int)cfg.hidden,
               TK = (int)cfg.top_k;
+    c->n_ev = 0;
+    stage_mark(c, -1, st);
     if (launch_router(c, d_ln2, L->rtr_w, Ti, E, H, TK, L->wmin, b.idx, b.rw,
                       nullptr, L->sh_gate, b.sgl, st))
         return 1;
+    stage_mark(c, APUS_CUDA_STAGE_ROUTER, st);
     if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
+    stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (prefill) {
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
                                 L->exp_gu, L->exp_d, L->sh_g, L->sh_u, L->sh_d,
@@ -805,6 +825,7 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
         if (run_decode_experts(c, L, d_ln2, Ti, b, true, st)) return 1;
     }
     if (run_finalize(c, cfg, Ti, b, d_out, d_tr, true, st)) return 1;
+    stage_mark(c, APUS_CUDA_STAGE_FINALIZE, st);
     if (d_tr && d_tr->rtr_idx)
         CU_OK(cudaMemcpyAsync(d_tr->rtr_idx, b.idx, T * TK * 4,
                               cudaMemcpyDeviceToDevice, st));
@@ -831,6 +852,29 @@ extern "C" int apus_cuda_moe_block_dev(ApusCudaLayer *layer,
         if (!layer->maps) return fail("%s", prefill_last_error());
     }
     return block_dev_locked(layer, d_ln2, d_out, T, d_tr, st);
+}
+
+extern "C" int apus_cuda_stage_timing(int enable) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    g_ctx->stage_timing = enable != 0;
+    g_ctx->n_ev = 0;
+    return 0;
+}
+extern "C" int apus_cuda_last_stage_ms(float *ms, int cap) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_ctx || !ms) return -1;
+    for (int i = 0; i < cap; i++) ms[i] = 0.0f;
+    if (g_ctx->n_ev < 2) return 0;
+    if (cudaEventSynchronize(g_ctx->ev[g_ctx->n_ev - 1]) != cudaSuccess)
+        return -1;
+    for (int i = 1; i < g_ctx->n_ev; i++) {
+        float t = 0.0f;
+        cudaEventElapsedTime(&t, g_ctx->ev[i - 1], g_ctx->ev[i]);
+        int sidx = g_ctx->ev_stage[i];
+        if (sidx >= 0 && sidx < cap) ms[sidx] += t;
+    }
+    return g_ctx->n_ev - 1;
 }
 
 extern "C" int apus_cuda_last_block_launches(void) {

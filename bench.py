@@ -1,0 +1,326 @@
+#!/usr/bin/env python3
+"""Benchmark of the MoE-block hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T]
+                  [--impl ours|reference]
+
+One "step" is one pass of the MoE block (router -> top-8 -> dispatch -> routed
+SwiGLU experts + shared expert -> weighted combine) over one batch of T
+synthetic tokens at the Qwen3.6-35B-A3B dimensions (H 2048, 256 experts, top-8,
+I 512).  Default workload: T=512 prefill, one layer, seed 0, weights resident
+in HBM.  Prints ONE JSON line.
+
+  value      tokens/s with inputs already in HBM (CUDA events, max over ranks)
+  e2e        tokens/s through the host-pointer C-ABI call the engine would
+             make (pinned host input, host output, copies inside the timing)
+  roofline   the dominant kernel's algorithmic bytes / its own measured time,
+             against the measured HBM copy bandwidth
+  cpu_baseline  the reference's own C code (oracle/_ref) on this box's cores
+
+--impl reference times only the reference CPU arm and prints the same line
+shape with "impl": "reference".
+"""
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG_DIR = os.path.join(ROOT, "apus-qwen3.6-35b-a3b_b200")
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_prefill_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0,
+                      bf16_tflops_sustained=1400.0)
+
+
+def load_package():
+    spec = importlib.util.spec_from_file_location(
+        "apus_b200", os.path.join(PKG_DIR, "__init__.py"),
+        submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["apus_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+def algorithmic_bytes(cfg, T, unique_experts):
+    """Bytes the block must move once: router matrix, every touched expert's
+    weights, the shared expert, the shared gate row, activations in and out."""
+    H, E, I, Is = cfg["hidden"], cfg["experts"], cfg["moe_inter"], cfg["shared_inter"]
+    slab = (2 * I * H + H * I) * 2
+    shared = (2 * Is * H + H * Is) * 2
+    return E * H * 2 + unique_experts * slab + shared + H * 2 + 2 * T * H * 2
+
+
+def flops(cfg, T):
+    H, E, I, Is, TK = (cfg["hidden"], cfg["experts"], cfg["moe_inter"],
+                       cfg["shared_inter"], cfg["top_k"])
+    per_tok = 2 * (E * H + TK * 3 * I * H + 3 * Is * H + H)
+    return T * per_tok
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.maxmhz = None
+        self.stop_flag = False
+
+    def run(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                 "sw_power_cap"]
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", str(self.index),
+                     "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                f = [s.strip() for s in out.split(",")]
+                self.samples.append(float(f[0]))
+                self.maxmhz = float(f[1])
+                for n, v in zip(names, f[2:]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return dict(sm_mhz=s[len(s) // 2] if s else None,
+                    sm_max_mhz=self.maxmhz, reasons=sorted(self.reasons),
+                    samples=len(s))
+
+
+def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth):
+    """Times the reference's own MoE block (apus_layer_moe_batch, AVX2 rows
+    over its pthread pool) on this host.  Returns (tokens/s, threads,
+    sample-description, ms_per_step)."""
+    from oracle import oracle
+    if not oracle.Reference.available():
+        return None
+    ref = oracle.Reference()
+    W = synth.host_weights(be, cfg, seed=seed)
+    x = synth.host_x(be, T, cfg["hidden"], seed=seed)
+    # bound the sample: the full batch when it is cheap, else a slice of it
+    Ts = T
+    t0 = time.perf_counter()
+    ref.moe_block(cfg, W, x[:min(T, 16)])
+    est = (time.perf_counter() - t0) * T / min(T, 16)
+    while Ts > 16 and est * Ts / T * (steps + warmup) > 60.0:
+        Ts //= 2
+    xs = x[:Ts]
+    for _ in range(warmup):
+        ref.moe_block(cfg, W, xs)
+    best = None
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        ref.moe_block(cfg, W, xs)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    sample = (f"{Ts} of {T} tokens, one layer, apus_layer_moe_batch, "
+              f"best of {steps}")
+    return Ts / best, ref.threads(), sample, best * 1e3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=512)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pkg = load_package()
+    import apus_b200.synth as synth
+    cfg = dict(synth.QWEN_CFG)
+    T = args.tokens
+    config = {"workload": f"one MoE layer, prefill T={T}, uniform router, seed "
+                          f"{args.seed}, H2048 E256 top8 I512",
+              "tokens_per_step": T, "layers": 1,
+              "l2_policy": "inputs larger than L2 (1.6 GB of weights per step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        be = pkg.Backend()
+        steps = max(1, min(args.steps, 5))
+        warm = max(1, min(args.warmup, 2))
+        r = cpu_reference_arm(cfg, T, args.seed, steps, warm, be, synth)
+        if r is None:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": "oracle/_ref was not built"}))
+            return
+        v, threads, sample, ms = r
+        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT,
+                "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16 storage, fp32 arithmetic",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads,
+                                 "kind": "reference", "sample": sample},
+                "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import numpy as np
+    import torch
+    if world > 1:
+        from apus_b200 import ep_bench
+        ep_bench.run(args, cfg, config, pkg, synth, METRIC, UNIT, peaks())
+        return
+
+    torch.cuda.set_device(0)
+    be = pkg.Backend()
+    be.enable()
+    H = cfg["hidden"]
+    W = synth.host_weights(be, cfg, seed=args.seed)
+    x_host = synth.host_x(be, T, H, seed=args.seed)
+    layer = be.layer_create(cfg, W)
+    be.reserve(cfg, T)
+    stream = torch.cuda.current_stream()
+    d_x = torch.from_numpy(x_host.view(np.int16)).cuda()
+    d_out = torch.empty_like(d_x)
+    d_idx = torch.empty((T, cfg["top_k"]), dtype=torch.int32, device="cuda")
+    sp = stream.cuda_stream
+
+    def step():
+        be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp)
+
+    # unique experts touched (for the algorithmic byte count)
+    be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp,
+                     d_trace={"idx": d_idx.data_ptr()})
+    torch.cuda.synchronize()
+    uniq = int(torch.unique(d_idx).numel())
+    launches_per_step = be.last_block_launches()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    status = be.last_block_status()
+
+    # per-stage times, measured live with CUDA events on the launching stream
+    be.stage_timing(True)
+    acc = {}
+    for _ in range(args.steps):
+        step()
+        for k, v in be.last_stage_ms().items():
+            acc[k] = acc.get(k, 0.0) + v
+    be.stage_timing(False)
+    stage_ms = {k: v / args.steps for k, v in acc.items()}
+
+    # end to end through the host-pointer entry point (pinned host buffers)
+    xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
+    xout = torch.empty_like(xin).pin_memory()
+    xin_np, xout_np = xin.numpy().view(np.uint16), xout.numpy().view(np.uint16)
+    c_cfg = pkg.backend.MoeCfg.from_dict(cfg)
+    c_w = pkg.backend.MoeW(*[W[k].ctypes.data for k in
+                             ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u",
+                              "sh_d", "sh_gate")])
+    import ctypes as C
+
+    def e2e_step():
+        rc = be.lib.apus_cuda_moe_block(
+            C.byref(c_cfg), C.byref(c_w),
+            xin_np.ctypes.data_as(C.POINTER(C.c_uint16)),
+            xout_np.ctypes.data_as(C.POINTER(C.c_uint16)), T, None)
+        if rc:
+            raise RuntimeError(be.last_error())
+    for _ in range(max(3, args.warmup)):
+        e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    sampler.stop_flag = True
+    sampler.join()
+    assert np.array_equal(xout_np, d_out.cpu().numpy().view(np.uint16)), \
+        "host-pointer and device-pointer entry points disagree"
+
+    pk = peaks()
+    dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
+    slab_gu = 2 * cfg["moe_inter"] * H * 2
+    slab_d = H * cfg["moe_inter"] * 2
+    A = T * cfg["top_k"]
+    if dom == "gate_up":
+        kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * cfg["moe_inter"] * 2
+    else:
+        kbytes = (uniq + 1) * slab_d + (A + T) * cfg["moe_inter"] * 2 + (A + T) * H * 2
+    achieved = kbytes / (stage_ms[dom] * 1e-3) / 1e9 if stage_ms.get(dom) else None
+    block_bytes = algorithmic_bytes(cfg, T, uniq)
+    line = {
+        "metric": METRIC, "value": T / (ms * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 storage, fp32 accumulate",
+        "data": "synthetic", "config": config,
+        "clocks": sampler.summary(),
+        "e2e": {"value": T / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved,
+                     "peak": pk["hbm_gbs"], "peak_source": pk["_source"],
+                     "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"] if achieved else None,
+                     "traffic": None,
+                     "algorithmic_bytes_per_launch": kbytes},
+        "block": {"algorithmic_bytes": block_bytes,
+                  "hbm_frac_of_measured": block_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                  "tensor_frac_of_measured": flops(cfg, T) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
+                  "unique_experts": uniq, "stage_ms": stage_ms,
+                  "us_per_token": ms * 1e3 / T, "device_status": status},
+    }
+    if not args.no_cpu_baseline:
+        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth)
+        if r is not None:
+            v, threads, sample, _ = r
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
+                                    "kind": "reference", "sample": sample}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -202,6 +202,23 @@ int apus_cuda_reserve(const ApusCudaMoeCfg *c, size_t T);
 /* Kernels one apus_cuda_moe_block_dev call launched last time (for the
  * benchmark's launch count). */
 int apus_cuda_last_block_launches(void);
+/* Per-stage device times of the block (benchmarks): with timing enabled,
+ * apus_cuda_moe_block_dev brackets each stage with CUDA events on the stream
+ * it launches on; apus_cuda_last_stage_ms waits for the last call's events
+ * and fills ms[stage] (milliseconds, indexed by the enum below), returning
+ * the number of intervals measured or -1. */
+enum {
+    APUS_CUDA_STAGE_ROUTER = 0,    /* fused router + top-k + shared-gate logit */
+    APUS_CUDA_STAGE_DISPATCH = 1,  /* histogram, scan, stable permute */
+    APUS_CUDA_STAGE_GATHER = 2,    /* prefill: permuted activation rows */
+    APUS_CUDA_STAGE_GATE_UP = 3,   /* gate/up products + SwiGLU */
+    APUS_CUDA_STAGE_DOWN = 4,      /* down products */
+    APUS_CUDA_STAGE_FINALIZE = 5,  /* weighted combine + shared + add */
+    APUS_CUDA_STAGE_COUNT = 6
+};
+int apus_cuda_stage_timing(int enable);
+int apus_cuda_last_stage_ms(float *ms, int cap);
+
 /* Device-side status word of the last block call: 0 = ok; nonzero = a
  * bounded wait inside a kernel gave up (the context stays usable). */
 int apus_cuda_last_block_status(void);

@@ -1,0 +1,150 @@
+"""GPU parity tests, kernel level, all through the C-ABI: the per-matmul
+hooks, the router and the dispatch against the CPU checker.  Integer and
+index results are compared bit for bit."""
+import os
+
+import numpy as np
+import pytest
+
+from test_oracle_cpu import rd, manifest, f32, tol_ok, rng_codes
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- per-matmul hooks: bitwise the CPU anchor (tests/m10/test_kernels.c) ----
+
+@pytest.mark.parametrize("O,K", [(1, 1), (3, 5), (7, 1), (33, 100), (64, 256),
+                                 (256, 2048), (1024, 2048), (2048, 512),
+                                 (512, 2048), (1, 2048)])
+def test_hook_gemv_matvec_bitwise(gpu, orc, O, K):
+    rng = np.random.default_rng(O * 131 + K)
+    w, x = rng_codes(rng, (O, K), 0.5), rng_codes(rng, K, 1.0)
+    assert np.array_equal(gpu.bf16_gemv(w, x), orc.gemv(w, x))
+    assert np.array_equal(gpu.bf16_matvec_f32(w, x), orc.matvec_f32(w, x))
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 64, 300])
+def test_hook_gemm_bitwise(gpu, orc, M):
+    rng = np.random.default_rng(M)
+    O, K = 96, 200
+    w, x = rng_codes(rng, (O, K), 0.5), rng_codes(rng, (M, K), 1.0)
+    assert np.array_equal(gpu.bf16_gemm(w, x), orc.gemm(w, x))
+
+
+def test_hook_zero_dims_and_counters(gpu):
+    assert gpu.lib.apus_cuda_bf16_gemv(None, None, None, 0, 8) != 0
+    assert gpu.lib.apus_cuda_bf16_gemm(None, None, None, 1, 0, 8) != 0
+    rng = np.random.default_rng(1)
+    w, x = rng_codes(rng, (64, 64), 0.5), rng_codes(rng, 64, 1.0)
+    up0, l0 = gpu.bytes_uploaded(), gpu.launches()
+    gpu.bf16_gemv(w, x)
+    gpu.bf16_gemv(w, x)      # second call reuses the resident copy
+    assert gpu.bytes_uploaded() - up0 == w.nbytes
+    assert gpu.launches() - l0 == 2
+
+
+def test_hooks_inside_the_reference_engine(gpu, ref, be, synth):
+    """Drop-in: the backend's three entry points installed into the
+    reference's own hook table; the reference's MoE block, run through its own
+    layer code, must reproduce its CPU result bit for bit (the per-op hooks
+    keep the anchor's order)."""
+    cfg = synth.MINI_CFG
+    W = synth.host_weights(be, cfg, seed=21, sigma=0.08)
+    x = synth.host_x(be, 5, cfg["hidden"], seed=21)
+    cpu = ref.moe_block(cfg, W, x)
+    l0 = gpu.launches()
+    ref.set_hooks(gpu.lib.apus_cuda_bf16_gemv, gpu.lib.apus_cuda_bf16_gemm,
+                  gpu.lib.apus_cuda_bf16_matvec_f32)
+    try:
+        for batched in (False, True):
+            hooked = ref.moe_block(cfg, W, x, batched=batched)
+            for k in ("idx", "w", "routed", "shared", "out"):
+                assert np.array_equal(cpu[k], hooked[k]), (k, batched)
+    finally:
+        ref.set_hooks(None, None, None)
+    assert gpu.launches() > l0       # the GPU really ran them
+
+
+# ---- router ----------------------------------------------------------------------
+
+def test_router_golden(gpu):
+    m = manifest()
+    E, K, TK = m["RTR_E"], m["RTR_K"], m["RTR_TK"]
+    x = rd("moe_rtr_x.bin", np.uint16)
+    wg = rd("moe_rtr_wg.bin", np.uint16).reshape(E, K)
+    idx, w = gpu.moe_route(x, wg, TK)
+    assert idx[0].tolist() == rd("moe_rtr_idx.bin", np.int64).tolist()
+    assert tol_ok(f32(w[0]).astype(np.float64), rd("moe_rtr_w.bin", np.float64),
+                  0.02, 0.008, 0.008).all()
+    assert gpu.moe_route_topn(x, wg, TK).tolist() == idx[0].tolist()
+    assert gpu.moe_route_topn(x, wg, TK + 4)[:TK].tolist() == idx[0].tolist()
+
+
+def test_router_tie_kats(gpu):
+    E, K, TK = 16, 4, 8
+    x = np.array([0x3F80, 0, 0, 0], np.uint16)
+    wg = np.zeros((E, K), np.uint16)
+    wg[:, 0] = 0x3F00
+    idx, w = gpu.moe_route(x, wg, TK)
+    assert idx[0].tolist() == list(range(8))
+    assert (w[0] == 0x3E00).all()
+    wg[:, 0] = 0
+    wg[:9, 0] = 0x3F80
+    idx, _ = gpu.moe_route(x, wg, TK)
+    assert idx[0].tolist() == list(range(8))
+
+
+@pytest.mark.parametrize("T,E,K,TK,sx,sw", [
+    (1, 256, 2048, 8, 1.0, 0.02), (2, 256, 2048, 8, 1.0, 0.02),
+    (5, 16, 128, 4, 1.0, 0.08), (64, 256, 2048, 8, 1.0, 0.02),
+    (300, 256, 2048, 8, 1.0, 0.02), (1111, 256, 2048, 8, 1.0, 0.02),
+    (37, 100, 72, 6, 1.0, 0.1), (9, 33, 37, 5, 1.0, 0.1),
+    (300, 256, 2048, 8, 1e-19, 1e-19),      # products underflow: literal chain
+])
+def test_router_bit_exact(gpu, orc, T, E, K, TK, sx, sw):
+    """Selected ids, BF16 logits and BF16 routing weights against the CPU
+    checker.  Logit ties are frequent here (256 BF16 logits per token), so
+    the lowest-index rule is exercised on almost every token."""
+    rng = np.random.default_rng(T * 7 + E)
+    x = rng_codes(rng, (T, K), 0.4 * sx)
+    wg = rng_codes(rng, (E, K), sw * 0.5)
+    idx, w, lg = gpu.moe_route(x, wg, TK, want_logits=True)
+    oi, ow, ol = orc.route_batch(x, wg, TK, want_logits=True)
+    assert np.array_equal(lg, ol)            # logits: bit-exact chains
+    assert np.array_equal(idx, oi)           # selection: bit-exact
+    # weights: expf last-bit class only — at most one BF16 ulp, and rare
+    d = np.abs(w.astype(np.int32) - ow.astype(np.int32))
+    assert d.max() <= 1
+    assert (d != 0).mean() <= 0.002
+
+
+# ---- dispatch ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("T,TK,E,skew", [
+    (1, 8, 256, False), (3, 8, 256, False), (5, 4, 16, False),
+    (64, 8, 256, False), (300, 8, 256, False), (512, 8, 256, False),
+    (513, 8, 256, True), (1000, 8, 256, True), (8192, 8, 256, True),
+    (8448, 8, 256, False), (700, 6, 1000, False)])
+def test_dispatch_bit_exact(gpu, orc, T, TK, E, skew):
+    rng = np.random.default_rng(T + E)
+    p = None
+    if skew:
+        p = np.arange(1, E + 1, dtype=np.float64) ** -1.1
+        p = p[rng.permutation(E)]
+        p /= p.sum()
+    idx = np.stack([rng.choice(E, TK, replace=False, p=p) for _ in range(T)]
+                   ).astype(np.int32)
+    counts, offsets, perm = gpu.moe_dispatch(idx, E)
+    oc, oo, op = orc.dispatch(idx, E)
+    assert np.array_equal(counts, oc)
+    assert np.array_equal(offsets, oo)
+    assert np.array_equal(perm, op)
+
+
+def test_dispatch_rejects_bad_expert_id(gpu):
+    idx = np.array([[0, 1, 2, 999]], np.int32)
+    with pytest.raises(Exception):
+        gpu.moe_dispatch(idx, 16)
+    # the context stays usable
+    c, o, p = gpu.moe_dispatch(np.array([[3, 1, 2, 0]], np.int32), 16)
+    assert p.tolist() == [3, 1, 2, 0]
