@@ -30,6 +30,8 @@
 
 using namespace apus;
 
+constexpr int ROUTER_SMALL_MAX_T = 64;
+
 /* ------------------------------------------------------------------------ */
 /* context                                                                   */
 /* ------------------------------------------------------------------------ */
@@ -76,6 +78,8 @@ struct Ctx {
     Arena io;      /* host-pointer staging */
     int *d_status = nullptr;
     unsigned int *d_scratch_u32 = nullptr;
+    unsigned int *d_router_counters = nullptr;   /* [ROUTER_SMALL_MAX_T], self-resetting */
+    float *d_router_logits = nullptr;            /* [ROUTER_SMALL_MAX_T][1024] */
     int decode_max_t = 64;
     int last_block_launches = 0;
     bool hooks_filled = false;
@@ -153,6 +157,10 @@ static int ctx_init() {
     CU_OK(cudaMalloc(&c->d_status, 256));
     CU_OK(cudaMemset(c->d_status, 0, 256));
     c->d_scratch_u32 = reinterpret_cast<unsigned int *>(c->d_status) + 16;
+    CU_OK(cudaMalloc(&c->d_router_counters, ROUTER_SMALL_MAX_T * 4));
+    CU_OK(cudaMemset(c->d_router_counters, 0, ROUTER_SMALL_MAX_T * 4));
+    CU_OK(cudaMalloc(&c->d_router_logits,
+                     (size_t)ROUTER_SMALL_MAX_T * 1024 * sizeof(float)));
     long mb = env_long("APUS_CUDA_DENSE_MB", -1);
     c->budget = mb < 0 ? ~0ull : (uint64_t)mb << 20;
     c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 64);
@@ -190,6 +198,11 @@ static void stage_mark(Ctx *c, int stage, cudaStream_t st) {
     cudaEventRecord(c->ev[c->n_ev], st);
     c->ev_stage[c->n_ev] = stage;
     c->n_ev++;
+}
+
+static cudaStream_t g_mark_stream = nullptr;
+static void mark_cb(int stage) {
+    if (g_ctx) stage_mark(g_ctx, stage, g_mark_stream);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -254,6 +267,8 @@ extern "C" void apus_cuda_disable(void) {
     if (c->ws.base) cudaFree(c->ws.base);
     if (c->io.base) cudaFree(c->io.base);
     if (c->d_status) cudaFree(c->d_status);
+    if (c->d_router_counters) cudaFree(c->d_router_counters);
+    if (c->d_router_logits) cudaFree(c->d_router_logits);
     if (c->stream) cudaStreamDestroy(c->stream);
     g_ctx = nullptr;
     delete c;
@@ -380,7 +395,28 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
                          cudaStream_t st) {
     if (E < 1 || E > 1024 || topk < 1 || topk > 32 || topk > E || K < 1)
         return fail("router: unsupported E=%d topk=%d K=%d", E, topk, K);
-    /* small T: one token per CTA keeps the chain latency at its floor;
+    /* few tokens: rows spread over many small CTAs, everything in flight at
+     * once (latency path) */
+    if (T <= ROUTER_SMALL_MAX_T && (K & 7) == 0 &&
+        (((uintptr_t)dwr | (uintptr_t)extra_row) & 15) == 0) {
+        const int rows = E + (extra_row ? 1 : 0);
+        size_t smem = (size_t)ROUTER_SMALL_ROWS * (K * 2 + 16) +
+                      (size_t)K * 4 + (size_t)E * 4;
+        if (smem <= (size_t)c->smem_optin) {
+            if (smem > 48 * 1024)
+                CU_OK(cudaFuncSetAttribute(
+                    router_small_kernel,
+                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            dim3 grid((rows + ROUTER_SMALL_ROWS - 1) / ROUTER_SMALL_ROWS, T);
+            router_small_kernel<<<grid, 32, smem, st>>>(
+                dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row,
+                extra_out, c->d_router_logits, c->d_router_counters,
+                c->d_status);
+            LAUNCHED();
+            return 0;
+        }
+    }
+    /* one token per CTA keeps the chain latency low for moderate T;
      * large T: eight chains per thread amortise the weight reads */
     if (T <= 2 * c->sm_count)
         return launch_router_tt<1>(c, dx, dwr, T, E, K, topk, wmin, didx, dw,
@@ -646,7 +682,7 @@ struct BlockBufs {
     DispatchOut d;
     int32_t *unit_hist;
     uint16_t *act, *sa, *eo, *sy, *xg;
-    int32_t *tiles;        /* prefill tile list */
+    void *tiles;           /* prefill tile lists */
     size_t total;
 };
 
@@ -666,7 +702,7 @@ static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
         dispatch_scratch_bytes(A, E),  /* unit_hist */
         A * I * 2, T * Is * 2, A * H * 2, T * H * 2, /* act sa eo sy */
         prefill ? A * H * 2 : 0,       /* xg */
-        prefill ? prefill_tile_list_bytes(A, T, E) : 0,
+        prefill ? prefill_tiles_bytes_for(c, A, T) : 0,
     };
     size_t total = 0;
     for (size_t s : sz) total += al256(s) + 256;
@@ -695,7 +731,7 @@ static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
     b->eo = (uint16_t *)p[14];
     b->sy = (uint16_t *)p[15];
     b->xg = (uint16_t *)p[16];
-    b->tiles = (int32_t *)p[17];
+    b->tiles = p[17];
     return 0;
 }
 
@@ -814,13 +850,15 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (prefill) {
+        const int before = c->last_block_launches;
+        g_mark_stream = st;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
-                                L->exp_gu, L->exp_d, L->sh_g, L->sh_u, L->sh_d,
-                                d_ln2, Ti, b.d, b.xg, b.act, b.sa, b.eo, b.sy,
-                                b.tiles, c->d_status, st,
-                                &c->last_block_launches))
+                                (int)L->e_begin, d_ln2, Ti, Ti * TK, true, b.d,
+                                b.xg, b.act, b.sa, b.eo, b.sy, b.tiles,
+                                c->d_status, st, &c->last_block_launches,
+                                mark_cb))
             return fail("%s", prefill_last_error());
-        c->launches += 0;   /* counted inside */
+        c->launches += (uint64_t)(c->last_block_launches - before);
     } else {
         if (run_decode_experts(c, L, d_ln2, Ti, b, true, st)) return 1;
     }

@@ -1,13 +1,651 @@
-/* placeholder until the tcgen05 grouped GEMM lands */
+/*
+ * prefill_gemm.cuh — the expert products for large token counts: a grouped
+ * BF16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in
+ * tensor memory), fed by TMA, over the token rows dispatch has permuted into
+ * expert-contiguous order.
+ *
+ * Replaces the per-expert loop of the CPU engine's batched body
+ * (c/layer.h:599-621: gather rows -> gate_up GEMM -> apus_moe_silu_act per row
+ * -> down GEMM -> scatter rows back) and its shared-expert GEMMs
+ * (c/layer.h:593-596).
+ *
+ * Orientation ("swap A/B"): the WEIGHT rows are the MMA's M dimension (always
+ * a full 128), the expert's TOKEN rows are N (16..128, rounded up to 16), so a
+ * cold expert with a handful of rows still issues full-height MMAs and the
+ * kernel degrades gracefully into a pure weight stream:
+ *
+ *   gate_up:  Dg[128 x N] = Wg[i0:i0+128, :] . X[r0:r0+N, :]^T     K = H
+ *             Du[128 x N] = Wu[i0:i0+128, :] . X[r0:r0+N, :]^T
+ *             epilogue in registers: g = rnd(Dg), u = rnd(Du);
+ *             routed act = rnd(rnd(silu(g)) * u)   (c/moe.h:387-395)
+ *             shared sa  = rnd(silu(g) * u)        (c/moe.h:438-445)
+ *   down:     D[128 x N]  = Wd[h0:h0+128, :] . ACT[r0:r0+N, :]^T   K = I
+ *             epilogue: y = rnd(D), stored at row perm[r] of the flat
+ *             assignment-ordered buffer (the engine's eo, c/layer.h:618)
+ *
+ * One persistent CTA per SM, 6 warps: warp 0 issues TMA loads into a
+ * shared-memory ring (128B-swizzled K-major tiles, no multicast), warp 1
+ * issues the MMAs and owns the 512 TMEM columns (two accumulator stages), warps
+ * 2-5 drain accumulators (tcgen05.ld) and run the epilogue while the next
+ * tile's MMAs proceed.  Every wait is bounded; a wait that runs out raises an
+ * abort flag, records a status code, and every role falls through to the
+ * common exit where TMEM is released.
+ */
 #pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+
 #include "../../include/backend_cuda.h"
+#include "common.cuh"
+#include "decode_gemv.cuh"
 #include "dispatch.cuh"
+
 namespace apus {
-struct PrefillMaps;
-inline bool prefill_supported(const ApusCudaMoeCfg &) { return false; }
-inline PrefillMaps *prefill_maps_create(const ApusCudaMoeCfg &, const uint16_t *, const uint16_t *, const uint16_t *, const uint16_t *, const uint16_t *, size_t) { return nullptr; }
-inline void prefill_maps_free(PrefillMaps *) {}
-inline size_t prefill_tile_list_bytes(size_t, size_t, size_t) { return 0; }
-inline const char *prefill_last_error() { return "prefill path not built"; }
-inline int run_prefill_experts(int, int, PrefillMaps *, const ApusCudaMoeCfg &, const uint16_t *, const uint16_t *, const uint16_t *, const uint16_t *, const uint16_t *, const uint16_t *, int, DispatchOut, uint16_t *, uint16_t *, uint16_t *, uint16_t *, uint16_t *, int32_t *, int *, cudaStream_t, int *) { return 1; }
+
+constexpr int PG_BM = 128;        /* weight rows per tile (MMA M) */
+constexpr int PG_BN = 128;        /* token rows per tile (MMA N, max) */
+constexpr int PG_BK = 64;         /* K elements per stage = one 128B swizzle row */
+constexpr int PG_THREADS = 192;
+constexpr int PG_TILE_BYTES = PG_BM * PG_BK * 2;   /* 16 KB */
+constexpr int PG_STAGES_GU = 4;   /* 3 tiles per stage: Wg, Wu, X */
+constexpr int PG_STAGES_DN = 6;   /* 2 tiles per stage: Wd, ACT */
+constexpr int PG_TMEM_COLS = 512;
+
+static char g_prefill_err[256] = "";
+inline const char *prefill_last_error() { return g_prefill_err; }
+
+/* ---- PTX wrappers ---------------------------------------------------------- */
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map,
+                                            int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::"
+        "complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
 }
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t *holder, uint32_t cols) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+            smem_u32(holder)),
+        "r"(cols)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::
+                     : "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
+                     taddr),
+                 "r"(cols)
+                 : "memory");
+}
+/* D[tmem] (+)= A[smem] * B[smem], BF16 in, fp32 accumulate */
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc,
+                                          uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+/* arrive on an mbarrier once every MMA issued so far by this thread is done */
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 "
+        "[%0];" ::"r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+        "%30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+          "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+/* K-major, 128-byte-swizzled operand tile [rows x 64 BF16]: rows are 128 B,
+ * eight-row groups are 1024 B apart (SBO), descriptor version 1 (sm_100),
+ * layout type 2 = SWIZZLE_128B.  The tile base must be 1024-byte aligned;
+ * stepping K by 16 elements advances the start address by 32 bytes. */
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;                 /* LBO (unused for swizzled K-major) */
+    d |= (uint64_t)(1024 >> 4) << 32;       /* SBO */
+    d |= (uint64_t)1 << 46;                 /* descriptor version */
+    d |= (uint64_t)2 << 61;                 /* SWIZZLE_128B */
+    return d;
+}
+/* kind::f16 instruction descriptor: D fp32, A/B BF16, both K-major */
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(PG_BM >> 4) << 24);
+}
+
+/* wait on an mbarrier unless the CTA has aborted; a timeout aborts it */
+__device__ __forceinline__ bool pg_wait(uint64_t *bar, uint32_t parity,
+                                        volatile int *abort_flag, int *status,
+                                        int code) {
+    if (*abort_flag) return false;
+    for (uint32_t i = 0; i < APUS_WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 256) {
+            __nanosleep(32);
+            if (*abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    set_status(status, code);
+    return false;
+}
+
+/* ---- tile list --------------------------------------------------------------
+ * One entry per (expert, weight-row tile, token-row tile): {v, m, row0, nrows}.
+ * v == E is the shared expert (rows are token indices); otherwise row0 is a
+ * position in dispatch order.  Tiles that share weights are adjacent, so when
+ * an expert has several token tiles its weights come from HBM once and from
+ * L2 afterwards. */
+struct TileLists {
+    int4 *gu;        /* gate_up tiles */
+    int4 *dn;        /* down tiles */
+    int *n_gu, *n_dn;
+};
+
+inline size_t prefill_max_ntiles(size_t A, size_t T, size_t E) {
+    return A / PG_BN + E + (T + PG_BN - 1) / PG_BN + 1;
+}
+inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
+                                      size_t T) {
+    size_t nt = prefill_max_ntiles(A, T, c.experts);
+    size_t m1 = (c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter) / PG_BM;
+    size_t m2 = c.hidden / PG_BM;
+    return (nt * m1 + nt * m2) * sizeof(int4) + 256;
+}
+
+__global__ void __launch_bounds__(1024)
+build_tiles_kernel(const int32_t *__restrict__ counts,
+                   const int32_t *__restrict__ offsets, int E, int T, int m_gu,
+                   int m_gu_sh, int m_dn, TileLists tl) {
+    __shared__ int warp_tot[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cnt = tid < E ? counts[tid] : 0;
+    const int nt = (cnt + PG_BN - 1) / PG_BN;
+    int inc = nt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += v;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int base = 0, total = 0;
+    for (int w = 0; w < 32; w++) {
+        if (w < warp) base += warp_tot[w];
+        total += warp_tot[w];
+    }
+    const int first = base + inc - nt;   /* token tiles before this expert */
+    if (tid < E && nt > 0) {
+        const int off = offsets[tid];
+        for (int m = 0; m < m_gu; m++)
+            for (int n = 0; n < nt; n++)
+                tl.gu[(size_t)first * m_gu + (size_t)m * nt + n] =
+                    make_int4(tid, m, off + n * PG_BN, min(PG_BN, cnt - n * PG_BN));
+        for (int m = 0; m < m_dn; m++)
+            for (int n = 0; n < nt; n++)
+                tl.dn[(size_t)first * m_dn + (size_t)m * nt + n] =
+                    make_int4(tid, m, off + n * PG_BN, min(PG_BN, cnt - n * PG_BN));
+    }
+    /* shared expert: dense over all T tokens */
+    const int nts = (T + PG_BN - 1) / PG_BN;
+    for (int i = tid; i < nts * m_gu_sh; i += blockDim.x) {
+        int m = i / nts, n = i - m * nts;
+        tl.gu[(size_t)total * m_gu + i] =
+            make_int4(E, m, n * PG_BN, min(PG_BN, T - n * PG_BN));
+    }
+    for (int i = tid; i < nts * m_dn; i += blockDim.x) {
+        int m = i / nts, n = i - m * nts;
+        tl.dn[(size_t)total * m_dn + i] =
+            make_int4(E, m, n * PG_BN, min(PG_BN, T - n * PG_BN));
+    }
+    if (tid == 0) {
+        *tl.n_gu = total * m_gu + nts * m_gu_sh;
+        *tl.n_dn = total * m_dn + nts * m_dn;
+    }
+}
+
+/* xg[p, :] = x[perm[p] / TK, :] — the rows of c/layer.h:603-605's memcpy */
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint16_t *__restrict__ x,
+                   const int32_t *__restrict__ perm, int A, int H, int TK,
+                   uint16_t *__restrict__ xg) {
+    const int c8 = H / 8;
+    const long total = (long)A * c8;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        const int p = (int)(i / c8), c = (int)(i - (long)p * c8);
+        const int tok = perm[p] / TK;
+        reinterpret_cast<uint4 *>(xg)[i] =
+            ldg16(x + (size_t)tok * H + (size_t)c * 8);
+    }
+}
+
+/* ---- the grouped GEMM -------------------------------------------------------- */
+struct GemmParams {
+    const int4 *tiles;
+    const int *n_tiles;
+    int K;                 /* reduction length */
+    int E;                 /* v == E: shared expert */
+    int e_begin;           /* first resident expert */
+    int rows_per_expert;   /* rows of the routed A tensor per expert */
+    int up_off;            /* gate_up: row offset of the up half (I) */
+    uint16_t *out_routed;  /* act [A, ld_routed]  or  eo [A, ld_routed] */
+    uint16_t *out_shared;  /* sa [T, ld_shared]   or  sy [T, ld_shared] */
+    int ld_routed, ld_shared;
+    const int32_t *perm;   /* down: sorted position -> flat assignment */
+    int *status;
+};
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(PG_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
+                    const __grid_constant__ CUtensorMap mapAs,    /* shared g | d */
+                    const __grid_constant__ CUtensorMap mapAs2,   /* shared u */
+                    const __grid_constant__ CUtensorMap mapB,     /* xg | act */
+                    const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
+                    GemmParams p) {
+    constexpr int STAGES = GATE_UP ? PG_STAGES_GU : PG_STAGES_DN;
+    constexpr int TILES_PER_STAGE = GATE_UP ? 3 : 2;
+    constexpr int STAGE_BYTES = TILES_PER_STAGE * PG_TILE_BYTES;
+
+    extern __shared__ unsigned char pg_smem_raw[];
+    /* 1024-byte alignment for the swizzled tiles */
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES;
+    uint64_t *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 128);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, PG_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    const int n_tiles = *p.n_tiles;
+    const int num_kb = p.K / PG_BK;
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (lane == 0) {
+            uint32_t kiter = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
+                const int4 t = __ldg(&p.tiles[tile]);
+                const bool shared = t.x == p.E;
+                const CUtensorMap *ma = shared ? &mapAs : &mapA;
+                const CUtensorMap *ma2 = shared ? &mapAs2 : &mapA;
+                const CUtensorMap *mb = shared ? &mapBs : &mapB;
+                const int arow =
+                    (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) + t.y * PG_BM;
+                const int arow2 = shared ? arow : arow + p.up_off;
+                for (int kb = 0; kb < num_kb; kb++, kiter++) {
+                    const int s = kiter % STAGES;
+                    const uint32_t ph = (kiter / STAGES) & 1u;
+                    if (!pg_wait(&empty[s], ph ^ 1u, abort_flag, p.status,
+                                 ST_MBAR_TIMEOUT)) {
+                        alive = false;
+                        break;
+                    }
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(st, ma, kb * PG_BK, arow, &full[s]);
+                    if (GATE_UP)
+                        tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
+                                    &full[s]);
+                    tma_load_2d(st + (TILES_PER_STAGE - 1) * PG_TILE_BYTES, mb,
+                                kb * PG_BK, t.z, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer ---------------- */
+        if (lane == 0) {
+            uint32_t kiter = 0;
+            bool alive = true;
+            int it = 0;
+            for (int tile = blockIdx.x; alive && tile < n_tiles;
+                 tile += gridDim.x, it++) {
+                const int4 t = __ldg(&p.tiles[tile]);
+                const int acc = it & 1;
+                const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+                const int n = ((t.w + 15) >> 4) << 4;
+                const uint32_t idesc = umma_idesc(n);
+                if (!pg_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status,
+                             ST_TMEM_TIMEOUT)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + (uint32_t)acc * 256u;
+                for (int kb = 0; kb < num_kb; kb++, kiter++) {
+                    const int s = kiter % STAGES;
+                    const uint32_t ph = (kiter / STAGES) & 1u;
+                    if (!pg_wait(&full[s], ph, abort_flag, p.status,
+                                 ST_MBAR_TIMEOUT)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t da = umma_smem_desc(sa);
+                    const uint64_t db = umma_smem_desc(
+                        sa + (TILES_PER_STAGE - 1) * PG_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < PG_BK / 16; k++) {
+                        const uint32_t accum = (kb | k) ? 1u : 0u;
+                        /* +32 bytes per 16-element K step (encoded >> 4) */
+                        umma_bf16(d0, da + 2u * k, db + 2u * k, idesc, accum);
+                        if (GATE_UP) {
+                            const uint64_t da2 = umma_smem_desc(sa + PG_TILE_BYTES);
+                            umma_bf16(d0 + 128u, da2 + 2u * k, db + 2u * k, idesc,
+                                      accum);
+                        }
+                    }
+                    umma_commit(&empty[s]);    /* frees the stage when done */
+                }
+                if (alive) umma_commit(&tfull[acc]);
+            }
+        }
+    } else {
+        /* ---------------- epilogue (warps 2..5) ---------------- */
+        const int q = warp & 3;                 /* TMEM lane quarter */
+        const int row = q * 32 + lane;          /* row inside the tile */
+        bool alive = true;
+        int it = 0;
+        for (int tile = blockIdx.x; alive && tile < n_tiles;
+             tile += gridDim.x, it++) {
+            const int4 t = __ldg(&p.tiles[tile]);
+            const bool shared = t.x == p.E;
+            const int acc = it & 1;
+            const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+            if (!pg_wait(&tfull[acc], aph, abort_flag, p.status,
+                         ST_TMEM_TIMEOUT)) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t taddr =
+                tmem_base + (uint32_t)acc * 256u + ((uint32_t)(q * 32) << 16);
+            uint16_t *out = shared ? p.out_shared : p.out_routed;
+            const int ld = shared ? p.ld_shared : p.ld_routed;
+            const int col = t.y * PG_BM + row;
+            for (int c0 = 0; c0 < t.w; c0 += 32) {
+                uint32_t g[32];
+                tmem_ld32(taddr + (uint32_t)c0, g);
+                if (GATE_UP) {
+                    uint32_t u[32];
+                    tmem_ld32(taddr + 128u + (uint32_t)c0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int n = c0 + j;
+                        if (n < t.w) {
+                            const float gv = bf16_round(__uint_as_float(g[j]));
+                            const float uv = bf16_round(__uint_as_float(u[j]));
+                            out[(size_t)(t.z + n) * ld + col] =
+                                shared ? silu_mul_bits(gv, uv)
+                                       : silu_act_bits(gv, uv);
+                        }
+                    }
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int n = c0 + j;
+                        if (n < t.w) {
+                            const int orow =
+                                shared ? t.z + n : __ldg(&p.perm[t.z + n]);
+                            out[(size_t)orow * ld + col] =
+                                bf16_bits(__uint_as_float(g[j]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&tempty[acc]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, PG_TMEM_COLS);
+    }
+}
+
+/* ---- host side ---------------------------------------------------------------- */
+typedef CUresult (*PFN_encodeTiled_local)(
+    CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+    CUtensorMapFloatOOBfill);
+
+struct PrefillMaps {
+    PFN_encodeTiled_local encode = nullptr;
+    CUtensorMap w_gu, sh_g, sh_u, w_d, sh_d;
+};
+
+inline bool prefill_supported(const ApusCudaMoeCfg &c) {
+    return c.hidden % PG_BM == 0 && c.moe_inter % PG_BM == 0 &&
+           c.shared_inter % PG_BM == 0 && c.hidden % PG_BK == 0 &&
+           c.moe_inter % PG_BK == 0 && c.shared_inter % PG_BK == 0 &&
+           c.shared_inter == c.moe_inter && c.experts <= 1024;
+}
+
+/* rows x cols BF16, row-major; box = 128 rows x 64 columns, 128B swizzle */
+inline int encode_2d(PFN_encodeTiled_local enc, CUtensorMap *m, const void *base,
+                     size_t rows, size_t cols) {
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)PG_BK, (cuuint32_t)PG_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base),
+                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "cuTensorMapEncodeTiled failed (%d) rows=%zu cols=%zu", (int)r,
+                 rows, cols);
+        return 1;
+    }
+    return 0;
+}
+
+inline PrefillMaps *prefill_maps_create(const ApusCudaMoeCfg &c,
+                                        const uint16_t *exp_gu,
+                                        const uint16_t *exp_d,
+                                        const uint16_t *sh_g,
+                                        const uint16_t *sh_u,
+                                        const uint16_t *sh_d, size_t n_experts) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault,
+                                &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "cuTensorMapEncodeTiled is not available from the driver");
+        return nullptr;
+    }
+    PrefillMaps *m = new PrefillMaps();
+    m->encode = (PFN_encodeTiled_local)fn;
+    const size_t H = c.hidden, I = c.moe_inter, Is = c.shared_inter;
+    int bad = 0;
+    if (n_experts) {
+        bad |= encode_2d(m->encode, &m->w_gu, exp_gu, n_experts * 2 * I, H);
+        bad |= encode_2d(m->encode, &m->w_d, exp_d, n_experts * H, I);
+    } else {
+        /* no routed experts resident: alias the shared maps (never read) */
+        bad |= encode_2d(m->encode, &m->w_gu, sh_g, Is, H);
+        bad |= encode_2d(m->encode, &m->w_d, sh_d, H, Is);
+    }
+    bad |= encode_2d(m->encode, &m->sh_g, sh_g, Is, H);
+    bad |= encode_2d(m->encode, &m->sh_u, sh_u, Is, H);
+    bad |= encode_2d(m->encode, &m->sh_d, sh_d, H, Is);
+    if (bad) {
+        delete m;
+        return nullptr;
+    }
+    return m;
+}
+inline void prefill_maps_free(PrefillMaps *m) { delete m; }
+
+inline int pg_smem_bytes(bool gate_up) {
+    int stages = gate_up ? PG_STAGES_GU : PG_STAGES_DN;
+    int per = (gate_up ? 3 : 2) * PG_TILE_BYTES;
+    return stages * per + 1024 /* alignment slack */ + 256 /* barriers */;
+}
+
+/* Routed + shared experts through the tensor-core path.  x [T,H] is the block
+ * input; d holds the dispatch results; xg/act/sa/eo/sy are workspace. */
+inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
+                               const ApusCudaMoeCfg &c, int e_begin,
+                               const uint16_t *x, int T, int A, bool do_shared,
+                               const DispatchOut &d, uint16_t *xg, uint16_t *act,
+                               uint16_t *sa, uint16_t *eo, uint16_t *sy,
+                               void *tiles_ws, int *status, cudaStream_t st,
+                               int *launches, void (*mark)(int stage)) {
+    const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
+              E = (int)c.experts, TK = A / (T > 0 ? T : 1);
+    (void)TK;
+    if (!maps) {
+        snprintf(g_prefill_err, sizeof g_prefill_err, "tensor maps missing");
+        return 1;
+    }
+    const int s1 = pg_smem_bytes(true), s2 = pg_smem_bytes(false);
+    if (s1 > smem_optin || s2 > smem_optin) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "grouped GEMM needs %d B shared memory", s1);
+        return 1;
+    }
+    /* tile lists */
+    const size_t nt = prefill_max_ntiles((size_t)A, (size_t)T, (size_t)E);
+    const int m_gu = I / PG_BM, m_gu_sh = Is / PG_BM, m_dn = H / PG_BM;
+    const size_t m1 = (size_t)(m_gu > m_gu_sh ? m_gu : m_gu_sh);
+    TileLists tl;
+    tl.gu = reinterpret_cast<int4 *>(tiles_ws);
+    tl.dn = tl.gu + nt * m1;
+    tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * m_dn);
+    tl.n_dn = tl.n_gu + 1;
+    build_tiles_kernel<<<1, 1024, 0, st>>>(d.counts, d.offsets, E,
+                                           do_shared ? T : 0, m_gu, m_gu_sh, m_dn,
+                                           tl);
+    (*launches)++;
+    /* permuted activation rows */
+    if (A > 0) {
+        long total = (long)A * (H / 8);
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > sm_count * 16) blocks = sm_count * 16;
+        gather_rows_kernel<<<blocks, 256, 0, st>>>(x, d.perm, A, H,
+                                                   A / (T > 0 ? T : 1), xg);
+        (*launches)++;
+    }
+    if (mark) mark(APUS_CUDA_STAGE_GATHER);
+    /* activation-side tensor maps (buffers move with the workspace) */
+    CUtensorMap m_xg, m_x, m_act, m_sa;
+    int bad = 0;
+    bad |= encode_2d(maps->encode, &m_xg, xg, (size_t)(A > 0 ? A : 1), H);
+    bad |= encode_2d(maps->encode, &m_x, x, (size_t)T, H);
+    bad |= encode_2d(maps->encode, &m_act, act, (size_t)(A > 0 ? A : 1), I);
+    bad |= encode_2d(maps->encode, &m_sa, sa, (size_t)T, Is);
+    if (bad) return 1;
+
+    cudaFuncSetAttribute(grouped_gemm_kernel<true>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
+    cudaFuncSetAttribute(grouped_gemm_kernel<false>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, s2);
+    GemmParams p1;
+    memset(&p1, 0, sizeof p1);
+    p1.tiles = tl.gu;
+    p1.n_tiles = tl.n_gu;
+    p1.K = H;
+    p1.E = E;
+    p1.e_begin = e_begin;
+    p1.rows_per_expert = 2 * I;
+    p1.up_off = I;
+    p1.out_routed = act;
+    p1.out_shared = sa;
+    p1.ld_routed = I;
+    p1.ld_shared = Is;
+    p1.status = status;
+    grouped_gemm_kernel<true><<<sm_count, PG_THREADS, s1, st>>>(
+        maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
+    (*launches)++;
+    if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
+    GemmParams p2 = p1;
+    p2.tiles = tl.dn;
+    p2.n_tiles = tl.n_dn;
+    p2.K = I;   /* == Is is required below */
+    p2.rows_per_expert = H;
+    p2.up_off = 0;
+    p2.out_routed = eo;
+    p2.out_shared = sy;
+    p2.ld_routed = H;
+    p2.ld_shared = H;
+    p2.perm = d.perm;
+    if (Is != I) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "tensor-core path needs shared_inter == moe_inter");
+        return 1;
+    }
+    grouped_gemm_kernel<false><<<sm_count, PG_THREADS, s2, st>>>(
+        maps->w_d, maps->sh_d, maps->sh_d, m_act, m_sa, p2);
+    (*launches)++;
+    if (mark) mark(APUS_CUDA_STAGE_DOWN);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(g_prefill_err, sizeof g_prefill_err, "grouped GEMM launch: %s",
+                 cudaGetErrorString(e));
+        return 1;
+    }
+    return 0;
+}
+
+}  // namespace apus

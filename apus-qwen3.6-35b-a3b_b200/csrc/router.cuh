@@ -81,6 +81,61 @@ __device__ __forceinline__ void router_chains(const uint16_t *__restrict__ wrow,
     }
 }
 
+/* One warp turns a token's E BF16-valued logits (fp32 in shared memory,
+ * overwritten) into the selection and the renormalised weights, exactly in
+ * the order of c/moe.h:321-371. */
+__device__ __forceinline__ void router_softmax_topk(float *p, int E, int topk,
+                                                    int lane,
+                                                    int32_t *__restrict__ idx_out,
+                                                    uint16_t *__restrict__ w_out) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, p[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int e = lane; e < E; e += 32)
+        p[e] = (float)exp((double)__fsub_rn(p[e], m));
+    __syncwarp();
+    float s = 0.0f;
+    if (lane == 0)
+        for (int e = 0; e < E; e++) s = __fadd_rn(s, p[e]);
+    s = __shfl_sync(0xffffffffu, s, 0);
+    for (int e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], s);
+    __syncwarp();
+
+    int my_e = 0;
+    float my_p = 0.0f;
+    for (int i = 0; i < topk; i++) {
+        float bv = -INFINITY;
+        int be = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            float v = p[e];
+            if (v > bv) { bv = v; be = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if (be == 0x7fffffff) {   /* nothing left above -inf: the CPU loop
+                                   * leaves best = 0 */
+            be = 0;
+            bv = p[0];
+        }
+        if (lane == i) { my_e = be; my_p = bv; }
+        if (lane == (be & 31)) p[be] = -INFINITY;
+        __syncwarp();
+    }
+    if (w_out) {
+        float sw = 0.0f;
+        for (int i = 0; i < topk; i++)
+            sw = __fadd_rn(sw, __shfl_sync(0xffffffffu, my_p, i));
+        if (lane < topk) w_out[lane] = bf16_bits(__fdiv_rn(my_p, sw));
+    }
+    if (lane < topk) idx_out[lane] = my_e;
+}
+
 /*
  * grid = ceil(T / TT); block = 256.  Dynamic shared memory:
  *   xs   float [TT][K]
@@ -164,56 +219,122 @@ router_topk_kernel(const uint16_t *__restrict__ x,
     const int warp = tid >> 5, lane = tid & 31;
     for (int t = warp; t < TT; t += ROUTER_THREADS / 32) {
         if (t0 + t >= T) break;
-        float *p = ps + (size_t)t * E;
-        float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) m = fmaxf(m, p[e]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        for (int e = lane; e < E; e += 32)
-            p[e] = (float)exp((double)__fsub_rn(p[e], m));
-        __syncwarp();
-        float s = 0.0f;
-        if (lane == 0)
-            for (int e = 0; e < E; e++) s = __fadd_rn(s, p[e]);
-        s = __shfl_sync(0xffffffffu, s, 0);
-        for (int e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], s);
-        __syncwarp();
-
-        int my_e = 0;
-        float my_p = 0.0f;
-        for (int i = 0; i < topk; i++) {
-            float bv = -INFINITY;
-            int be = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                float v = p[e];
-                if (v > bv) { bv = v; be = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-            }
-            if (be == 0x7fffffff) {   /* nothing left above -inf: the CPU
-                                       * loop leaves best = 0 */
-                be = 0;
-                bv = p[0];
-            }
-            if (lane == i) { my_e = be; my_p = bv; }
-            if (lane == (be & 31)) p[be] = -INFINITY;
-            __syncwarp();
-        }
-        if (w_out) {
-            float sw = 0.0f;
-            for (int i = 0; i < topk; i++)
-                sw = __fadd_rn(sw, __shfl_sync(0xffffffffu, my_p, i));
-            if (lane < topk)
-                w_out[(size_t)(t0 + t) * topk + lane] =
-                    bf16_bits(__fdiv_rn(my_p, sw));
-        }
-        if (lane < topk) idx_out[(size_t)(t0 + t) * topk + lane] = my_e;
+        router_softmax_topk(ps + (size_t)t * E, E, topk, lane,
+                            idx_out + (size_t)(t0 + t) * topk,
+                            w_out ? w_out + (size_t)(t0 + t) * topk : nullptr);
     }
+}
+
+/*
+ * Latency path for few tokens.  grid = (ceil(rows / 8), T), block = 32: a CTA
+ * pulls eight router rows into shared memory with one bulk copy each (all in
+ * flight at once, so the 1 MiB router matrix arrives spread over 32 SMs instead
+ * of trickling through one), lanes 0..7 walk one exact chain each, and the
+ * BF16 logits go to global memory.  The CTA that arrives last for its token
+ * (one atomic counter per token, which it resets for the next call) runs the
+ * softmax / top-k warp.  No CTA ever waits on another.
+ * Requires K % 8 == 0 and a 16-byte-aligned router matrix.
+ * Dynamic shared memory: 8 * (K*2 + 16) + K*4 + E*4 bytes.
+ */
+constexpr int ROUTER_SMALL_ROWS = 8;
+
+__global__ void __launch_bounds__(32)
+router_small_kernel(const uint16_t *__restrict__ x,
+                    const uint16_t *__restrict__ wr, int T, int E, int K,
+                    int topk, float wmin, int32_t *__restrict__ idx_out,
+                    uint16_t *__restrict__ w_out,
+                    uint16_t *__restrict__ logits_out,
+                    const uint16_t *__restrict__ extra_row,
+                    uint16_t *__restrict__ extra_out,
+                    float *__restrict__ logits_ws,     /* [T][E] fp32 */
+                    unsigned int *__restrict__ counters, /* [T], zero between calls */
+                    int *status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int pitch = K * 2 + 16;                 /* bytes; de-conflicts banks */
+    unsigned char *rows_s = smem_raw;
+    float *xs = reinterpret_cast<float *>(smem_raw + ROUTER_SMALL_ROWS * pitch);
+    float *ps = xs + K;
+    __shared__ __align__(8) uint64_t bar;
+
+    const int lane = threadIdx.x;
+    const int t = blockIdx.y;
+    const int rows_total = E + (extra_row ? 1 : 0);
+    const int r0 = blockIdx.x * ROUTER_SMALL_ROWS;
+    const int nrows = min(ROUTER_SMALL_ROWS, rows_total - r0);
+
+    if (lane == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    if (lane == 0) {
+        mbar_expect_tx(&bar, (uint32_t)nrows * (uint32_t)K * 2u);
+        for (int r = 0; r < nrows; r++) {
+            const uint16_t *src = (r0 + r == E) ? extra_row
+                                                : wr + (size_t)(r0 + r) * K;
+            bulk_g2s(rows_s + (size_t)r * pitch, src, (uint32_t)K * 2u, &bar);
+        }
+    }
+    unsigned int xmin = 0x7f800000u;
+    for (int k = lane; k < K; k += 32) {
+        uint16_t c = x[(size_t)t * K + k];
+        xs[k] = bf16_f32(c);
+        unsigned int a = ((unsigned int)c << 16) & 0x7fffffffu;
+        if (a != 0 && a < xmin) xmin = a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        xmin = min(xmin, __shfl_xor_sync(0xffffffffu, xmin, o));
+    __syncwarp();
+    const bool use_fma =
+        (wmin > 0.0f) &&
+        ((double)wmin * (double)__uint_as_float(xmin) >= 7.52316384526264e-37);
+    const bool arrived = mbar_wait(&bar, 0);
+    if (!arrived) set_status(status, ST_MBAR_TIMEOUT);
+    if (arrived && lane < nrows) {
+        const uint16_t *wrow =
+            reinterpret_cast<const uint16_t *>(rows_s + (size_t)lane * pitch);
+        float acc = 0.0f;
+        const bool fma_row = use_fma && (r0 + lane != E);
+        for (int k = 0; k < K; k += 8) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + k);
+            const float4 xa = *reinterpret_cast<const float4 *>(xs + k);
+            const float4 xb = *reinterpret_cast<const float4 *>(xs + k + 4);
+            const float wf[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y),
+                                 bf16hi(wv.y), bf16lo(wv.z), bf16hi(wv.z),
+                                 bf16lo(wv.w), bf16hi(wv.w)};
+            const float xf[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            if (fma_row) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc = __fmaf_rn(wf[j], xf[j], acc);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    acc = __fadd_rn(acc, __fmul_rn(wf[j], xf[j]));
+            }
+        }
+        const uint16_t code = bf16_bits(acc);
+        if (r0 + lane == E) {
+            extra_out[t] = code;
+        } else {
+            logits_ws[(size_t)t * E + r0 + lane] = bf16_f32(code);
+            if (logits_out) logits_out[(size_t)t * E + r0 + lane] = code;
+        }
+    }
+    /* last CTA of this token finishes the job */
+    __threadfence();
+    __syncwarp();
+    unsigned int old = 0;
+    if (lane == 0) old = atomicAdd(&counters[t], 1u);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != gridDim.x - 1) return;
+    __threadfence();
+    for (int e = lane; e < E; e += 32)
+        ps[e] = __ldcg(&logits_ws[(size_t)t * E + e]);
+    __syncwarp();
+    if (lane == 0) counters[t] = 0;
+    router_softmax_topk(ps, E, topk, lane, idx_out + (size_t)t * topk,
+                        w_out ? w_out + (size_t)t * topk : nullptr);
 }
 
 /* smallest nonzero |w| over n BF16 codes, as fp32 bits (min-reduced into

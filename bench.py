@@ -210,7 +210,8 @@ def main():
     x_host = synth.host_x(be, T, H, seed=args.seed)
     layer = be.layer_create(cfg, W)
     be.reserve(cfg, T)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()       # every launch and event goes here
+    torch.cuda.set_stream(stream)
     d_x = torch.from_numpy(x_host.view(np.int16)).cuda()
     d_out = torch.empty_like(d_x)
     d_idx = torch.empty((T, cfg["top_k"]), dtype=torch.int32, device="cuda")

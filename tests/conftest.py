@@ -60,11 +60,15 @@ def ref():
     return oracle.Reference()
 
 
-@pytest.fixture(scope="session")
+@pytest.fixture
 def gpu(be):
-    """Enable the backend on the device; fails loudly without one."""
+    """Enable the backend on the device (fails loudly without one).  Each
+    test gets a fresh residency table: the backend keys resident weights by
+    host address (the engine's stable-pointer rule), and numpy reuses the
+    addresses of arrays an earlier test freed."""
     be.enable()
     yield be
+    be.disable()
 
 
 def rel_l2(a, b):

@@ -49,8 +49,11 @@ def test_block_mini(gpu, orc, be, synth, T):
 @pytest.mark.parametrize("cfg", [
     dict(hidden=512, experts=64, moe_inter=128, shared_inter=64, top_k=8),
     dict(hidden=256, experts=8, moe_inter=64, shared_inter=128, top_k=2),
+    # shapes the tensor-core path accepts (T > 64 takes it)
+    dict(hidden=512, experts=64, moe_inter=128, shared_inter=128, top_k=8),
+    dict(hidden=256, experts=8, moe_inter=256, shared_inter=256, top_k=3),
 ])
-@pytest.mark.parametrize("T", [1, 40, 200])
+@pytest.mark.parametrize("T", [1, 40, 65, 200, 777])
 def test_block_medium(gpu, orc, be, synth, cfg, T):
     W = synth.host_weights(be, cfg, seed=77, sigma=0.05)
     x = synth.host_x(be, T, cfg["hidden"], seed=77 + T)
