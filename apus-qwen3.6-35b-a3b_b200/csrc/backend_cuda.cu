@@ -416,6 +416,37 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
             return 0;
         }
     }
+    /* many tokens: TMA-staged router tiles, then one warp per token */
+    if (T > ROUTER_SMALL_MAX_T && dlogits && E % RL_ROWS == 0 &&
+        K % RL_BK == 0 && (((uintptr_t)dwr) & 15) == 0) {
+        PFN_encodeTiled_local enc = tensor_map_encoder();
+        if (!enc) return fail("%s", prefill_last_error());
+        CUtensorMap map_w;
+        if (encode_2d(enc, &map_w, dwr, (size_t)E, (size_t)K))
+            return fail("%s", prefill_last_error());
+        const int tt = T >= 16 * c->sm_count ? 8 : (T >= 4 * c->sm_count ? 4 : 2);
+        const size_t xb = ((size_t)tt * RL_BK * 4 + 1023) & ~(size_t)1023;
+        const size_t smem = RL_STAGES * ((size_t)RL_ROWS * RL_BK * 2 + xb) + 1024 + 64;
+        dim3 grid((T + tt - 1) / tt, E / RL_ROWS);
+#define RL_LAUNCH(TTV)                                                          \
+        do {                                                                    \
+            CU_OK(cudaFuncSetAttribute(                                         \
+                router_logits_kernel<TTV>,                                      \
+                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+            router_logits_kernel<TTV><<<grid, ROUTER_THREADS, smem, st>>>(      \
+                map_w, dx, T, E, K, wmin, dlogits, extra_row, extra_out,        \
+                c->d_status);                                                   \
+        } while (0)
+        if (tt == 8) RL_LAUNCH(8);
+        else if (tt == 4) RL_LAUNCH(4);
+        else RL_LAUNCH(2);
+#undef RL_LAUNCH
+        LAUNCHED();
+        router_select_kernel<<<(T + 7) / 8, 256, (size_t)8 * E * sizeof(float), st>>>(
+            dlogits, T, E, topk, didx, dw);
+        LAUNCHED();
+        return 0;
+    }
     /* one token per CTA keeps the chain latency low for moderate T;
      * large T: eight chains per thread amortise the weight reads */
     if (T <= 2 * c->sm_count)
@@ -438,7 +469,7 @@ static int launch_dispatch(Ctx *c, const int32_t *didx, int A, int E,
                            DispatchOut o, int32_t *unit_hist,
                            cudaStream_t st) {
     if (E < 1 || E > 1024) return fail("dispatch: unsupported E=%d", E);
-    if (A <= 4096) {
+    if (A <= 1024) {
         dispatch_small_kernel<<<1, 256, 2 * E * sizeof(int), st>>>(
             didx, A, E, o, c->d_status);
         LAUNCHED();
@@ -493,7 +524,7 @@ static int route_host(const uint16_t *x, const uint16_t *wg, int32_t *idx,
     uint16_t *dwr = (uint16_t *)c->io.take(E * K * 2);
     int32_t *didx = (int32_t *)c->io.take(T * topk * 4);
     uint16_t *dw = (uint16_t *)c->io.take(T * topk * 2);
-    uint16_t *dl = logits ? (uint16_t *)c->io.take(T * E * 2) : nullptr;
+    uint16_t *dl = (uint16_t *)c->io.take(T * E * 2);
     CU_OK(cudaMemcpyAsync(dx, x, T * K * 2, cudaMemcpyHostToDevice, c->stream));
     CU_OK(cudaMemcpyAsync(dwr, wg, E * K * 2, cudaMemcpyHostToDevice, c->stream));
     float wmin = 0.0f;
@@ -678,7 +709,7 @@ extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
 
 struct BlockBufs {
     int32_t *idx;
-    uint16_t *rw, *sgl;
+    uint16_t *rw, *sgl, *logits;
     DispatchOut d;
     int32_t *unit_hist;
     uint16_t *act, *sa, *eo, *sy, *xg;
@@ -697,6 +728,7 @@ static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
         A * 4,                         /* idx */
         A * 2,                         /* rw */
         T * 2,                         /* sgl */
+        T * E * 2,                     /* router logits */
         E * 4, (E + 1) * 4, A * 4, A * 4,            /* counts offsets perm pos */
         (A + E) * 4, (A + E) * 4, (A + E) * 4, 256,  /* groups, n_groups */
         dispatch_scratch_bytes(A, E),  /* unit_hist */
@@ -717,21 +749,22 @@ static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
     b->idx = (int32_t *)p[0];
     b->rw = (uint16_t *)p[1];
     b->sgl = (uint16_t *)p[2];
-    b->d.counts = (int32_t *)p[3];
-    b->d.offsets = (int32_t *)p[4];
-    b->d.perm = (int32_t *)p[5];
-    b->d.pos = (int32_t *)p[6];
-    b->d.grp_expert = (int32_t *)p[7];
-    b->d.grp_first = (int32_t *)p[8];
-    b->d.grp_n = (int32_t *)p[9];
-    b->d.n_groups = (int32_t *)p[10];
-    b->unit_hist = (int32_t *)p[11];
-    b->act = (uint16_t *)p[12];
-    b->sa = (uint16_t *)p[13];
-    b->eo = (uint16_t *)p[14];
-    b->sy = (uint16_t *)p[15];
-    b->xg = (uint16_t *)p[16];
-    b->tiles = p[17];
+    b->logits = (uint16_t *)p[3];
+    b->d.counts = (int32_t *)p[4];
+    b->d.offsets = (int32_t *)p[5];
+    b->d.perm = (int32_t *)p[6];
+    b->d.pos = (int32_t *)p[7];
+    b->d.grp_expert = (int32_t *)p[8];
+    b->d.grp_first = (int32_t *)p[9];
+    b->d.grp_n = (int32_t *)p[10];
+    b->d.n_groups = (int32_t *)p[11];
+    b->unit_hist = (int32_t *)p[12];
+    b->act = (uint16_t *)p[13];
+    b->sa = (uint16_t *)p[14];
+    b->eo = (uint16_t *)p[15];
+    b->sy = (uint16_t *)p[16];
+    b->xg = (uint16_t *)p[17];
+    b->tiles = p[18];
     return 0;
 }
 
@@ -844,7 +877,7 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     c->n_ev = 0;
     stage_mark(c, -1, st);
     if (launch_router(c, d_ln2, L->rtr_w, Ti, E, H, TK, L->wmin, b.idx, b.rw,
-                      nullptr, L->sh_gate, b.sgl, st))
+                      b.logits, L->sh_gate, b.sgl, st))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_ROUTER, st);
     if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
@@ -1096,3 +1129,4 @@ extern "C" int apus_synth_fill_dev(uint16_t *d_dst, size_t n, uint64_t seed,
     LAUNCHED();
     return 0;
 }
+

@@ -473,6 +473,24 @@ struct PrefillMaps {
     CUtensorMap w_gu, sh_g, sh_u, w_d, sh_d;
 };
 
+/* cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (the
+ * library does not link libcuda, so it loads on machines without a driver) */
+inline PFN_encodeTiled_local tensor_map_encoder() {
+    static PFN_encodeTiled_local cached = nullptr;
+    if (cached) return cached;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault,
+                                &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "cuTensorMapEncodeTiled is not available from the driver");
+        return nullptr;
+    }
+    cached = (PFN_encodeTiled_local)fn;
+    return cached;
+}
+
 inline bool prefill_supported(const ApusCudaMoeCfg &c) {
     return c.hidden % PG_BM == 0 && c.moe_inter % PG_BM == 0 &&
            c.shared_inter % PG_BM == 0 && c.hidden % PG_BK == 0 &&
@@ -506,17 +524,10 @@ inline PrefillMaps *prefill_maps_create(const ApusCudaMoeCfg &c,
                                         const uint16_t *sh_g,
                                         const uint16_t *sh_u,
                                         const uint16_t *sh_d, size_t n_experts) {
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault,
-                                &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess || !fn) {
-        snprintf(g_prefill_err, sizeof g_prefill_err,
-                 "cuTensorMapEncodeTiled is not available from the driver");
-        return nullptr;
-    }
+    PFN_encodeTiled_local fn = tensor_map_encoder();
+    if (!fn) return nullptr;
     PrefillMaps *m = new PrefillMaps();
-    m->encode = (PFN_encodeTiled_local)fn;
+    m->encode = fn;
     const size_t H = c.hidden, I = c.moe_inter, Is = c.shared_inter;
     int bad = 0;
     if (n_experts) {

@@ -27,9 +27,20 @@
  * on p with strict '>' from -inf; renormalisation sum in selection order.
  */
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace apus {
+
+__device__ __forceinline__ void tma_load_2d_rl(void *dst, const CUtensorMap *map,
+                                               int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::"
+        "complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
 
 constexpr int ROUTER_THREADS = 288;   /* 256 expert chains + a warp for the extra row */
 
@@ -334,6 +345,201 @@ router_small_kernel(const uint16_t *__restrict__ x,
     __syncwarp();
     if (lane == 0) counters[t] = 0;
     router_softmax_topk(ps, E, topk, lane, idx_out + (size_t)t * topk,
+                        w_out ? w_out + (size_t)t * topk : nullptr);
+}
+
+/*
+ * Throughput path for many tokens, in two kernels.
+ *
+ * router_logits_kernel<TT>: grid = (ceil(T/TT), E/256), block = 288.  A CTA
+ * scores 256 experts against TT tokens.  The router matrix streams through a
+ * three-stage shared-memory ring of [256 rows x 64 k] tiles loaded by TMA
+ * (128-byte swizzle, no multicast), the token tile is converted to fp32 in
+ * the same ring, and thread e walks TT exact chains for expert row e with one
+ * 16-byte swizzled shared load per eight k.  Lanes 0..TT-1 of the ninth warp
+ * score the optional extra row (the shared expert's gate) the same way.
+ * BF16 logits go to logits_out [T, E].  Requires E % 256 == 0, K % 64 == 0.
+ *
+ * router_select_kernel: one warp per token turns the logits into ids and
+ * weights (router_softmax_topk).
+ */
+constexpr int RL_STAGES = 3;
+constexpr int RL_ROWS = 256;
+constexpr int RL_BK = 64;
+
+template <int TT>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box {64,128} */
+                     const uint16_t *__restrict__ x, int T, int E, int K,
+                     float wmin, uint16_t *__restrict__ logits_out,
+                     const uint16_t *__restrict__ extra_row,
+                     uint16_t *__restrict__ extra_out, int *status) {
+    extern __shared__ unsigned char rl_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(rl_smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int W_BYTES = RL_ROWS * RL_BK * 2;           /* 32 KB */
+    constexpr int X_BYTES = TT * RL_BK * 4;
+    constexpr int STAGE = W_BYTES + ((X_BYTES + 1023) & ~1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + RL_STAGES * STAGE);
+    __shared__ unsigned int s_xmin;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = blockIdx.x * TT;
+    const int e0 = blockIdx.y * RL_ROWS;
+    const int nkb = K / RL_BK;
+    if (tid == 0) {
+        for (int s = 0; s < RL_STAGES; s++) mbar_init(&full[s], 1);
+        mbar_fence_init();
+        s_xmin = 0x7f800000u;
+    }
+    __syncthreads();
+
+    auto issue = [&](int kb) {   /* thread 0 */
+        const int s = kb % RL_STAGES;
+        unsigned char *st = smem + (size_t)s * STAGE;
+        mbar_expect_tx(&full[s], W_BYTES);
+        tma_load_2d_rl(st, &map_w, kb * RL_BK, e0, &full[s]);
+        tma_load_2d_rl(st + W_BYTES / 2, &map_w, kb * RL_BK, e0 + 128, &full[s]);
+    };
+    /* The token tile's k-slice for a stage: each thread fetches up to two
+     * elements into registers (x_fetch) early, so the global-load latency
+     * hides behind the chains, and drops them into the stage afterwards
+     * (x_store). */
+    constexpr int XE = TT * RL_BK;                 /* elements per stage */
+    static_assert(XE <= 2 * ROUTER_THREADS, "token tile too large");
+    uint16_t xr0 = 0, xr1 = 0;
+    auto x_fetch = [&](int kb) {
+        const int i0 = tid, i1 = tid + ROUTER_THREADS;
+        xr0 = 0; xr1 = 0;
+        if (i0 < XE) {
+            const int t = i0 / RL_BK, j = i0 - t * RL_BK;
+            if (t0 + t < T) xr0 = __ldg(x + (size_t)(t0 + t) * K + kb * RL_BK + j);
+        }
+        if (i1 < XE) {
+            const int t = i1 / RL_BK, j = i1 - t * RL_BK;
+            if (t0 + t < T) xr1 = __ldg(x + (size_t)(t0 + t) * K + kb * RL_BK + j);
+        }
+    };
+    auto x_store = [&](int kb) {
+        const int s = kb % RL_STAGES;
+        float *xs = reinterpret_cast<float *>(smem + (size_t)s * STAGE + W_BYTES);
+        if (tid < XE) xs[tid] = bf16_f32(xr0);
+        if (tid + ROUTER_THREADS < XE) xs[tid + ROUTER_THREADS] = bf16_f32(xr1);
+    };
+    if (tid == 0)
+        for (int kb = 0; kb < RL_STAGES && kb < nkb; kb++) issue(kb);
+    for (int kb = 0; kb < RL_STAGES && kb < nkb; kb++) {
+        x_fetch(kb);
+        x_store(kb);
+    }
+
+    /* smallest nonzero |x| of the token tile (FMA-exactness guard) */
+    unsigned int xmin = 0x7f800000u;
+    for (int i = tid; i < TT * (K / 8); i += ROUTER_THREADS) {
+        const int t = i / (K / 8), c = i - t * (K / 8);
+        if (t0 + t < T) {
+            const uint4 v = ldg16(x + (size_t)(t0 + t) * K + (size_t)c * 8);
+            const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                unsigned int a = (wds[q] << 16) & 0x7fffffffu;
+                unsigned int b = wds[q] & 0x7fff0000u;
+                if (a != 0 && a < xmin) xmin = a;
+                if (b != 0 && b < xmin) xmin = b;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        xmin = min(xmin, __shfl_xor_sync(0xffffffffu, xmin, o));
+    if (lane == 0) atomicMin(&s_xmin, xmin);
+    __syncthreads();
+    const bool use_fma =
+        (wmin > 0.0f) &&
+        ((double)wmin * (double)__uint_as_float(s_xmin) >= 7.52316384526264e-37);
+
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.0f;
+    const bool is_expert = tid < RL_ROWS;
+    const bool is_extra = extra_row && blockIdx.y == 0 && warp == RL_ROWS / 32 &&
+                          lane < TT;
+    bool ok = true;
+    for (int kb = 0; kb < nkb; kb++) {
+        const int s = kb % RL_STAGES;
+        if (kb + RL_STAGES < nkb) x_fetch(kb + RL_STAGES);
+        if (ok && !mbar_wait(&full[s], (uint32_t)(kb / RL_STAGES) & 1u)) {
+            ok = false;
+            set_status(status, ST_MBAR_TIMEOUT);
+        }
+        const unsigned char *st = smem + (size_t)s * STAGE;
+        const float *xs = reinterpret_cast<const float *>(st + W_BYTES);
+        if (ok && is_expert) {
+            const unsigned char *wrow =
+                st + (tid >> 7) * (W_BYTES / 2) + (tid & 127) * 128;
+#pragma unroll 2
+            for (int c = 0; c < 8; c++) {
+                const uint4 wv = *reinterpret_cast<const uint4 *>(
+                    wrow + ((c ^ (tid & 7)) << 4));
+                const float wf[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y),
+                                     bf16hi(wv.y), bf16lo(wv.z), bf16hi(wv.z),
+                                     bf16lo(wv.w), bf16hi(wv.w)};
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    const float4 xa = *reinterpret_cast<const float4 *>(
+                        xs + t * RL_BK + c * 8);
+                    const float4 xb = *reinterpret_cast<const float4 *>(
+                        xs + t * RL_BK + c * 8 + 4);
+                    const float xf[8] = {xa.x, xa.y, xa.z, xa.w,
+                                         xb.x, xb.y, xb.z, xb.w};
+                    if (use_fma) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            acc[t] = __fmaf_rn(wf[j], xf[j], acc[t]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            acc[t] = __fadd_rn(acc[t], __fmul_rn(wf[j], xf[j]));
+                    }
+                }
+            }
+        } else if (ok && is_extra) {
+            /* lane t: the extra row against token t (literal chain) */
+            float a = acc[0];
+            for (int j = 0; j < RL_BK; j++)
+                a = __fadd_rn(a, __fmul_rn(bf16_f32(__ldg(extra_row + kb * RL_BK + j)),
+                                           xs[lane * RL_BK + j]));
+            acc[0] = a;
+        }
+        __syncthreads();            /* everyone is done with stage s */
+        if (kb + RL_STAGES < nkb) {
+            if (tid == 0 && ok) issue(kb + RL_STAGES);
+            x_store(kb + RL_STAGES);
+        }
+    }
+    if (!ok) return;
+    if (is_expert) {
+#pragma unroll
+        for (int t = 0; t < TT; t++)
+            if (t0 + t < T)
+                logits_out[(size_t)(t0 + t) * E + e0 + tid] = bf16_bits(acc[t]);
+    } else if (is_extra) {
+        if (t0 + lane < T) extra_out[t0 + lane] = bf16_bits(acc[0]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+router_select_kernel(const uint16_t *__restrict__ logits, int T, int E,
+                     int topk, int32_t *__restrict__ idx_out,
+                     uint16_t *__restrict__ w_out) {
+    extern __shared__ float sel_smem[];   /* [8][E] */
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    float *p = sel_smem + (size_t)warp * E;
+    for (int e = lane; e < E; e += 32) p[e] = bf16_f32(logits[(size_t)t * E + e]);
+    __syncwarp();
+    router_softmax_topk(p, E, topk, lane, idx_out + (size_t)t * topk,
                         w_out ? w_out + (size_t)t * topk : nullptr);
 }
 
