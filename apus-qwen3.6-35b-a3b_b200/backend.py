@@ -63,7 +63,8 @@ SYMBOLS = [
     "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
-    "apus_cuda_route_dev", "apus_cuda_dispatch_dev", "apus_cuda_rmsnorm_dev",
+    "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
+    "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
 ]
 
@@ -118,6 +119,8 @@ class Backend:
         L.apus_cuda_last_stage_ms.argtypes = [C.POINTER(C.c_float), C.c_int]
         L.apus_cuda_route_dev.argtypes = [vp, vp, sz, vp, vp, vp]
         L.apus_cuda_dispatch_dev.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
+        L.apus_cuda_dispatch_dev_static.argtypes = [vp, sz, sz, sz, vp, vp, vp,
+                                                    vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
         L.apus_synth_fill_host.argtypes = [u16p, sz, C.c_uint64, C.c_uint32,
@@ -328,6 +331,14 @@ class Backend:
                                                     d_counts, d_offsets,
                                                     d_perm, stream),
                     "apus_cuda_dispatch_dev")
+
+    def dispatch_dev_static(self, d_idx, T, topk, E, d_counts, d_offsets,
+                            d_perm, stream=None):
+        """apus_cuda_dispatch_dev_static: the dispatch with its scratch in
+        the library's built-in array; never allocates."""
+        self._check(self.lib.apus_cuda_dispatch_dev_static(
+            d_idx, T, topk, E, d_counts, d_offsets, d_perm, stream),
+            "apus_cuda_dispatch_dev_static")
 
     def rmsnorm_dev(self, d_x, d_w, d_y, T, N, stream=None):
         self._check(self.lib.apus_cuda_rmsnorm_dev(d_x, d_w, d_y, T, N,

@@ -1130,3 +1130,77 @@ extern "C" int apus_synth_fill_dev(uint16_t *d_dst, size_t n, uint64_t seed,
     return 0;
 }
 
+/* ------------------------------------------------------------------------ */
+/* dispatch without any allocation                                           */
+/* ------------------------------------------------------------------------ */
+
+/* Scratch for apus_cuda_dispatch_dev_static: the per-unit histograms of the
+ * three-pass dispatch plus one status word.  It is part of the library image,
+ * so every GPU that loads the library carries this 1 MiB until the process
+ * exits, whether or not the entry point is ever called. */
+#define APUS_STATIC_SCRATCH_INTS 262144u
+static __device__ __align__(256) int32_t
+    g_dispatch_static_scratch[APUS_STATIC_SCRATCH_INTS + 64];
+
+/* Device address of the array above, per device.  The array's name is only a
+ * host-side handle here; the address a kernel can use comes from
+ * cudaGetSymbolAddress, asked once per device with that device current. */
+static int32_t *g_dispatch_static_addr[64] = {};
+static std::mutex g_dispatch_static_mu;
+
+extern "C" int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T,
+                                             size_t topk, size_t E,
+                                             int32_t *d_counts,
+                                             int32_t *d_offsets,
+                                             int32_t *d_perm, void *stream) {
+    const size_t A = T * topk;
+    if (!d_idx || !d_counts || !d_offsets || !d_perm || !A || !E)
+        return fail("dispatch_dev_static: bad args");
+    if (E > 1024) return fail("dispatch_dev_static: unsupported E=%zu", E);
+    if (A > 0x7fffffffu) return fail("dispatch_dev_static: T*topk too large");
+    const size_t units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
+    if (A > 4096 && units * E > APUS_STATIC_SCRATCH_INTS)
+        return fail("dispatch_dev_static: ceil(T*topk/256)*E = %zu exceeds the "
+                    "built-in scratch of %u entries; use apus_cuda_dispatch_dev",
+                    units * E, APUS_STATIC_SCRATCH_INTS);
+    int dev = -1;
+    CU_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64)
+        return fail("dispatch_dev_static: device ordinal %d not supported", dev);
+    int32_t *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_dispatch_static_mu);
+        if (!g_dispatch_static_addr[dev]) {
+            void *p = nullptr;
+            CU_OK(cudaGetSymbolAddress(&p, g_dispatch_static_scratch));
+            g_dispatch_static_addr[dev] = static_cast<int32_t *>(p);
+        }
+        scratch = g_dispatch_static_addr[dev];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int *status = reinterpret_cast<int *>(scratch + APUS_STATIC_SCRATCH_INTS);
+    CU_OK(cudaMemsetAsync(status, 0, sizeof(int), st));
+    DispatchOut o;
+    memset(&o, 0, sizeof o);
+    o.counts = d_counts;
+    o.offsets = d_offsets;
+    o.perm = d_perm;
+    const int Ai = (int)A, Ei = (int)E;
+    if (A <= 4096) {
+        dispatch_small_kernel<<<1, 256, 2 * E * sizeof(int), st>>>(d_idx, Ai, Ei,
+                                                                   o, status);
+    } else {
+        const int blocks = (int)((units + DISPATCH_WARPS - 1) / DISPATCH_WARPS);
+        const size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);
+        dispatch_hist_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
+            d_idx, Ai, Ei, scratch, status);
+        dispatch_scan_kernel<<<1, 1024, 0, st>>>(scratch, (int)units, Ei, o);
+        dispatch_permute_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
+            d_idx, Ai, Ei, scratch, o);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail("dispatch_dev_static: launch failed: %s",
+                    cudaGetErrorString(e));
+    return 0;
+}

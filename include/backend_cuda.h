@@ -230,6 +230,35 @@ int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T, size_t topk,
                            size_t E, int32_t *d_counts, int32_t *d_offsets,
                            int32_t *d_perm, void *stream);
 
+/* Same result as apus_cuda_dispatch_dev, for callers that must not touch the
+ * device allocator.  (No counterpart in the reference engine, which has no
+ * device memory at all.)  Who needs it: a serving loop that has handed every
+ * free byte of HBM to its own pool, so a cudaMalloc from a library would fail
+ * or fragment it; code running between the begin and end of a section where
+ * allocation is forbidden by its owner; latency-critical paths where an
+ * allocator call means an implicit device synchronisation.  This entry point
+ * calls no cudaMalloc, cudaFree or other allocating routine: the per-unit
+ * histogram scratch the three-pass dispatch needs lives in a 1 MiB array
+ * built into the library (every GPU that loads the library holds it until the
+ * process exits).  The caller still supplies d_idx and the three outputs.
+ *
+ * Limit: ceil(T*topk/256) * E <= 262144 (e.g. T*topk up to 262144 at E=256);
+ * larger problems are refused with an error, not truncated.  E <= 1024.
+ *
+ * The first call on each device looks up the array's device address (with
+ * that device current) and should therefore be made once, outside any stream
+ * capture, before the calls that matter.  `stream` is used as given (NULL =
+ * the default stream); the call enqueues and returns without synchronising.
+ * All calls share the one array, and it keeps whatever the last call left
+ * there; the kernels overwrite every entry they later read and the status
+ * word is cleared on each call, but two calls whose kernels overlap on the
+ * GPU (different streams, no ordering between them) race on it.  Expert ids
+ * outside [0, E) are skipped silently here. */
+int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T, size_t topk,
+                                  size_t E, int32_t *d_counts,
+                                  int32_t *d_offsets, int32_t *d_perm,
+                                  void *stream);
+
 /* ---- the two steps either side of the block (c/layer.h:386,388) --------- */
 /* y = rmsnorm(x, gain 1+w) per row (c/attn.h:175-186; w NULL = zero gain
  * offset); out = rnd(a + b) (c/layer.h:230-234).  Device pointers. */
