@@ -63,6 +63,8 @@ SYMBOLS = [
     "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
+    "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
+    "apus_cuda_ep_finish_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
     "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
@@ -121,6 +123,12 @@ class Backend:
         L.apus_cuda_dispatch_dev.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
         L.apus_cuda_dispatch_dev_static.argtypes = [vp, sz, sz, sz, vp, vp, vp,
                                                     vp]
+        L.apus_cuda_ep_route_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp]
+        L.apus_cuda_ep_pack_dev.argtypes = [vp, vp, sz, sz, sz, sz, sz, vp, vp,
+                                            vp, vp, vp]
+        L.apus_cuda_experts_dev.argtypes = [vp, vp, vp, sz, vp, vp]
+        L.apus_cuda_ep_finish_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp,
+                                              C.POINTER(MoeTrace), vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
         L.apus_synth_fill_host.argtypes = [u16p, sz, C.c_uint64, C.c_uint32,
@@ -339,6 +347,33 @@ class Backend:
         self._check(self.lib.apus_cuda_dispatch_dev_static(
             d_idx, T, topk, E, d_counts, d_offsets, d_perm, stream),
             "apus_cuda_dispatch_dev_static")
+
+    # ---- expert parallelism ---------------------------------------------------
+    def ep_route_dev(self, layer, d_x, T, d_idx, d_w, d_sgl, stream=None):
+        self._check(self.lib.apus_cuda_ep_route_dev(layer, d_x, T, d_idx, d_w,
+                                                    d_sgl, stream),
+                    "apus_cuda_ep_route_dev")
+
+    def ep_pack_dev(self, d_x, d_idx, T, topk, H, E, n_ranks, d_send_x,
+                    d_send_e, d_send_counts, d_pos, stream=None):
+        self._check(self.lib.apus_cuda_ep_pack_dev(
+            d_x, d_idx, T, topk, H, E, n_ranks, d_send_x, d_send_e,
+            d_send_counts, d_pos, stream), "apus_cuda_ep_pack_dev")
+
+    def experts_dev(self, layer, d_x, d_e, R, d_y, stream=None):
+        self._check(self.lib.apus_cuda_experts_dev(layer, d_x, d_e, R, d_y,
+                                                   stream),
+                    "apus_cuda_experts_dev")
+
+    def ep_finish_dev(self, layer, d_x, T, d_y_sorted, d_pos, d_w, d_sgl,
+                      d_out, stream=None, d_trace=None):
+        tr = None
+        if d_trace:
+            tr = MoeTrace(None, None, d_trace.get("routed"),
+                          d_trace.get("shared"), d_trace.get("out"))
+        self._check(self.lib.apus_cuda_ep_finish_dev(
+            layer, d_x, T, d_y_sorted, d_pos, d_w, d_sgl, d_out,
+            C.byref(tr) if tr else None, stream), "apus_cuda_ep_finish_dev")
 
     def rmsnorm_dev(self, d_x, d_w, d_y, T, N, stream=None):
         self._check(self.lib.apus_cuda_rmsnorm_dev(d_x, d_w, d_y, T, N,

@@ -90,6 +90,8 @@ struct Ctx {
     int ev_stage[16] = {};
 };
 
+namespace apus { bool g_apus_use_pdl = true; }
+
 static Ctx *g_ctx = nullptr;
 static std::recursive_mutex g_mu;
 static char g_err[512] = "";
@@ -164,6 +166,7 @@ static int ctx_init() {
     long mb = env_long("APUS_CUDA_DENSE_MB", -1);
     c->budget = mb < 0 ? ~0ull : (uint64_t)mb << 20;
     c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 64);
+    g_apus_use_pdl = env_long("APUS_CUDA_PDL", 1) != 0;
     g_ctx = c;
     return 0;
 }
@@ -382,8 +385,7 @@ static int launch_router_tt(Ctx *c, const uint16_t *dx, const uint16_t *dwr,
                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)smem));
     int grid = (T + TT - 1) / TT;
-    router_topk_kernel<TT><<<grid, ROUTER_THREADS, smem, st>>>(
-        dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row, extra_out);
+    launch_k(router_topk_kernel<TT>, dim3(grid), dim3(ROUTER_THREADS), smem, st, dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row, extra_out);
     LAUNCHED();
     return 0;
 }
@@ -408,8 +410,7 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
                     router_small_kernel,
                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             dim3 grid((rows + ROUTER_SMALL_ROWS - 1) / ROUTER_SMALL_ROWS, T);
-            router_small_kernel<<<grid, 32, smem, st>>>(
-                dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row,
+            launch_k(router_small_kernel, dim3(grid), dim3(32), smem, st, dx, dwr, T, E, K, topk, wmin, didx, dw, dlogits, extra_row,
                 extra_out, c->d_router_logits, c->d_router_counters,
                 c->d_status);
             LAUNCHED();
@@ -417,33 +418,40 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         }
     }
     /* many tokens: TMA-staged router tiles, then one warp per token */
-    if (T > ROUTER_SMALL_MAX_T && dlogits && E % RL_ROWS == 0 &&
-        K % RL_BK == 0 && (((uintptr_t)dwr) & 15) == 0) {
+    if (T > ROUTER_SMALL_MAX_T && dlogits && E % 256 == 0 && K % RL_BK == 0 &&
+        (((uintptr_t)dwr | (uintptr_t)dx) & 15) == 0) {
         PFN_encodeTiled_local enc = tensor_map_encoder();
         if (!enc) return fail("%s", prefill_last_error());
         CUtensorMap map_w;
         if (encode_2d(enc, &map_w, dwr, (size_t)E, (size_t)K))
             return fail("%s", prefill_last_error());
-        const int tt = T >= 16 * c->sm_count ? 8 : (T >= 4 * c->sm_count ? 4 : 2);
-        const size_t xb = ((size_t)tt * RL_BK * 4 + 1023) & ~(size_t)1023;
-        const size_t smem = RL_STAGES * ((size_t)RL_ROWS * RL_BK * 2 + xb) + 1024 + 64;
-        dim3 grid((T + tt - 1) / tt, E / RL_ROWS);
-#define RL_LAUNCH(TTV)                                                          \
+        /* the token tile sets the L2 traffic (T/TT copies of the matrix);
+         * take the largest one that still gives every SM a CTA */
+        const int tt = T >= 32 * c->sm_count ? 32 : (T >= 16 * c->sm_count ? 16 : 8);
+        const int rows = tt == 8 ? 128 : 256;
+        const size_t xb = ((size_t)tt * RL_XPITCH * 4 + 1023) & ~(size_t)1023;
+        const size_t smem = RL_STAGES * ((size_t)rows * RL_BK * 2 + xb) + 1024 + 64;
+        dim3 grid((T + tt - 1) / tt, E / rows);
+#define RL_LAUNCH(TTV, ROWSV)                                                   \
         do {                                                                    \
-            CU_OK(cudaFuncSetAttribute(                                         \
-                router_logits_kernel<TTV>,                                      \
-                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
-            router_logits_kernel<TTV><<<grid, ROUTER_THREADS, smem, st>>>(      \
-                map_w, dx, T, E, K, wmin, dlogits, extra_row, extra_out,        \
-                c->d_status);                                                   \
+            static bool set_ = false;                                           \
+            if (!set_) {                                                        \
+                CU_OK(cudaFuncSetAttribute(                                     \
+                    router_logits_kernel<TTV, ROWSV>,                           \
+                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+                set_ = true;                                                    \
+            }                                                                   \
+            launch_k(router_logits_kernel<TTV, ROWSV>, grid, dim3(ROWSV + 32),  \
+                     smem, st, map_w, dx, T, E, K, wmin, dlogits, extra_row,    \
+                     extra_out, c->d_status);                                   \
         } while (0)
-        if (tt == 8) RL_LAUNCH(8);
-        else if (tt == 4) RL_LAUNCH(4);
-        else RL_LAUNCH(2);
+        if (tt == 32) RL_LAUNCH(32, 256);
+        else if (tt == 16) RL_LAUNCH(16, 256);
+        else RL_LAUNCH(8, 128);
 #undef RL_LAUNCH
         LAUNCHED();
-        router_select_kernel<<<(T + 7) / 8, 256, (size_t)8 * E * sizeof(float), st>>>(
-            dlogits, T, E, topk, didx, dw);
+        launch_k(router_select_kernel, dim3((T + 7) / 8), dim3(256),
+                 (size_t)8 * E * sizeof(float), st, dlogits, T, E, topk, didx, dw);
         LAUNCHED();
         return 0;
     }
@@ -467,24 +475,29 @@ static size_t dispatch_scratch_bytes(size_t A, size_t E) {
 
 static int launch_dispatch(Ctx *c, const int32_t *didx, int A, int E,
                            DispatchOut o, int32_t *unit_hist,
-                           cudaStream_t st) {
+                           cudaStream_t st, DispatchKey kx = DispatchKey{0, 1}) {
     if (E < 1 || E > 1024) return fail("dispatch: unsupported E=%d", E);
-    if (A <= 1024) {
-        dispatch_small_kernel<<<1, 256, 2 * E * sizeof(int), st>>>(
-            didx, A, E, o, c->d_status);
+    if (A <= DISPATCH_SMALL_MAX) {
+        const size_t smem = (size_t)32 * E * sizeof(int);
+        static bool attr_set = false;
+        if (!attr_set) {
+            CU_OK(cudaFuncSetAttribute(dispatch_small_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       32 * 1024 * (int)sizeof(int)));
+            attr_set = true;
+        }
+        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), smem, st, didx, A, E, kx, o, c->d_status);
         LAUNCHED();
         return 0;
     }
     int units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
     int blocks = (units + DISPATCH_WARPS - 1) / DISPATCH_WARPS;
     size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);
-    dispatch_hist_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
-        didx, A, E, unit_hist, c->d_status);
+    launch_k(dispatch_hist_kernel, dim3(blocks), dim3(DISPATCH_WARPS * 32), smem, st, didx, A, E, kx, unit_hist, c->d_status);
     LAUNCHED();
-    dispatch_scan_kernel<<<1, 1024, 0, st>>>(unit_hist, units, E, o);
+    launch_k(dispatch_scan_kernel, dim3(1), dim3(1024), 0, st, unit_hist, units, E, o);
     LAUNCHED();
-    dispatch_permute_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
-        didx, A, E, unit_hist, o);
+    launch_k(dispatch_permute_kernel, dim3(blocks), dim3(DISPATCH_WARPS * 32), smem, st, didx, A, E, kx, unit_hist, o);
     LAUNCHED();
     return 0;
 }
@@ -786,9 +799,12 @@ static int decode_smem_bytes(const ApusCudaMoeCfg &c, bool down) {
                  DEC_WARPS * DEC_STAGES * 8 + 128);
 }
 
-/* routed + shared experts through the grouped-GEMV kernels */
+/* routed and/or shared experts through the grouped-GEMV kernels.  x [T,H];
+ * TK slots per token; routed outputs go to eo_out in flat assignment order;
+ * expert ids in the group list are relative to expert_base. */
 static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
-                              int T, BlockBufs &b, bool do_shared,
+                              int T, int TK, int expert_base, BlockBufs &b,
+                              bool do_shared, uint16_t *eo_out,
                               cudaStream_t st) {
     const ApusCudaMoeCfg &cfg = L->cfg;
     DecodeArgs a;
@@ -797,8 +813,8 @@ static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
     a.H = (int)cfg.hidden;
     a.I = (int)cfg.moe_inter;
     a.Is = (int)cfg.shared_inter;
-    a.TK = (int)cfg.top_k;
-    a.expert_begin = (int)L->e_begin;
+    a.TK = TK;
+    a.expert_begin = expert_base;
     a.x = dx;
     a.exp_gu = L->exp_gu;
     a.exp_d = L->exp_d;
@@ -812,7 +828,7 @@ static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
     a.n_groups = b.d.n_groups;
     a.act = b.act;
     a.sa = b.sa;
-    a.eo = b.eo;
+    a.eo = eo_out;
     a.sy = b.sy;
     a.do_shared = do_shared ? 1 : 0;
     a.status = c->d_status;
@@ -821,31 +837,41 @@ static int run_decode_experts(Ctx *c, ApusCudaLayer *L, const uint16_t *dx,
         return fail("decode kernels need %d/%d B shared memory (> %d)", s1, s2,
                     c->smem_optin);
     if (cfg.hidden % DOWN_ROWS) return fail("hidden must be a multiple of 8");
-    CU_OK(cudaFuncSetAttribute(decode_gate_up_kernel,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, s1));
-    CU_OK(cudaFuncSetAttribute(decode_down_kernel,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
-    decode_gate_up_kernel<<<c->sm_count, DEC_THREADS, s1, st>>>(a);
+    static int set1 = 0, set2 = 0;
+    if (s1 > set1) {
+        CU_OK(cudaFuncSetAttribute(decode_gate_up_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, s1));
+        set1 = s1;
+    }
+    if (s2 > set2) {
+        CU_OK(cudaFuncSetAttribute(decode_down_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, s2));
+        set2 = s2;
+    }
+    launch_k(decode_gate_up_kernel, dim3(c->sm_count), dim3(DEC_THREADS), s1, st, a);
     LAUNCHED();
     stage_mark(c, APUS_CUDA_STAGE_GATE_UP, st);
-    decode_down_kernel<<<c->sm_count, DEC_THREADS, s2, st>>>(a);
+    launch_k(decode_down_kernel, dim3(c->sm_count), dim3(DEC_THREADS), s2, st, a);
     LAUNCHED();
     stage_mark(c, APUS_CUDA_STAGE_DOWN, st);
     return 0;
 }
 
-static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T, BlockBufs &b,
-                        uint16_t *d_out, const ApusCudaMoeTrace *tr,
-                        bool with_shared, cudaStream_t st) {
+static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T,
+                        const uint16_t *eo, const int32_t *pos,
+                        const uint16_t *rw, const uint16_t *sy,
+                        const uint16_t *sgl, uint16_t *d_out,
+                        const ApusCudaMoeTrace *tr, cudaStream_t st) {
     FinalizeArgs f;
     memset(&f, 0, sizeof f);
     f.T = T;
     f.H = (int)cfg.hidden;
     f.TK = (int)cfg.top_k;
-    f.eo = b.eo;
-    f.rw = b.rw;
-    f.sy = with_shared ? b.sy : nullptr;
-    f.sgl = b.sgl;
+    f.eo = eo;
+    f.pos = pos;
+    f.rw = rw;
+    f.sy = sy;
+    f.sgl = sgl;
     f.out = d_out;
     f.tr_routed = tr ? tr->moe_routed : nullptr;
     f.tr_shared = tr ? tr->moe_shared : nullptr;
@@ -853,7 +879,7 @@ static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T, BlockBufs &b,
     long total = (long)T * (cfg.hidden / 8);
     int blocks = (int)((total + 255) / 256);
     if (blocks > c->sm_count * 8) blocks = c->sm_count * 8;
-    moe_finalize_kernel<<<blocks, 256, 0, st>>>(f);
+    launch_k(moe_finalize_kernel, dim3(blocks), dim3(256), 0, st, f);
     LAUNCHED();
     return 0;
 }
@@ -886,16 +912,17 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
         const int before = c->last_block_launches;
         g_mark_stream = st;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
-                                (int)L->e_begin, d_ln2, Ti, Ti * TK, true, b.d,
+                                (int)L->e_begin, d_ln2, Ti, Ti * TK, TK, true, b.d,
                                 b.xg, b.act, b.sa, b.eo, b.sy, b.tiles,
                                 c->d_status, st, &c->last_block_launches,
                                 mark_cb))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
     } else {
-        if (run_decode_experts(c, L, d_ln2, Ti, b, true, st)) return 1;
+        if (run_decode_experts(c, L, d_ln2, Ti, TK, 0, b, true, b.eo, st)) return 1;
     }
-    if (run_finalize(c, cfg, Ti, b, d_out, d_tr, true, st)) return 1;
+    if (run_finalize(c, cfg, Ti, b.eo, nullptr, b.rw, b.sy, b.sgl, d_out, d_tr, st))
+        return 1;
     stage_mark(c, APUS_CUDA_STAGE_FINALIZE, st);
     if (d_tr && d_tr->rtr_idx)
         CU_OK(cudaMemcpyAsync(d_tr->rtr_idx, b.idx, T * TK * 4,
@@ -1026,6 +1053,169 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
                     "an index was out of range)", st);
     }
     return 0;
+}
+
+
+/* ------------------------------------------------------------------------ */
+/* expert parallelism                                                        */
+/* ------------------------------------------------------------------------ */
+
+static int ensure_maps(ApusCudaLayer *L) {
+    if (L->maps || !prefill_supported(L->cfg)) return 0;
+    L->maps = prefill_maps_create(L->cfg, L->exp_gu, L->exp_d, L->sh_g, L->sh_u,
+                                  L->sh_d, L->e_end - L->e_begin);
+    if (!L->maps) return fail("%s", prefill_last_error());
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
+                                      size_t T, int32_t *d_idx, uint16_t *d_w,
+                                      uint16_t *d_sgl, void *stream) {
+    if (!L || !d_x || !d_idx || !d_w || !d_sgl || !T)
+        return fail("ep_route_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    const size_t E = L->cfg.experts;
+    if (arena_reserve(c->ws, T * E * 2 + 4096)) return 1;
+    c->ws.reset();
+    uint16_t *logits = (uint16_t *)c->ws.take(T * E * 2);
+    return launch_router(c, d_x, L->rtr_w, (int)T, (int)E, (int)L->cfg.hidden,
+                         (int)L->cfg.top_k, L->wmin, d_idx, d_w, logits,
+                         L->sh_gate, d_sgl, st);
+}
+
+/* gather kernel for the pack step: send_e[p] = idx[perm[p]] */
+__global__ void ep_gather_ids_kernel(const int32_t *__restrict__ idx,
+                                     const int32_t *__restrict__ perm, int A,
+                                     int32_t *__restrict__ out) {
+    pdl_enter();
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < A;
+         p += gridDim.x * blockDim.x)
+        out[p] = idx[perm[p]];
+}
+
+extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
+                                     size_t T, size_t topk, size_t H, size_t E,
+                                     size_t n_ranks, uint16_t *d_send_x,
+                                     int32_t *d_send_e, int32_t *d_send_counts,
+                                     int32_t *d_pos, void *stream) {
+    const size_t A = T * topk;
+    if (!d_x || !d_idx || !d_send_x || !d_send_e || !d_send_counts || !d_pos ||
+        !A || !n_ranks || E % n_ranks || H % 8)
+        return fail("ep_pack_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    const size_t need = dispatch_scratch_bytes(A, n_ranks) + A * 4 +
+                        (n_ranks + 1) * 4 + 4096;
+    if (arena_reserve(c->ws, need)) return 1;
+    c->ws.reset();
+    DispatchOut o;
+    memset(&o, 0, sizeof o);
+    o.counts = d_send_counts;
+    o.offsets = (int32_t *)c->ws.take((n_ranks + 1) * 4);
+    o.perm = (int32_t *)c->ws.take(A * 4);
+    o.pos = d_pos;
+    int32_t *uh = (int32_t *)c->ws.take(dispatch_scratch_bytes(A, n_ranks));
+    if (launch_dispatch(c, d_idx, (int)A, (int)n_ranks, o, uh, st,
+                        DispatchKey{0, (int)(E / n_ranks)}))
+        return 1;
+    long total = (long)A * (long)(H / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > c->sm_count * 16) blocks = c->sm_count * 16;
+    launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, d_x, o.perm,
+             (int)A, (int)H, (int)topk, d_send_x);
+    LAUNCHED();
+    launch_k(ep_gather_ids_kernel, dim3((unsigned)((A + 255) / 256)), dim3(256),
+             0, st, d_idx, o.perm, (int)A, d_send_e);
+    LAUNCHED();
+    return 0;
+}
+
+extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
+                                     const int32_t *d_e, size_t R,
+                                     uint16_t *d_y, void *stream) {
+    if (!L || !d_x || !d_e || !d_y) return fail("experts_dev: bad args");
+    if (!R) return 0;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    const size_t ne = L->e_end - L->e_begin;
+    if (!ne) return fail("experts_dev: no routed experts resident");
+    ApusCudaMoeCfg cx = L->cfg;       /* the shape dispatch and tiling see */
+    cx.experts = ne;
+    cx.top_k = 1;
+    const bool prefill = (int)R > c->decode_max_t && prefill_supported(L->cfg);
+    if (prefill && ensure_maps(L)) return 1;
+    BlockBufs b;
+    block_layout(cx, R, nullptr, &b, prefill);
+    if (arena_reserve(c->ws, b.total)) return 1;
+    if (block_layout(cx, R, &c->ws, &b, prefill)) return 1;
+    if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
+                        DispatchKey{(int)L->e_begin, 1}))
+        return 1;
+    if (prefill) {
+        const int before = c->last_block_launches;
+        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x,
+                                (int)R, (int)R, 1, false, b.d, b.xg, b.act, b.sa,
+                                d_y, b.sy, b.tiles, c->d_status, st,
+                                &c->last_block_launches, nullptr))
+            return fail("%s", prefill_last_error());
+        c->launches += (uint64_t)(c->last_block_launches - before);
+        return 0;
+    }
+    return run_decode_experts(c, L, d_x, (int)R, 1, 0, b, false, d_y, st);
+}
+
+extern "C" int apus_cuda_ep_finish_dev(ApusCudaLayer *L, const uint16_t *d_x,
+                                       size_t T, const uint16_t *d_y_sorted,
+                                       const int32_t *d_pos,
+                                       const uint16_t *d_w,
+                                       const uint16_t *d_sgl, uint16_t *d_out,
+                                       const ApusCudaMoeTrace *d_tr,
+                                       void *stream) {
+    if (!L || !d_x || !d_y_sorted || !d_pos || !d_w || !d_sgl || !d_out || !T)
+        return fail("ep_finish_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    const ApusCudaMoeCfg &cfg = L->cfg;
+    /* shared expert only: a dispatch result with no routed rows */
+    ApusCudaMoeCfg cx = cfg;
+    cx.top_k = 1;
+    const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
+    if (prefill && ensure_maps(L)) return 1;
+    BlockBufs b;
+    block_layout(cx, T, nullptr, &b, prefill);
+    if (arena_reserve(c->ws, b.total)) return 1;
+    if (block_layout(cx, T, &c->ws, &b, prefill)) return 1;
+    CU_OK(cudaMemsetAsync(b.d.counts, 0, cfg.experts * 4, st));
+    CU_OK(cudaMemsetAsync(b.d.offsets, 0, (cfg.experts + 1) * 4, st));
+    CU_OK(cudaMemsetAsync(b.d.n_groups, 0, 4, st));
+    if (prefill) {
+        const int before = c->last_block_launches;
+        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
+                                (int)L->e_begin, d_x, (int)T, 0, 1, true, b.d,
+                                b.xg, b.act, b.sa, b.eo, b.sy, b.tiles,
+                                c->d_status, st, &c->last_block_launches,
+                                nullptr))
+            return fail("%s", prefill_last_error());
+        c->launches += (uint64_t)(c->last_block_launches - before);
+    } else {
+        if (run_decode_experts(c, L, d_x, (int)T, 1, 0, b, true, b.eo, st))
+            return 1;
+    }
+    return run_finalize(c, cfg, (int)T, d_y_sorted, d_pos, d_w, b.sy, d_sgl,
+                        d_out, d_tr, st);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -1159,7 +1349,7 @@ extern "C" int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T,
     if (E > 1024) return fail("dispatch_dev_static: unsupported E=%zu", E);
     if (A > 0x7fffffffu) return fail("dispatch_dev_static: T*topk too large");
     const size_t units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
-    if (A > 4096 && units * E > APUS_STATIC_SCRATCH_INTS)
+    if (A > (size_t)DISPATCH_SMALL_MAX && units * E > APUS_STATIC_SCRATCH_INTS)
         return fail("dispatch_dev_static: ceil(T*topk/256)*E = %zu exceeds the "
                     "built-in scratch of %u entries; use apus_cuda_dispatch_dev",
                     units * E, APUS_STATIC_SCRATCH_INTS);
@@ -1186,17 +1376,17 @@ extern "C" int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T,
     o.offsets = d_offsets;
     o.perm = d_perm;
     const int Ai = (int)A, Ei = (int)E;
-    if (A <= 4096) {
-        dispatch_small_kernel<<<1, 256, 2 * E * sizeof(int), st>>>(d_idx, Ai, Ei,
-                                                                   o, status);
+    if (A <= (size_t)DISPATCH_SMALL_MAX) {
+        CU_OK(cudaFuncSetAttribute(dispatch_small_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   32 * 1024 * (int)sizeof(int)));
+        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), (size_t)32 * E * sizeof(int), st, d_idx, Ai, Ei, DispatchKey{0, 1}, o, status);
     } else {
         const int blocks = (int)((units + DISPATCH_WARPS - 1) / DISPATCH_WARPS);
         const size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);
-        dispatch_hist_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
-            d_idx, Ai, Ei, scratch, status);
-        dispatch_scan_kernel<<<1, 1024, 0, st>>>(scratch, (int)units, Ei, o);
-        dispatch_permute_kernel<<<blocks, DISPATCH_WARPS * 32, smem, st>>>(
-            d_idx, Ai, Ei, scratch, o);
+        launch_k(dispatch_hist_kernel, dim3(blocks), dim3(DISPATCH_WARPS * 32), smem, st, d_idx, Ai, Ei, DispatchKey{0, 1}, scratch, status);
+        launch_k(dispatch_scan_kernel, dim3(1), dim3(1024), 0, st, scratch, (int)units, Ei, o);
+        launch_k(dispatch_permute_kernel, dim3(blocks), dim3(DISPATCH_WARPS * 32), smem, st, d_idx, Ai, Ei, DispatchKey{0, 1}, scratch, o);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)

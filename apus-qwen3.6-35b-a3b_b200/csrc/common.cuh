@@ -137,10 +137,38 @@ __device__ __forceinline__ uint4 ldg16(const void *p) {
     return __ldg(reinterpret_cast<const uint4 *>(p));
 }
 
+/* Programmatic dependent launch: every kernel of the block begins with
+ * pdl_enter(): it lets the next kernel in the stream be scheduled early (its
+ * own prologue then overlaps this kernel's tail) and waits until the previous
+ * kernel's memory is complete and visible.  Without the launch attribute both
+ * instructions are no-ops. */
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+/* host: launch with the programmatic-stream-serialization attribute */
+extern bool g_apus_use_pdl;
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                            size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_apus_use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace apus

@@ -116,6 +116,7 @@ __device__ __forceinline__ void gate_up_rows(const uint16_t *gs,
  */
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_gate_up_kernel(DecodeArgs a) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int H = a.H;
     const int stage_elems = 2 * H;
@@ -269,6 +270,7 @@ __device__ __forceinline__ void down_rows(const uint16_t *ws,
 /* H must be a multiple of DOWN_ROWS.  Ring stage = DOWN_ROWS weight rows. */
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_down_kernel(DecodeArgs a) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int Imax = max(a.I, a.Is);
     const int stage_elems = DOWN_ROWS * Imax;
@@ -415,7 +417,8 @@ decode_down_kernel(DecodeArgs a) {
  */
 struct FinalizeArgs {
     int T, H, TK;
-    const uint16_t *eo;      /* [A, H] flat assignment order */
+    const uint16_t *eo;      /* [A, H] flat assignment order ... */
+    const int32_t *pos;      /* ... or, if not NULL, row pos[t*TK+j] of eo */
     const uint16_t *rw;      /* [T, TK] */
     const uint16_t *sy;      /* [T, H] (NULL: no shared expert term) */
     const uint16_t *sgl;     /* [T] shared-gate logits */
@@ -425,6 +428,7 @@ struct FinalizeArgs {
 
 __global__ void __launch_bounds__(256)
 moe_finalize_kernel(FinalizeArgs a) {
+    pdl_enter();
     const int cols8 = a.H / 8;
     const long total = (long)a.T * cols8;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -435,9 +439,10 @@ moe_finalize_kernel(FinalizeArgs a) {
         for (int j = 0; j < 8; j++) acc[j] = 0.0f;
         for (int s = 0; s < a.TK; s++) {
             const float w = bf16_f32(a.rw[(size_t)t * a.TK + s]);
+            const size_t flat = (size_t)t * a.TK + s;
+            const size_t row = a.pos ? (size_t)a.pos[flat] : flat;
             float y[8];
-            unpack8(ldg16(a.eo + ((size_t)t * a.TK + s) * a.H + (size_t)c * 8),
-                    y);
+            unpack8(ldg16(a.eo + row * a.H + (size_t)c * 8), y);
 #pragma unroll
             for (int j = 0; j < 8; j++)
                 acc[j] = __fadd_rn(acc[j], __fmul_rn(w, y[j]));

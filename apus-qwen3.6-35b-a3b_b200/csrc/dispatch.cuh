@@ -32,6 +32,18 @@ constexpr int DISPATCH_UNIT = 256;      /* assignments per warp */
 constexpr int DISPATCH_WARPS = 8;       /* warps per block */
 constexpr int GROUP_TOKENS = 4;         /* rows per decode token group */
 
+/* The sort key of an assignment is (idx - key_base) / key_div: plain expert
+ * ids for the block (0, 1), expert ids local to a rank's slice (begin, 1), or
+ * the owning rank under expert parallelism (0, experts per rank). */
+struct DispatchKey {
+    int base;
+    int div;
+};
+__device__ __forceinline__ int dispatch_key(int raw, DispatchKey kx) {
+    const int v = raw - kx.base;
+    return v < 0 ? -1 : v / kx.div;
+}
+
 struct DispatchOut {
     int32_t *counts;     /* [E] */
     int32_t *offsets;    /* [E+1] */
@@ -44,33 +56,51 @@ struct DispatchOut {
 };
 
 /* ---- small problems: one block does everything -------------------------- */
-/* A <= 4096, E <= 1024.  Shared: hist[E] + cursor[E] + scratch. */
-__global__ void __launch_bounds__(256)
+/* A <= 32 * DISPATCH_UNIT, E <= 1024; block = 1024 threads = 32 warps, each
+ * warp owning one unit of up to 256 consecutive assignments.  Dynamic shared
+ * memory: int [32][E] (per-warp histograms, then per-warp cursors). */
+constexpr int DISPATCH_SMALL_MAX = 32 * DISPATCH_UNIT;
+
+__global__ void __launch_bounds__(1024)
 dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
-                      DispatchOut o, int *status) {
-    extern __shared__ int sm[];
-    int *hist = sm;            /* [E] */
-    int *cursor = sm + E;      /* [E] */
-    __shared__ int warp_tot[8];
+                      DispatchKey kx, DispatchOut o, int *status) {
+    pdl_enter();
+    extern __shared__ int sm[];          /* [32][E] */
+    __shared__ int warp_tot[32];
     __shared__ int s_ngroups;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int e = tid; e < E; e += 256) hist[e] = 0;
+    int *h = sm + warp * E;
+    for (int e = lane; e < E; e += 32) h[e] = 0;
     if (tid == 0) s_ngroups = 0;
-    __syncthreads();
-    for (int a = tid; a < A; a += 256) {
-        int k = idx[a];
-        if (k < 0 || k >= E) { set_status(status, ST_BAD_INDEX); continue; }
-        atomicAdd(&hist[k], 1);
+    __syncwarp();
+    /* this warp's keys stay in registers for both passes */
+    const int a_lo = warp * DISPATCH_UNIT;
+    int keys[DISPATCH_UNIT / 32];
+#pragma unroll
+    for (int s = 0; s < DISPATCH_UNIT / 32; s++) {
+        const int a = a_lo + s * 32 + lane;
+        int k = (a < A) ? dispatch_key(idx[a], kx) : -1;
+        if (a < A && (k < 0 || k >= E)) {
+            set_status(status, ST_BAD_INDEX);
+            k = -1;
+        }
+        keys[s] = k;
+        if (k >= 0) atomicAdd(&h[k], 1);
     }
     __syncthreads();
-    /* exclusive scan over experts: thread t owns bins [t*per, (t+1)*per) */
-    const int per = (E + 255) / 256;
-    int local = 0;
-    for (int j = 0; j < per; j++) {
-        int e = tid * per + j;
-        if (e < E) local += hist[e];
+    /* per expert: exclusive prefix over the 32 warps (in place) and total */
+    int total = 0;
+    for (int e = tid; e < E; e += 1024) {   /* E <= 1024: at most one e */
+        int run = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; w++) {
+            int v = sm[w * E + e];
+            sm[w * E + e] = run;
+            run += v;
+        }
+        total = run;
     }
-    int inc = local;
+    int inc = total;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
         int v = __shfl_up_sync(0xffffffffu, inc, d);
@@ -80,49 +110,43 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     __syncthreads();
     int base = 0;
     for (int w = 0; w < warp; w++) base += warp_tot[w];
-    int run = base + inc - local;
-    for (int j = 0; j < per; j++) {
-        int e = tid * per + j;
-        if (e < E) {
-            int c = hist[e];
-            o.counts[e] = c;
-            o.offsets[e] = run;
-            cursor[e] = run;
-            if (o.grp_expert && c > 0) {
-                int ng = (c + GROUP_TOKENS - 1) / GROUP_TOKENS;
-                int g0 = atomicAdd(&s_ngroups, ng);
-                /* group order is irrelevant to results; record and move on */
-                for (int g = 0; g < ng; g++) {
-                    o.grp_expert[g0 + g] = e;
-                    o.grp_first[g0 + g] = run + g * GROUP_TOKENS;
-                    int left = c - g * GROUP_TOKENS;
-                    o.grp_n[g0 + g] = left < GROUP_TOKENS ? left : GROUP_TOKENS;
-                }
+    const int off = base + inc - total;
+    if (tid < E) {
+        o.counts[tid] = total;
+        o.offsets[tid] = off;
+        for (int w = 0; w < 32; w++) sm[w * E + tid] += off;   /* cursors */
+        if (o.grp_expert && total > 0) {
+            int ng = (total + GROUP_TOKENS - 1) / GROUP_TOKENS;
+            int g0 = atomicAdd(&s_ngroups, ng);
+            /* group order is irrelevant to results */
+            for (int g = 0; g < ng; g++) {
+                o.grp_expert[g0 + g] = tid;
+                o.grp_first[g0 + g] = off + g * GROUP_TOKENS;
+                int left = total - g * GROUP_TOKENS;
+                o.grp_n[g0 + g] = left < GROUP_TOKENS ? left : GROUP_TOKENS;
             }
-            run += c;
         }
     }
-    if (tid == 255) o.offsets[E] = base + inc;   /* == number of valid keys */
+    if (tid == 1023) o.offsets[E] = base + inc;   /* == number of valid keys */
     __syncthreads();
     if (tid == 0 && o.n_groups) *o.n_groups = s_ngroups;
-    /* stable placement: warp 0 walks the assignments in order */
-    if (warp == 0) {
-        for (int a0 = 0; a0 < A; a0 += 32) {
-            int a = a0 + lane;
-            int k = (a < A) ? idx[a] : -1;
-            bool ok = (k >= 0 && k < E);
-            unsigned act = __ballot_sync(0xffffffffu, ok);
-            if (ok) {
-                unsigned peers = __match_any_sync(act, k);
-                int rank = __popc(peers & ((1u << lane) - 1u));
-                int dst = cursor[k] + rank;
-                o.perm[dst] = a;
-                if (o.pos) o.pos[a] = dst;
-                __syncwarp(act);
-                if (rank == 0) cursor[k] += __popc(peers);
-            }
-            __syncwarp();
+    /* stable placement inside each warp's unit */
+#pragma unroll
+    for (int s = 0; s < DISPATCH_UNIT / 32; s++) {
+        const int a = a_lo + s * 32 + lane;
+        const int k = keys[s];
+        const bool ok = k >= 0;
+        const unsigned act = __ballot_sync(0xffffffffu, ok);
+        if (ok) {
+            const unsigned peers = __match_any_sync(act, k);
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            const int dst = h[k] + rank;
+            o.perm[dst] = a;
+            if (o.pos) o.pos[a] = dst;
+            __syncwarp(act);
+            if (rank == 0) h[k] += __popc(peers);
         }
+        __syncwarp();
     }
 }
 
@@ -130,7 +154,9 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
 /* pass 1: per-unit histograms, unit_hist[unit][e] */
 __global__ void __launch_bounds__(DISPATCH_WARPS * 32)
 dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
-                     int32_t *__restrict__ unit_hist, int *status) {
+                     DispatchKey kx, int32_t *__restrict__ unit_hist,
+                     int *status) {
+    pdl_enter();
     extern __shared__ int sm[];   /* [DISPATCH_WARPS][E] */
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int unit = blockIdx.x * DISPATCH_WARPS + warp;
@@ -141,7 +167,7 @@ dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
     if (a_lo < A) {
         const int a_hi = min(A, a_lo + DISPATCH_UNIT);
         for (int a = a_lo + lane; a < a_hi; a += 32) {
-            int k = idx[a];
+            int k = dispatch_key(idx[a], kx);
             if (k < 0 || k >= E) { set_status(status, ST_BAD_INDEX); continue; }
             atomicAdd(&h[k], 1);
         }
@@ -157,16 +183,25 @@ dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
 __global__ void __launch_bounds__(1024)
 dispatch_scan_kernel(int32_t *__restrict__ unit_hist, int n_units, int E,
                      DispatchOut o) {
+    pdl_enter();
     __shared__ int warp_tot[32];
     __shared__ int s_ngroups;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) s_ngroups = 0;
     int total = 0;
     if (tid < E) {
-        for (int u = 0; u < n_units; u++) {
-            int v = unit_hist[(size_t)u * E + tid];
-            unit_hist[(size_t)u * E + tid] = total;
-            total += v;
+        for (int u0 = 0; u0 < n_units; u0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                v[j] = (u0 + j < n_units)
+                           ? unit_hist[(size_t)(u0 + j) * E + tid] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (u0 + j < n_units)
+                    unit_hist[(size_t)(u0 + j) * E + tid] = total;
+                total += v[j];
+            }
         }
     }
     int inc = total;
@@ -202,7 +237,9 @@ dispatch_scan_kernel(int32_t *__restrict__ unit_hist, int n_units, int E,
 /* pass 3: stable placement inside each unit */
 __global__ void __launch_bounds__(DISPATCH_WARPS * 32)
 dispatch_permute_kernel(const int32_t *__restrict__ idx, int A, int E,
-                        const int32_t *__restrict__ unit_hist, DispatchOut o) {
+                        DispatchKey kx, const int32_t *__restrict__ unit_hist,
+                        DispatchOut o) {
+    pdl_enter();
     extern __shared__ int sm[];   /* [DISPATCH_WARPS][E] cursors */
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int unit = blockIdx.x * DISPATCH_WARPS + warp;
@@ -215,7 +252,7 @@ dispatch_permute_kernel(const int32_t *__restrict__ idx, int A, int E,
     const int a_hi = min(A, a_lo + DISPATCH_UNIT);
     for (int a0 = a_lo; a0 < a_hi; a0 += 32) {
         int a = a0 + lane;
-        int k = (a < a_hi) ? idx[a] : -1;
+        int k = (a < a_hi) ? dispatch_key(idx[a], kx) : -1;
         bool ok = (k >= 0 && k < E);
         unsigned act = __ballot_sync(0xffffffffu, ok);
         if (ok) {

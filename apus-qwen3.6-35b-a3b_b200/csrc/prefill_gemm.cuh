@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(1024)
 build_tiles_kernel(const int32_t *__restrict__ counts,
                    const int32_t *__restrict__ offsets, int E, int T, int m_gu,
                    int m_gu_sh, int m_dn, TileLists tl) {
+    pdl_enter();
     __shared__ int warp_tot[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cnt = tid < E ? counts[tid] : 0;
@@ -241,6 +242,7 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint16_t *__restrict__ x,
                    const int32_t *__restrict__ perm, int A, int H, int TK,
                    uint16_t *__restrict__ xg) {
+    pdl_enter();
     const int c8 = H / 8;
     const long total = (long)A * c8;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -276,6 +278,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapB,     /* xg | act */
                     const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
                     GemmParams p) {
+    pdl_enter();
     constexpr int STAGES = GATE_UP ? PG_STAGES_GU : PG_STAGES_DN;
     constexpr int TILES_PER_STAGE = GATE_UP ? 3 : 2;
     constexpr int STAGE_BYTES = TILES_PER_STAGE * PG_TILE_BYTES;
@@ -559,14 +562,14 @@ inline int pg_smem_bytes(bool gate_up) {
  * input; d holds the dispatch results; xg/act/sa/eo/sy are workspace. */
 inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                                const ApusCudaMoeCfg &c, int e_begin,
-                               const uint16_t *x, int T, int A, bool do_shared,
+                               const uint16_t *x, int T, int A, int TK,
+                               bool do_shared,
                                const DispatchOut &d, uint16_t *xg, uint16_t *act,
                                uint16_t *sa, uint16_t *eo, uint16_t *sy,
                                void *tiles_ws, int *status, cudaStream_t st,
                                int *launches, void (*mark)(int stage)) {
     const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
-              E = (int)c.experts, TK = A / (T > 0 ? T : 1);
-    (void)TK;
+              E = (int)c.experts;
     if (!maps) {
         snprintf(g_prefill_err, sizeof g_prefill_err, "tensor maps missing");
         return 1;
@@ -586,7 +589,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     tl.dn = tl.gu + nt * m1;
     tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * m_dn);
     tl.n_dn = tl.n_gu + 1;
-    build_tiles_kernel<<<1, 1024, 0, st>>>(d.counts, d.offsets, E,
+    launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, d.counts, d.offsets, E,
                                            do_shared ? T : 0, m_gu, m_gu_sh, m_dn,
                                            tl);
     (*launches)++;
@@ -595,18 +598,21 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
-        gather_rows_kernel<<<blocks, 256, 0, st>>>(x, d.perm, A, H,
-                                                   A / (T > 0 ? T : 1), xg);
+        launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H,
+                 TK, xg);
         (*launches)++;
     }
     if (mark) mark(APUS_CUDA_STAGE_GATHER);
     /* activation-side tensor maps (buffers move with the workspace) */
     CUtensorMap m_xg, m_x, m_act, m_sa;
     int bad = 0;
-    bad |= encode_2d(maps->encode, &m_xg, xg, (size_t)(A > 0 ? A : 1), H);
-    bad |= encode_2d(maps->encode, &m_x, x, (size_t)T, H);
-    bad |= encode_2d(maps->encode, &m_act, act, (size_t)(A > 0 ? A : 1), I);
-    bad |= encode_2d(maps->encode, &m_sa, sa, (size_t)T, Is);
+    bad |= encode_2d(maps->encode, &m_xg, A > 0 ? (const void *)xg : (const void *)x,
+                     (size_t)(A > 0 ? A : 1), H);
+    bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H);
+    bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
+                     (size_t)(A > 0 ? A : 1), I);
+    bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
+                     (size_t)(do_shared && T > 0 ? T : 1), Is);
     if (bad) return 1;
 
     cudaFuncSetAttribute(grouped_gemm_kernel<true>,
@@ -627,8 +633,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_routed = I;
     p1.ld_shared = Is;
     p1.status = status;
-    grouped_gemm_kernel<true><<<sm_count, PG_THREADS, s1, st>>>(
-        maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
+    launch_k(grouped_gemm_kernel<true>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
     GemmParams p2 = p1;
@@ -647,8 +652,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                  "tensor-core path needs shared_inter == moe_inter");
         return 1;
     }
-    grouped_gemm_kernel<false><<<sm_count, PG_THREADS, s2, st>>>(
-        maps->w_d, maps->sh_d, maps->sh_d, m_act, m_sa, p2);
+    launch_k(grouped_gemm_kernel<false>, dim3(sm_count), dim3(PG_THREADS), s2, st, maps->w_d, maps->sh_d, maps->sh_d, m_act, m_sa, p2);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_DOWN);
     cudaError_t e = cudaGetLastError();

@@ -114,28 +114,31 @@ __device__ __forceinline__ void router_softmax_topk(float *p, int E, int topk,
     for (int e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], s);
     __syncwarp();
 
+    /* Selection.  Probabilities are non-negative, so their fp32 bit patterns
+     * order like unsigned integers.  Each round: the warp-wide maximum
+     * pattern (one redux), then the lowest index holding it (a second redux)
+     * -- the strict '>' scan from -inf of the CPU loop, which keeps the lowest
+     * index on ties.  A selected entry is overwritten with -inf (negative as
+     * an integer) and can never win again. */
     int my_e = 0;
     float my_p = 0.0f;
     for (int i = 0; i < topk; i++) {
-        float bv = -INFINITY;
-        int be = 0x7fffffff;
+        int bb = -1, be = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            float v = p[e];
-            if (v > bv) { bv = v; be = e; }
+            const int v = __float_as_int(p[e]);
+            if (v > bb) { bb = v; be = e; }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        const int wb = __reduce_max_sync(0xffffffffu, bb);
+        int we;
+        if (wb < 0) {          /* nothing left above -inf: CPU leaves best = 0 */
+            we = 0;
+        } else {
+            we = (int)__reduce_min_sync(0xffffffffu,
+                                        bb == wb ? (unsigned)be : 0x7fffffffu);
         }
-        if (be == 0x7fffffff) {   /* nothing left above -inf: the CPU loop
-                                   * leaves best = 0 */
-            be = 0;
-            bv = p[0];
-        }
-        if (lane == i) { my_e = be; my_p = bv; }
-        if (lane == (be & 31)) p[be] = -INFINITY;
+        const float wp = wb < 0 ? p[0] : __int_as_float(wb);
+        if (lane == i) { my_e = we; my_p = wp; }
+        if (lane == (we & 31)) p[we] = -INFINITY;
         __syncwarp();
     }
     if (w_out) {
@@ -168,6 +171,7 @@ router_topk_kernel(const uint16_t *__restrict__ x,
                    uint16_t *__restrict__ logits_out,
                    const uint16_t *__restrict__ extra_row,
                    uint16_t *__restrict__ extra_out) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float *xs = reinterpret_cast<float *>(smem_raw);
     float *ps = xs + (size_t)TT * K;
@@ -260,6 +264,7 @@ router_small_kernel(const uint16_t *__restrict__ x,
                     float *__restrict__ logits_ws,     /* [T][E] fp32 */
                     unsigned int *__restrict__ counters, /* [T], zero between calls */
                     int *status) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int pitch = K * 2 + 16;                 /* bytes; de-conflicts banks */
     unsigned char *rows_s = smem_raw;
@@ -287,11 +292,20 @@ router_small_kernel(const uint16_t *__restrict__ x,
         }
     }
     unsigned int xmin = 0x7f800000u;
-    for (int k = lane; k < K; k += 32) {
-        uint16_t c = x[(size_t)t * K + k];
-        xs[k] = bf16_f32(c);
-        unsigned int a = ((unsigned int)c << 16) & 0x7fffffffu;
-        if (a != 0 && a < xmin) xmin = a;
+#pragma unroll 4
+    for (int c = lane; c < K / 8; c += 32) {
+        const uint4 v = ldg16(x + (size_t)t * K + (size_t)c * 8);
+        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+        float4 *d = reinterpret_cast<float4 *>(xs + c * 8);
+        d[0] = make_float4(bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y));
+        d[1] = make_float4(bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w));
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            unsigned int a = (wds[q] << 16) & 0x7fffffffu;
+            unsigned int b = wds[q] & 0x7fff0000u;
+            if (a != 0 && a < xmin) xmin = a;
+            if (b != 0 && b < xmin) xmin = b;
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -307,10 +321,28 @@ router_small_kernel(const uint16_t *__restrict__ x,
             reinterpret_cast<const uint16_t *>(rows_s + (size_t)lane * pitch);
         float acc = 0.0f;
         const bool fma_row = use_fma && (r0 + lane != E);
+        /* The chain is the critical path (one dependent FMA per k); the
+         * operands of the next two 8-wide pieces are fetched from shared
+         * memory while the current piece's FMAs retire. */
+        uint4 wv0 = *reinterpret_cast<const uint4 *>(wrow);
+        float4 xa0 = *reinterpret_cast<const float4 *>(xs);
+        float4 xb0 = *reinterpret_cast<const float4 *>(xs + 4);
+        uint4 wv1 = wv0;
+        float4 xa1 = xa0, xb1 = xb0;
+        if (K > 8) {
+            wv1 = *reinterpret_cast<const uint4 *>(wrow + 8);
+            xa1 = *reinterpret_cast<const float4 *>(xs + 8);
+            xb1 = *reinterpret_cast<const float4 *>(xs + 12);
+        }
         for (int k = 0; k < K; k += 8) {
-            const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + k);
-            const float4 xa = *reinterpret_cast<const float4 *>(xs + k);
-            const float4 xb = *reinterpret_cast<const float4 *>(xs + k + 4);
+            const uint4 wv = wv0;
+            const float4 xa = xa0, xb = xb0;
+            wv0 = wv1; xa0 = xa1; xb0 = xb1;
+            if (k + 16 < K) {
+                wv1 = *reinterpret_cast<const uint4 *>(wrow + k + 16);
+                xa1 = *reinterpret_cast<const float4 *>(xs + k + 16);
+                xb1 = *reinterpret_cast<const float4 *>(xs + k + 20);
+            }
             const float wf[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y),
                                  bf16hi(wv.y), bf16lo(wv.z), bf16hi(wv.z),
                                  bf16lo(wv.w), bf16hi(wv.w)};
@@ -351,41 +383,58 @@ router_small_kernel(const uint16_t *__restrict__ x,
 /*
  * Throughput path for many tokens, in two kernels.
  *
- * router_logits_kernel<TT>: grid = (ceil(T/TT), E/256), block = 288.  A CTA
- * scores 256 experts against TT tokens.  The router matrix streams through a
- * three-stage shared-memory ring of [256 rows x 64 k] tiles loaded by TMA
- * (128-byte swizzle, no multicast), the token tile is converted to fp32 in
- * the same ring, and thread e walks TT exact chains for expert row e with one
- * 16-byte swizzled shared load per eight k.  Lanes 0..TT-1 of the ninth warp
- * score the optional extra row (the shared expert's gate) the same way.
- * BF16 logits go to logits_out [T, E].  Requires E % 256 == 0, K % 64 == 0.
+ * router_logits_kernel<TT, ROWS>: grid = (ceil(T/TT), E/ROWS), block = ROWS+32.
+ * A CTA scores ROWS experts (128 or 256) against TT tokens (8, 16 or 32).
+ * Its slice of the router matrix streams through a three-stage shared-memory
+ * ring of [ROWS x 64 k] tiles loaded by TMA (128-byte swizzle, no multicast);
+ * the token tile's k-slice rides in the same ring as fp32.
+ *
+ * Shared memory serves one 128-byte wavefront per cycle whether or not the
+ * lanes of a load want the same address, so a thread that owned one expert
+ * and read every token's x by broadcast would spend four wavefronts per four
+ * FMAs.  Instead each thread owns a 4-expert x (TT/4)-token register tile
+ * (lane = 8 expert groups x 4 token groups): per eight k it loads 4 weight
+ * vectors and TT/4 x vectors and issues 32*(TT/4) FMAs, every chain still
+ * strictly ascending in k.  Every token tile re-reads the whole router matrix
+ * from L2, so TT also sets the L2 traffic (T/TT MiB at the real dims): the host
+ * picks the largest TT that still fills the SMs.  Lanes 0..TT-1 of the last
+ * warp score the optional extra row (the shared expert's gate).  BF16 logits
+ * go to logits_out [T, E].  Requires E % ROWS == 0, K % 64 == 0.
  *
  * router_select_kernel: one warp per token turns the logits into ids and
  * weights (router_softmax_topk).
  */
 constexpr int RL_STAGES = 3;
-constexpr int RL_ROWS = 256;
 constexpr int RL_BK = 64;
+constexpr int RL_XPITCH = RL_BK + 4;   /* floats; keeps 4 token groups on
+                                        * different banks */
 
-template <int TT>
-__global__ void __launch_bounds__(ROUTER_THREADS)
+template <int TT, int ROWS>
+__global__ void __launch_bounds__(ROWS + 32)
 router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box {64,128} */
                      const uint16_t *__restrict__ x, int T, int E, int K,
                      float wmin, uint16_t *__restrict__ logits_out,
                      const uint16_t *__restrict__ extra_row,
                      uint16_t *__restrict__ extra_out, int *status) {
+    pdl_enter();
+    static_assert(TT <= 32 && TT % 4 == 0, "token tile");
+    constexpr int THREADS = ROWS + 32;
+    constexpr int TPT = TT / 4;          /* tokens per thread */
+    constexpr int EPT = 4;               /* experts per thread */
+    /* ROWS experts / (8 expert groups * EPT) warps do the chains */
+    constexpr int CHAIN_WARPS = ROWS / 32;
     extern __shared__ unsigned char rl_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(rl_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int W_BYTES = RL_ROWS * RL_BK * 2;           /* 32 KB */
-    constexpr int X_BYTES = TT * RL_BK * 4;
+    constexpr int W_BYTES = ROWS * RL_BK * 2;
+    constexpr int X_BYTES = TT * RL_XPITCH * 4;
     constexpr int STAGE = W_BYTES + ((X_BYTES + 1023) & ~1023);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + RL_STAGES * STAGE);
     __shared__ unsigned int s_xmin;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t0 = blockIdx.x * TT;
-    const int e0 = blockIdx.y * RL_ROWS;
+    const int e0 = blockIdx.y * ROWS;
     const int nkb = K / RL_BK;
     if (tid == 0) {
         for (int s = 0; s < RL_STAGES; s++) mbar_init(&full[s], 1);
@@ -398,33 +447,34 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         const int s = kb % RL_STAGES;
         unsigned char *st = smem + (size_t)s * STAGE;
         mbar_expect_tx(&full[s], W_BYTES);
-        tma_load_2d_rl(st, &map_w, kb * RL_BK, e0, &full[s]);
-        tma_load_2d_rl(st + W_BYTES / 2, &map_w, kb * RL_BK, e0 + 128, &full[s]);
+#pragma unroll
+        for (int b = 0; b < ROWS / 128; b++)
+            tma_load_2d_rl(st + b * 16384, &map_w, kb * RL_BK, e0 + b * 128,
+                           &full[s]);
     };
-    /* The token tile's k-slice for a stage: each thread fetches up to two
-     * elements into registers (x_fetch) early, so the global-load latency
-     * hides behind the chains, and drops them into the stage afterwards
-     * (x_store). */
-    constexpr int XE = TT * RL_BK;                 /* elements per stage */
-    static_assert(XE <= 2 * ROUTER_THREADS, "token tile too large");
-    uint16_t xr0 = 0, xr1 = 0;
+    /* The token tile's k-slice for a stage: a thread fetches one 16-byte
+     * piece into registers early (x_fetch), so the global-load latency hides
+     * behind the chains, and widens it into the stage afterwards (x_store). */
+    constexpr int XV = TT * RL_BK / 8;             /* 16-byte pieces per stage */
+    static_assert(XV <= THREADS, "token tile too large for one piece per thread");
+    uint4 xr = make_uint4(0, 0, 0, 0);
     auto x_fetch = [&](int kb) {
-        const int i0 = tid, i1 = tid + ROUTER_THREADS;
-        xr0 = 0; xr1 = 0;
-        if (i0 < XE) {
-            const int t = i0 / RL_BK, j = i0 - t * RL_BK;
-            if (t0 + t < T) xr0 = __ldg(x + (size_t)(t0 + t) * K + kb * RL_BK + j);
-        }
-        if (i1 < XE) {
-            const int t = i1 / RL_BK, j = i1 - t * RL_BK;
-            if (t0 + t < T) xr1 = __ldg(x + (size_t)(t0 + t) * K + kb * RL_BK + j);
+        xr = make_uint4(0, 0, 0, 0);
+        if (tid < XV) {
+            const int t = tid >> 3, j = tid & 7;
+            if (t0 + t < T)
+                xr = ldg16(x + (size_t)(t0 + t) * K + kb * RL_BK + j * 8);
         }
     };
     auto x_store = [&](int kb) {
-        const int s = kb % RL_STAGES;
-        float *xs = reinterpret_cast<float *>(smem + (size_t)s * STAGE + W_BYTES);
-        if (tid < XE) xs[tid] = bf16_f32(xr0);
-        if (tid + ROUTER_THREADS < XE) xs[tid + ROUTER_THREADS] = bf16_f32(xr1);
+        if (tid < XV) {
+            const int s = kb % RL_STAGES;
+            float *xs = reinterpret_cast<float *>(smem + (size_t)s * STAGE + W_BYTES);
+            float4 *d = reinterpret_cast<float4 *>(xs + (tid >> 3) * RL_XPITCH +
+                                                   (tid & 7) * 8);
+            d[0] = make_float4(bf16lo(xr.x), bf16hi(xr.x), bf16lo(xr.y), bf16hi(xr.y));
+            d[1] = make_float4(bf16lo(xr.z), bf16hi(xr.z), bf16lo(xr.w), bf16hi(xr.w));
+        }
     };
     if (tid == 0)
         for (int kb = 0; kb < RL_STAGES && kb < nkb; kb++) issue(kb);
@@ -435,7 +485,7 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
 
     /* smallest nonzero |x| of the token tile (FMA-exactness guard) */
     unsigned int xmin = 0x7f800000u;
-    for (int i = tid; i < TT * (K / 8); i += ROUTER_THREADS) {
+    for (int i = tid; i < TT * (K / 8); i += THREADS) {
         const int t = i / (K / 8), c = i - t * (K / 8);
         if (t0 + t < T) {
             const uint4 v = ldg16(x + (size_t)(t0 + t) * K + (size_t)c * 8);
@@ -458,11 +508,18 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         (wmin > 0.0f) &&
         ((double)wmin * (double)__uint_as_float(s_xmin) >= 7.52316384526264e-37);
 
-    float acc[TT];
+    /* register tile: experts er0..er0+3 (rows inside the CTA's slice), tokens
+     * tg, tg+4, tg+8, ... */
+    float acc[EPT][TPT];
 #pragma unroll
-    for (int t = 0; t < TT; t++) acc[t] = 0.0f;
-    const bool is_expert = tid < RL_ROWS;
-    const bool is_extra = extra_row && blockIdx.y == 0 && warp == RL_ROWS / 32 &&
+    for (int i = 0; i < EPT; i++)
+#pragma unroll
+        for (int j = 0; j < TPT; j++) acc[i][j] = 0.0f;
+    float acc_extra = 0.0f;
+    const bool is_chain = warp < CHAIN_WARPS;
+    const int er0 = warp * 32 + (lane >> 2) * EPT;
+    const int tg = lane & 3;
+    const bool is_extra = extra_row && blockIdx.y == 0 && warp == CHAIN_WARPS &&
                           lane < TT;
     bool ok = true;
     for (int kb = 0; kb < nkb; kb++) {
@@ -474,42 +531,51 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         }
         const unsigned char *st = smem + (size_t)s * STAGE;
         const float *xs = reinterpret_cast<const float *>(st + W_BYTES);
-        if (ok && is_expert) {
-            const unsigned char *wrow =
-                st + (tid >> 7) * (W_BYTES / 2) + (tid & 127) * 128;
+        if (ok && is_chain) {
 #pragma unroll 2
             for (int c = 0; c < 8; c++) {
-                const uint4 wv = *reinterpret_cast<const uint4 *>(
-                    wrow + ((c ^ (tid & 7)) << 4));
-                const float wf[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y),
-                                     bf16hi(wv.y), bf16lo(wv.z), bf16hi(wv.z),
-                                     bf16lo(wv.w), bf16hi(wv.w)};
+                float wf[EPT][8];
 #pragma unroll
-                for (int t = 0; t < TT; t++) {
-                    const float4 xa = *reinterpret_cast<const float4 *>(
-                        xs + t * RL_BK + c * 8);
-                    const float4 xb = *reinterpret_cast<const float4 *>(
-                        xs + t * RL_BK + c * 8 + 4);
+                for (int i = 0; i < EPT; i++) {
+                    const int r = er0 + i;
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(
+                        st + (r >> 7) * 16384 + (r & 127) * 128 +
+                        ((c ^ (r & 7)) << 4));
+                    wf[i][0] = bf16lo(wv.x); wf[i][1] = bf16hi(wv.x);
+                    wf[i][2] = bf16lo(wv.y); wf[i][3] = bf16hi(wv.y);
+                    wf[i][4] = bf16lo(wv.z); wf[i][5] = bf16hi(wv.z);
+                    wf[i][6] = bf16lo(wv.w); wf[i][7] = bf16hi(wv.w);
+                }
+#pragma unroll
+                for (int j = 0; j < TPT; j++) {
+                    const float *xp = xs + (j * 4 + tg) * RL_XPITCH + c * 8;
+                    const float4 xa = *reinterpret_cast<const float4 *>(xp);
+                    const float4 xb = *reinterpret_cast<const float4 *>(xp + 4);
                     const float xf[8] = {xa.x, xa.y, xa.z, xa.w,
                                          xb.x, xb.y, xb.z, xb.w};
                     if (use_fma) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            acc[t] = __fmaf_rn(wf[j], xf[j], acc[t]);
+                        for (int kk = 0; kk < 8; kk++)
+#pragma unroll
+                            for (int i = 0; i < EPT; i++)
+                                acc[i][j] = __fmaf_rn(wf[i][kk], xf[kk], acc[i][j]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            acc[t] = __fadd_rn(acc[t], __fmul_rn(wf[j], xf[j]));
+                        for (int kk = 0; kk < 8; kk++)
+#pragma unroll
+                            for (int i = 0; i < EPT; i++)
+                                acc[i][j] = __fadd_rn(
+                                    acc[i][j], __fmul_rn(wf[i][kk], xf[kk]));
                     }
                 }
             }
         } else if (ok && is_extra) {
             /* lane t: the extra row against token t (literal chain) */
-            float a = acc[0];
+            float a = acc_extra;
             for (int j = 0; j < RL_BK; j++)
                 a = __fadd_rn(a, __fmul_rn(bf16_f32(__ldg(extra_row + kb * RL_BK + j)),
-                                           xs[lane * RL_BK + j]));
-            acc[0] = a;
+                                           xs[lane * RL_XPITCH + j]));
+            acc_extra = a;
         }
         __syncthreads();            /* everyone is done with stage s */
         if (kb + RL_STAGES < nkb) {
@@ -518,13 +584,20 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         }
     }
     if (!ok) return;
-    if (is_expert) {
+    if (is_chain) {
 #pragma unroll
-        for (int t = 0; t < TT; t++)
-            if (t0 + t < T)
-                logits_out[(size_t)(t0 + t) * E + e0 + tid] = bf16_bits(acc[t]);
+        for (int j = 0; j < TPT; j++) {
+            const int t = t0 + j * 4 + tg;
+            if (t < T) {
+                /* four consecutive experts: one 8-byte store */
+                uint2 v;
+                v.x = pack_bf16(acc[0][j], acc[1][j]);
+                v.y = pack_bf16(acc[2][j], acc[3][j]);
+                *reinterpret_cast<uint2 *>(logits_out + (size_t)t * E + e0 + er0) = v;
+            }
+        }
     } else if (is_extra) {
-        if (t0 + lane < T) extra_out[t0 + lane] = bf16_bits(acc[0]);
+        if (t0 + lane < T) extra_out[t0 + lane] = bf16_bits(acc_extra);
     }
 }
 
@@ -532,6 +605,7 @@ __global__ void __launch_bounds__(256)
 router_select_kernel(const uint16_t *__restrict__ logits, int T, int E,
                      int topk, int32_t *__restrict__ idx_out,
                      uint16_t *__restrict__ w_out) {
+    pdl_enter();
     extern __shared__ float sel_smem[];   /* [8][E] */
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 8 + warp;

@@ -1,0 +1,111 @@
+"""Expert-parallel MoE block: one process per GPU, experts [r*E/N, (r+1)*E/N)
+resident on rank r, tokens data-parallel, two all-to-alls per block.
+
+The reference engine is a single process; what is mirrored here is only the
+math of its batched MoE body (c/layer.h:570-651).  The compute steps are the
+C entry points apus_cuda_ep_route_dev / _ep_pack_dev / _experts_dev /
+_ep_finish_dev; this module adds the exchange with torch.distributed
+(all_to_all_single over NCCL on GPUs, over gloo in the CPU tests).
+
+`ops` is the object that provides those four steps on torch tensors; the
+product implementation is CudaOps below.  (Tests drive the same exchange logic
+over gloo with a CPU stand-in for `ops`.)
+"""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def split_sizes(counts):
+    """all_to_all_single split lists from a per-destination count vector."""
+    return [int(c) for c in counts]
+
+
+class EPBlock:
+    def __init__(self, ops, cfg, rank, world, group=None):
+        assert cfg["experts"] % world == 0
+        self.ops, self.cfg, self.rank, self.world = ops, cfg, rank, world
+        self.group = group
+        self.last_sent_rows = 0
+        self.last_recv_rows = 0
+
+    def forward(self, x):
+        """x: [T_local, H] int16 tensor of BF16 codes on the ops' device.
+        Returns [T_local, H]."""
+        cfg, N = self.cfg, self.world
+        T, H = x.shape
+        TK, E = cfg["top_k"], cfg["experts"]
+        idx, w, sgl = self.ops.route(x)
+        send_x, send_e, send_counts, pos = self.ops.pack(x, idx, N)
+        # counts exchange (tiny), then rows + expert ids
+        sc = send_counts.to(torch.int64)
+        rc = torch.empty_like(sc)
+        dist.all_to_all_single(rc, sc, group=self.group)
+        in_splits = split_sizes(sc.cpu().numpy())
+        out_splits = split_sizes(rc.cpu().numpy())
+        R = sum(out_splits)
+        recv_x = x.new_empty((R, H))
+        recv_e = send_e.new_empty((R,))
+        # rows travel as bytes: 16-bit integer tensors are not a collective
+        # datatype in NCCL or gloo
+        dist.all_to_all_single(recv_x.view(torch.uint8), send_x.view(torch.uint8),
+                               out_splits, in_splits, group=self.group)
+        dist.all_to_all_single(recv_e, send_e, out_splits, in_splits,
+                               group=self.group)
+        recv_y = self.ops.experts(recv_x, recv_e)
+        back_y = x.new_empty((T * TK, H))
+        dist.all_to_all_single(back_y.view(torch.uint8),
+                               recv_y.view(torch.uint8), in_splits, out_splits,
+                               group=self.group)
+        self.last_sent_rows = T * TK - in_splits[self.rank]
+        self.last_recv_rows = R - out_splits[self.rank]
+        return self.ops.finish(x, back_y, pos, w, sgl)
+
+
+class CudaOps:
+    """The four compute steps on CUDA tensors through the C-ABI."""
+
+    def __init__(self, be, layer, cfg):
+        self.be, self.layer, self.cfg = be, layer, cfg
+
+    def _s(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def route(self, x):
+        T = x.shape[0]
+        TK = self.cfg["top_k"]
+        idx = torch.empty((T, TK), dtype=torch.int32, device=x.device)
+        w = torch.empty((T, TK), dtype=torch.int16, device=x.device)
+        sgl = torch.empty((T,), dtype=torch.int16, device=x.device)
+        self.be.ep_route_dev(self.layer, x.data_ptr(), T, idx.data_ptr(),
+                             w.data_ptr(), sgl.data_ptr(), stream=self._s())
+        return idx, w, sgl
+
+    def pack(self, x, idx, n_ranks):
+        T, H = x.shape
+        TK, E = self.cfg["top_k"], self.cfg["experts"]
+        A = T * TK
+        send_x = torch.empty((A, H), dtype=torch.int16, device=x.device)
+        send_e = torch.empty((A,), dtype=torch.int32, device=x.device)
+        counts = torch.empty((n_ranks,), dtype=torch.int32, device=x.device)
+        pos = torch.empty((A,), dtype=torch.int32, device=x.device)
+        self.be.ep_pack_dev(x.data_ptr(), idx.data_ptr(), T, TK, H, E, n_ranks,
+                            send_x.data_ptr(), send_e.data_ptr(),
+                            counts.data_ptr(), pos.data_ptr(), stream=self._s())
+        return send_x, send_e, counts, pos
+
+    def experts(self, rx, re):
+        R, H = rx.shape
+        y = torch.empty((R, H), dtype=torch.int16, device=rx.device)
+        if R:
+            self.be.experts_dev(self.layer, rx.data_ptr(), re.data_ptr(), R,
+                                y.data_ptr(), stream=self._s())
+        return y
+
+    def finish(self, x, y_sorted, pos, w, sgl):
+        T, H = x.shape
+        out = torch.empty_like(x)
+        self.be.ep_finish_dev(self.layer, x.data_ptr(), T, y_sorted.data_ptr(),
+                              pos.data_ptr(), w.data_ptr(), sgl.data_ptr(),
+                              out.data_ptr(), stream=self._s())
+        return out

@@ -1,0 +1,105 @@
+"""bench.py's multi-GPU arm: the expert-parallel block over NCCL, one process
+per GPU (launched by torch.distributed.run)."""
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def run(args, cfg, config, pkg, synth, metric, unit, peaks):
+    from . import ep
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("APUS_CUDA_DEVICE", str(local))
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", local))
+    be = pkg.Backend()
+    be.enable()
+    H, E = cfg["hidden"], cfg["experts"]
+    T = args.tokens                      # tokens per rank (weak scaling)
+    per = E // world
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    sp = stream.cuda_stream
+    # this rank's experts, generated in place in HBM
+    layer = be.layer_create(cfg, None, rank * per, (rank + 1) * per)
+    synth.device_weights(be, layer, cfg, seed=args.seed, layer=0,
+                         expert_begin=rank * per, stream=sp)
+    x_all = synth.host_x(be, T * world, H, seed=args.seed)
+    x_host = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
+    d_x = torch.from_numpy(x_host).cuda()
+    blk = ep.EPBlock(ep.CudaOps(be, layer, cfg), cfg, rank, world)
+
+    def step():
+        return blk.forward(d_x)
+
+    out = step()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    l0 = be.launches()
+    e0.record(stream)
+    for _ in range(args.steps):
+        out = step()
+    e1.record(stream)
+    launches = torch.tensor([float(be.launches() - l0)], device="cuda")
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    status = be.last_block_status()
+
+    # end to end: pinned host input -> device, block, result back to host
+    xin = torch.from_numpy(x_host).pin_memory()
+    hout = torch.empty_like(xin).pin_memory()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        d_x.copy_(xin, non_blocking=True)
+        o = step()
+        hout.copy_(o, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps],
+                       device="cuda")
+    dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e.item())
+    rows = torch.tensor([blk.last_sent_rows, blk.last_recv_rows],
+                        dtype=torch.float64, device="cuda")
+    dist.all_reduce(rows, op=dist.ReduceOp.SUM)
+    dist.all_reduce(launches, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        Tg = T * world
+        cfgline = dict(config)
+        cfgline["workload"] = (f"one MoE layer, expert-parallel over {world} "
+                               f"GPUs ({per} experts per GPU), {T} tokens per "
+                               f"GPU, uniform router, seed {args.seed}")
+        cfgline["tokens_per_step"] = Tg
+        cfgline["parallelism"] = f"ep{world}"
+        cfgline["launch"] = "host launches"
+        line = {
+            "metric": metric, "value": Tg / (ms * 1e-3), "unit": unit,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 storage, fp32 accumulate",
+            "data": "synthetic", "config": cfgline,
+            "e2e": {"value": Tg / (e2e_ms * 1e-3), "unit": unit,
+                    "h2d_bytes_per_step": Tg * H * 2,
+                    "d2h_bytes_per_step": Tg * H * 2, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches.item()),
+            "exchange": {"rows_sent_per_step": float(rows[0]),
+                         "bytes_each_way_per_step": float(rows[0]) * H * 2,
+                         "collective": "all_to_all_single (NCCL), rows as bytes"},
+            "block": {"device_status": status},
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()

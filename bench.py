@@ -158,6 +158,9 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every step from the host instead of "
+                         "replaying a captured CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -227,6 +230,24 @@ def main():
     uniq = int(torch.unique(d_idx).numel())
     launches_per_step = be.last_block_launches()
 
+    # one block call captured into a CUDA graph: the replay is what a serving
+    # loop would issue per layer (no per-launch host work)
+    launch_mode = "host launches"
+    if not args.no_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T,
+                                 stream=torch.cuda.current_stream().cuda_stream)
+            direct = step
+            step = g.replay
+            launch_mode = "cuda graph replay"
+        except Exception as e:          # capture unsupported: say so, go on
+            launch_mode = f"host launches (graph capture failed: {e})"
+            torch.cuda.synchronize()
+    config["launch"] = launch_mode
+
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -243,6 +264,8 @@ def main():
     status = be.last_block_status()
 
     # per-stage times, measured live with CUDA events on the launching stream
+    if launch_mode.startswith("cuda graph"):
+        step = direct
     be.stage_timing(True)
     acc = {}
     for _ in range(args.steps):

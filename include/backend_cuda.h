@@ -223,6 +223,55 @@ int apus_cuda_last_stage_ms(float *ms, int cap);
  * bounded wait inside a kernel gave up (the context stays usable). */
 int apus_cuda_last_block_status(void);
 
+/* ---- expert parallelism -----------------------------------------------------
+ * Net-new: the reference engine is one process (no counterpart beyond the
+ * math of c/layer.h:570-651).  A rank holds experts [begin, end) of every
+ * layer (apus_cuda_layer_create) plus the replicated router, shared expert and
+ * shared gate, and owns a slice of the tokens.  One block step on a rank:
+ *
+ *   1. apus_cuda_ep_route_dev   router on the rank's tokens -> idx, w, sgl
+ *   2. apus_cuda_ep_pack_dev    stable sort of the T*topk assignments by
+ *                               owning rank; packs the rows to send
+ *   3. all-to-all of (row, expert id) — the caller's collective (NCCL)
+ *   4. apus_cuda_experts_dev    the resident experts on the received rows
+ *   5. all-to-all of the BF16 expert outputs back — the caller's collective
+ *   6. apus_cuda_ep_finish_dev  shared expert on the rank's tokens, weighted
+ *                               combine in slot order, gate, add
+ *
+ * Every assignment's expert output is rounded to BF16 exactly where the
+ * single-GPU block rounds it, and step 6 combines in the same slot order, so
+ * the result equals apus_cuda_moe_block_dev bit for bit at any rank count.
+ * All pointers are device pointers; calls enqueue on `stream` and do not
+ * synchronise. */
+
+/* d_x [T,H] -> d_idx [T,topk], d_w [T,topk] BF16, d_sgl [T] BF16 (the shared
+ * gate logit, c/layer.h:355). */
+int apus_cuda_ep_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
+                           int32_t *d_idx, uint16_t *d_w, uint16_t *d_sgl,
+                           void *stream);
+/* Owner of expert e is e / (E / n_ranks).  Outputs, all in send order p (rank
+ * 0's rows first, inside a rank by token then slot): d_send_x [T*topk, H] (the
+ * token row of assignment p), d_send_e [T*topk] (its global expert id),
+ * d_send_counts [n_ranks], d_pos [T*topk] (send position of flat assignment
+ * t*topk + j). */
+int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx, size_t T,
+                          size_t topk, size_t H, size_t E, size_t n_ranks,
+                          uint16_t *d_send_x, int32_t *d_send_e,
+                          int32_t *d_send_counts, int32_t *d_pos, void *stream);
+/* d_y[r] = rnd(Wd[e_r] . act(Wgu[e_r] . d_x[r])) for R rows, e_r = d_e[r] a
+ * global id inside the layer's resident range (c/layer.h:346-348 per row).
+ * R == 0 is a no-op. */
+int apus_cuda_experts_dev(ApusCudaLayer *layer, const uint16_t *d_x,
+                          const int32_t *d_e, size_t R, uint16_t *d_y,
+                          void *stream);
+/* d_y_sorted [T*topk, H]: expert outputs in send order; d_pos from step 2;
+ * d_w, d_sgl from step 1.  Writes d_out [T,H] (and the trace rows). */
+int apus_cuda_ep_finish_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
+                            const uint16_t *d_y_sorted, const int32_t *d_pos,
+                            const uint16_t *d_w, const uint16_t *d_sgl,
+                            uint16_t *d_out, const ApusCudaMoeTrace *d_tr,
+                            void *stream);
+
 /* ---- stages of the block, device pointers (kernel-level tests) ---------- */
 int apus_cuda_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
                         int32_t *d_idx, uint16_t *d_w, void *stream);

@@ -1,0 +1,105 @@
+"""Expert-parallel entry points on one GPU: N ranks emulated in one process
+(each with its own partial layer; the two all-to-alls done by slicing), and
+the real torch.distributed path at world size 1.  The result must equal the
+single-GPU block bit for bit."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def emulate(be, ep, torch, cfg, W, x, N):
+    T, H = x.shape
+    per, E, TK = T // N, cfg["experts"], cfg["top_k"]
+    layers = [be.layer_create(cfg, W, r * E // N, (r + 1) * E // N)
+              for r in range(N)]
+    ops = [ep.CudaOps(be, layers[r], cfg) for r in range(N)]
+    xs = [torch.from_numpy(x[r * per:(r + 1) * per].view(np.int16).copy()).cuda()
+          for r in range(N)]
+    routed = [ops[r].route(xs[r]) for r in range(N)]
+    packed = [ops[r].pack(xs[r], routed[r][0], N) for r in range(N)]
+    torch.cuda.synchronize()
+    counts = [p[2].cpu().numpy() for p in packed]          # [src][dst]
+    offs = [np.concatenate([[0], np.cumsum(c)]) for c in counts]
+    back = [torch.empty((per * TK, H), dtype=torch.int16, device="cuda")
+            for _ in range(N)]
+    for dst in range(N):
+        rx = torch.cat([packed[src][0][offs[src][dst]:offs[src][dst + 1]]
+                        for src in range(N)])
+        re = torch.cat([packed[src][1][offs[src][dst]:offs[src][dst + 1]]
+                        for src in range(N)])
+        assert int(re.min()) >= dst * E // N and int(re.max()) < (dst + 1) * E // N
+        y = ops[dst].experts(rx, re)
+        o = 0
+        for src in range(N):
+            n = counts[src][dst]
+            back[src][offs[src][dst]:offs[src][dst + 1]] = y[o:o + n]
+            o += n
+    outs = [ops[r].finish(xs[r], back[r], packed[r][3], routed[r][1],
+                          routed[r][2]) for r in range(N)]
+    torch.cuda.synchronize()
+    assert be.last_block_status() == 0
+    out = np.concatenate([o.cpu().numpy().view(np.uint16) for o in outs])
+    for l in layers:
+        be.layer_destroy(l)
+    return out
+
+
+@pytest.mark.parametrize("path", ["gemm", "gemv"])
+@pytest.mark.parametrize("N,T", [(2, 20), (2, 200), (4, 400), (8, 1024)])
+def test_ep_emulated_ranks_equal_single_gpu(be, synth, N, T, path, monkeypatch):
+    """With both sides pinned to the same expert kernels (a row's result does
+    not depend on which other rows share its tile or group), the N-rank result
+    is the single-GPU result bit for bit."""
+    import torch
+    from apus_b200 import ep
+    monkeypatch.setenv("APUS_CUDA_DECODE_MAX_T",
+                       "0" if path == "gemm" else "1000000")
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
+        x = synth.host_x(be, T, cfg["hidden"], seed=13)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        got = emulate(be, ep, torch, cfg, W, x, N)
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
+
+
+def test_ep_matches_checker(gpu, orc, be, synth):
+    import torch
+    from apus_b200 import ep
+    cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128, top_k=8)
+    W = synth.host_weights(be, cfg, seed=14, sigma=0.05)
+    x = synth.host_x(be, 96, cfg["hidden"], seed=14)
+    got = emulate(be, ep, torch, cfg, W, x, 2)
+    exp = orc.moe_block(cfg, W, x)["out"]
+    a, b = synth.bf16_to_f32(got), synth.bf16_to_f32(exp)
+    assert np.abs(a - b).max() <= 2e-2
+    assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 1e-2
+
+
+def test_ep_world_size_one_process_group(gpu, be, synth):
+    """The torch.distributed path itself (NCCL, one rank)."""
+    import torch
+    import torch.distributed as dist
+    from apus_b200 import ep
+    cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128, top_k=8)
+    W = synth.host_weights(be, cfg, seed=15, sigma=0.05)
+    x = synth.host_x(be, 150, cfg["hidden"], seed=15)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(29700 + os.getpid() % 1000))
+    dist.init_process_group("nccl", rank=0, world_size=1)
+    try:
+        layer = be.layer_create(cfg, W)
+        blk = ep.EPBlock(ep.CudaOps(be, layer, cfg), cfg, 0, 1)
+        out = blk.forward(torch.from_numpy(x.view(np.int16).copy()).cuda())
+        torch.cuda.synchronize()
+        whole = gpu.moe_block(cfg, W, x, trace=False)["out"]
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), whole)
+    finally:
+        dist.destroy_process_group()
