@@ -712,6 +712,8 @@ extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
     if (!L) return fail("null layer");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
+    /* set-up call: whatever stream filled the tensor, wait for it */
+    CU_OK(cudaDeviceSynchronize());
     return min_nonzero(g_ctx, L->rtr_w, L->cfg.experts * L->cfg.hidden,
                        &L->wmin, g_ctx->stream);
 }
@@ -940,7 +942,7 @@ extern "C" int apus_cuda_moe_block_dev(ApusCudaLayer *layer,
     if (!layer || !d_ln2 || !d_out || !T) return fail("moe_block_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     if (layer->maps == nullptr && prefill_supported(layer->cfg) &&
         (int)T > g_ctx->decode_max_t) {
         layer->maps = prefill_maps_create(layer->cfg, layer->exp_gu,
@@ -1077,7 +1079,7 @@ extern "C" int apus_cuda_ep_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     const size_t E = L->cfg.experts;
     if (arena_reserve(c->ws, T * E * 2 + 4096)) return 1;
     c->ws.reset();
@@ -1110,7 +1112,7 @@ extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     const size_t need = dispatch_scratch_bytes(A, n_ranks) + A * 4 +
                         (n_ranks + 1) * 4 + 4096;
     if (arena_reserve(c->ws, need)) return 1;
@@ -1146,7 +1148,7 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     const size_t ne = L->e_end - L->e_begin;
     if (!ne) return fail("experts_dev: no routed experts resident");
     ApusCudaMoeCfg cx = L->cfg;       /* the shape dispatch and tiling see */
@@ -1187,7 +1189,7 @@ extern "C" int apus_cuda_ep_finish_dev(ApusCudaLayer *L, const uint16_t *d_x,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     const ApusCudaMoeCfg &cfg = L->cfg;
     /* shared expert only: a dispatch result with no routed rows */
     ApusCudaMoeCfg cx = cfg;
@@ -1229,7 +1231,7 @@ extern "C" int apus_cuda_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     g_ctx->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     return launch_router(g_ctx, d_x, L->rtr_w, (int)T, (int)L->cfg.experts,
                          (int)L->cfg.hidden, (int)L->cfg.top_k, L->wmin, d_idx,
                          d_w, nullptr, nullptr, nullptr, st);
@@ -1245,7 +1247,7 @@ extern "C" int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     size_t need = dispatch_scratch_bytes(A, E) + 1024;
     if (arena_reserve(c->io, need)) return 1;
     c->io.reset();
@@ -1264,7 +1266,7 @@ extern "C" int apus_cuda_rmsnorm_dev(const uint16_t *d_x, const uint16_t *d_w,
     if (!d_x || !d_y || !T || !N) return fail("rmsnorm_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     size_t smem = 4 * N * sizeof(float);
     if (smem > 48 * 1024) {
         if (smem > (size_t)g_ctx->smem_optin) return fail("rmsnorm: N too large");
@@ -1283,7 +1285,7 @@ extern "C" int apus_cuda_resadd_dev(const uint16_t *d_a, const uint16_t *d_b,
     if (!d_a || !d_b || !d_out || !n) return fail("resadd_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     size_t blocks = (n + 255) / 256;
     if (blocks > (size_t)g_ctx->sm_count * 16) blocks = g_ctx->sm_count * 16;
     resadd_kernel<<<(unsigned)blocks, 256, 0, st>>>(d_a, d_b, d_out, n);
@@ -1310,7 +1312,7 @@ extern "C" int apus_synth_fill_dev(uint16_t *d_dst, size_t n, uint64_t seed,
     if (!d_dst || !n) return fail("synth_fill_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_ctx->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     const uint64_t key = apus_synth_key(seed, layer, tensor_id);
     size_t blocks = (n + 255) / 256;
     if (blocks > (size_t)g_ctx->sm_count * 32) blocks = g_ctx->sm_count * 32;

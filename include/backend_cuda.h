@@ -187,8 +187,8 @@ void *apus_cuda_layer_tensor(ApusCudaLayer *layer, int which, size_t *elems);
 int apus_cuda_layer_refresh(ApusCudaLayer *layer);
 
 /* The block on device pointers: d_ln2 [T,H] -> d_out [T,H]; d_tr members are
- * device pointers (or NULL).  Enqueued on `stream` (a cudaStream_t, NULL =
- * the backend's own stream); does not synchronise.  Workspace comes from a
+ * device pointers (or NULL).  Enqueued on `stream` (a cudaStream_t; NULL is the
+ * CUDA default stream, as everywhere in this header); does not synchronise.  Workspace comes from a
  * per-process arena that grows on demand (growth synchronises; call
  * apus_cuda_reserve first to avoid that inside a timed region or a stream
  * capture).  Path selection: T <= APUS_CUDA_DECODE_MAX_T (default 64) takes
