@@ -240,6 +240,54 @@ router_topk_kernel(const uint16_t *__restrict__ x,
     }
 }
 
+/* One exact chain over a router row and a token, both in shared memory.  The
+ * dependent add (or fused multiply-add) per k is the critical path, so the
+ * loop body holds nothing else that touches `acc`: FMA and literal
+ * multiply-then-add are separate instantiations, and 64 k of operands are
+ * loaded ahead of the 64 chain steps that consume them. */
+template <bool FMA>
+__device__ __forceinline__ float small_chain(const uint16_t *__restrict__ wrow,
+                                             const float *__restrict__ xs,
+                                             int K) {
+    float acc = 0.0f;
+    int k = 0;
+#pragma unroll 2
+    for (; k + 64 <= K; k += 64) {
+        uint4 wv[8];
+        float4 xv[16];
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            wv[c] = *reinterpret_cast<const uint4 *>(wrow + k + c * 8);
+            xv[2 * c] = *reinterpret_cast<const float4 *>(xs + k + c * 8);
+            xv[2 * c + 1] = *reinterpret_cast<const float4 *>(xs + k + c * 8 + 4);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const float wf[8] = {bf16lo(wv[c].x), bf16hi(wv[c].x), bf16lo(wv[c].y),
+                                 bf16hi(wv[c].y), bf16lo(wv[c].z), bf16hi(wv[c].z),
+                                 bf16lo(wv[c].w), bf16hi(wv[c].w)};
+            const float xf[8] = {xv[2 * c].x,     xv[2 * c].y,     xv[2 * c].z,
+                                 xv[2 * c].w,     xv[2 * c + 1].x, xv[2 * c + 1].y,
+                                 xv[2 * c + 1].z, xv[2 * c + 1].w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (FMA)
+                    acc = __fmaf_rn(wf[j], xf[j], acc);
+                else
+                    acc = __fadd_rn(acc, __fmul_rn(wf[j], xf[j]));
+            }
+        }
+    }
+    for (; k < K; k++) {       /* K % 64 tail (K is a multiple of 8) */
+        const float wf = bf16_f32(wrow[k]);
+        if (FMA)
+            acc = __fmaf_rn(wf, xs[k], acc);
+        else
+            acc = __fadd_rn(acc, __fmul_rn(wf, xs[k]));
+    }
+    return acc;
+}
+
 /*
  * Latency path for few tokens.  grid = (ceil(rows / 8), T), block = 32: a CTA
  * pulls eight router rows into shared memory with one bulk copy each (all in
@@ -319,43 +367,9 @@ router_small_kernel(const uint16_t *__restrict__ x,
     if (arrived && lane < nrows) {
         const uint16_t *wrow =
             reinterpret_cast<const uint16_t *>(rows_s + (size_t)lane * pitch);
-        float acc = 0.0f;
         const bool fma_row = use_fma && (r0 + lane != E);
-        /* The chain is the critical path (one dependent FMA per k); the
-         * operands of the next two 8-wide pieces are fetched from shared
-         * memory while the current piece's FMAs retire. */
-        uint4 wv0 = *reinterpret_cast<const uint4 *>(wrow);
-        float4 xa0 = *reinterpret_cast<const float4 *>(xs);
-        float4 xb0 = *reinterpret_cast<const float4 *>(xs + 4);
-        uint4 wv1 = wv0;
-        float4 xa1 = xa0, xb1 = xb0;
-        if (K > 8) {
-            wv1 = *reinterpret_cast<const uint4 *>(wrow + 8);
-            xa1 = *reinterpret_cast<const float4 *>(xs + 8);
-            xb1 = *reinterpret_cast<const float4 *>(xs + 12);
-        }
-        for (int k = 0; k < K; k += 8) {
-            const uint4 wv = wv0;
-            const float4 xa = xa0, xb = xb0;
-            wv0 = wv1; xa0 = xa1; xb0 = xb1;
-            if (k + 16 < K) {
-                wv1 = *reinterpret_cast<const uint4 *>(wrow + k + 16);
-                xa1 = *reinterpret_cast<const float4 *>(xs + k + 16);
-                xb1 = *reinterpret_cast<const float4 *>(xs + k + 20);
-            }
-            const float wf[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y),
-                                 bf16hi(wv.y), bf16lo(wv.z), bf16hi(wv.z),
-                                 bf16lo(wv.w), bf16hi(wv.w)};
-            const float xf[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-            if (fma_row) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc = __fmaf_rn(wf[j], xf[j], acc);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    acc = __fadd_rn(acc, __fmul_rn(wf[j], xf[j]));
-            }
-        }
+        const float acc = fma_row ? small_chain<true>(wrow, xs, K)
+                                  : small_chain<false>(wrow, xs, K);
         const uint16_t code = bf16_bits(acc);
         if (r0 + lane == E) {
             extra_out[t] = code;
@@ -378,6 +392,53 @@ router_small_kernel(const uint16_t *__restrict__ x,
     if (lane == 0) counters[t] = 0;
     router_softmax_topk(ps, E, topk, lane, idx_out + (size_t)t * topk,
                         w_out ? w_out + (size_t)t * topk : nullptr);
+}
+
+constexpr int RL_STAGES = 3;
+constexpr int RL_BK = 64;
+constexpr int RL_XPITCH = RL_BK + 4;   /* floats; keeps 4 token groups on
+                                        * different banks */
+
+/* One 64-k block of router_logits_kernel's register tile (4 experts x TT/4
+ * tokens per thread); FMA and literal multiply-then-add are separate
+ * instantiations so neither chain carries the other's instructions. */
+template <int TT, bool FMA>
+__device__ __forceinline__ void logits_kblock(const unsigned char *__restrict__ st,
+                                              const float *__restrict__ xs,
+                                              int er0, int tg,
+                                              float (&acc)[4][TT / 4]) {
+    constexpr int TPT = TT / 4;
+#pragma unroll 2
+    for (int c = 0; c < 8; c++) {
+        float wf[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = er0 + i;
+            const uint4 wv = *reinterpret_cast<const uint4 *>(
+                st + (r >> 7) * 16384 + (r & 127) * 128 + ((c ^ (r & 7)) << 4));
+            wf[i][0] = bf16lo(wv.x); wf[i][1] = bf16hi(wv.x);
+            wf[i][2] = bf16lo(wv.y); wf[i][3] = bf16hi(wv.y);
+            wf[i][4] = bf16lo(wv.z); wf[i][5] = bf16hi(wv.z);
+            wf[i][6] = bf16lo(wv.w); wf[i][7] = bf16hi(wv.w);
+        }
+#pragma unroll
+        for (int j = 0; j < TPT; j++) {
+            const float *xp = xs + (j * 4 + tg) * RL_XPITCH + c * 8;
+            const float4 xa = *reinterpret_cast<const float4 *>(xp);
+            const float4 xb = *reinterpret_cast<const float4 *>(xp + 4);
+            const float xf[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (FMA)
+                        acc[i][j] = __fmaf_rn(wf[i][kk], xf[kk], acc[i][j]);
+                    else
+                        acc[i][j] = __fadd_rn(acc[i][j],
+                                              __fmul_rn(wf[i][kk], xf[kk]));
+                }
+        }
+    }
 }
 
 /*
@@ -404,10 +465,6 @@ router_small_kernel(const uint16_t *__restrict__ x,
  * router_select_kernel: one warp per token turns the logits into ids and
  * weights (router_softmax_topk).
  */
-constexpr int RL_STAGES = 3;
-constexpr int RL_BK = 64;
-constexpr int RL_XPITCH = RL_BK + 4;   /* floats; keeps 4 token groups on
-                                        * different banks */
 
 template <int TT, int ROWS>
 __global__ void __launch_bounds__(ROWS + 32)
@@ -482,6 +539,13 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         x_fetch(kb);
         x_store(kb);
     }
+    /* from here on the piece for stage kb+STAGES is fetched a whole k-block
+     * before it is stored (xr_hold carries it across one iteration) */
+    uint4 xr_hold = make_uint4(0, 0, 0, 0);
+    if (RL_STAGES < nkb) {
+        x_fetch(RL_STAGES);
+        xr_hold = xr;
+    }
 
     /* smallest nonzero |x| of the token tile (FMA-exactness guard) */
     unsigned int xmin = 0x7f800000u;
@@ -524,7 +588,11 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
     bool ok = true;
     for (int kb = 0; kb < nkb; kb++) {
         const int s = kb % RL_STAGES;
-        if (kb + RL_STAGES < nkb) x_fetch(kb + RL_STAGES);
+        const uint4 xr_store = xr_hold;              /* piece for kb+STAGES */
+        if (kb + RL_STAGES + 1 < nkb) {
+            x_fetch(kb + RL_STAGES + 1);
+            xr_hold = xr;
+        }
         if (ok && !mbar_wait(&full[s], (uint32_t)(kb / RL_STAGES) & 1u)) {
             ok = false;
             set_status(status, ST_MBAR_TIMEOUT);
@@ -532,54 +600,34 @@ router_logits_kernel(const __grid_constant__ CUtensorMap map_w,   /* [E, K] box 
         const unsigned char *st = smem + (size_t)s * STAGE;
         const float *xs = reinterpret_cast<const float *>(st + W_BYTES);
         if (ok && is_chain) {
-#pragma unroll 2
-            for (int c = 0; c < 8; c++) {
-                float wf[EPT][8];
-#pragma unroll
-                for (int i = 0; i < EPT; i++) {
-                    const int r = er0 + i;
-                    const uint4 wv = *reinterpret_cast<const uint4 *>(
-                        st + (r >> 7) * 16384 + (r & 127) * 128 +
-                        ((c ^ (r & 7)) << 4));
-                    wf[i][0] = bf16lo(wv.x); wf[i][1] = bf16hi(wv.x);
-                    wf[i][2] = bf16lo(wv.y); wf[i][3] = bf16hi(wv.y);
-                    wf[i][4] = bf16lo(wv.z); wf[i][5] = bf16hi(wv.z);
-                    wf[i][6] = bf16lo(wv.w); wf[i][7] = bf16hi(wv.w);
-                }
-#pragma unroll
-                for (int j = 0; j < TPT; j++) {
-                    const float *xp = xs + (j * 4 + tg) * RL_XPITCH + c * 8;
-                    const float4 xa = *reinterpret_cast<const float4 *>(xp);
-                    const float4 xb = *reinterpret_cast<const float4 *>(xp + 4);
-                    const float xf[8] = {xa.x, xa.y, xa.z, xa.w,
-                                         xb.x, xb.y, xb.z, xb.w};
-                    if (use_fma) {
-#pragma unroll
-                        for (int kk = 0; kk < 8; kk++)
-#pragma unroll
-                            for (int i = 0; i < EPT; i++)
-                                acc[i][j] = __fmaf_rn(wf[i][kk], xf[kk], acc[i][j]);
-                    } else {
-#pragma unroll
-                        for (int kk = 0; kk < 8; kk++)
-#pragma unroll
-                            for (int i = 0; i < EPT; i++)
-                                acc[i][j] = __fadd_rn(
-                                    acc[i][j], __fmul_rn(wf[i][kk], xf[kk]));
-                    }
-                }
-            }
+            if (use_fma)
+                logits_kblock<TT, true>(st, xs, er0, tg, acc);
+            else
+                logits_kblock<TT, false>(st, xs, er0, tg, acc);
         } else if (ok && is_extra) {
             /* lane t: the extra row against token t (literal chain) */
             float a = acc_extra;
-            for (int j = 0; j < RL_BK; j++)
-                a = __fadd_rn(a, __fmul_rn(bf16_f32(__ldg(extra_row + kb * RL_BK + j)),
-                                           xs[lane * RL_XPITCH + j]));
+            uint4 ev[RL_BK / 8];
+#pragma unroll
+            for (int c = 0; c < RL_BK / 8; c++)
+                ev[c] = ldg16(extra_row + kb * RL_BK + c * 8);
+#pragma unroll
+            for (int c = 0; c < RL_BK / 8; c++) {
+                const float ef[8] = {bf16lo(ev[c].x), bf16hi(ev[c].x),
+                                     bf16lo(ev[c].y), bf16hi(ev[c].y),
+                                     bf16lo(ev[c].z), bf16hi(ev[c].z),
+                                     bf16lo(ev[c].w), bf16hi(ev[c].w)};
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    a = __fadd_rn(a, __fmul_rn(ef[j],
+                                               xs[lane * RL_XPITCH + c * 8 + j]));
+            }
             acc_extra = a;
         }
         __syncthreads();            /* everyone is done with stage s */
         if (kb + RL_STAGES < nkb) {
             if (tid == 0 && ok) issue(kb + RL_STAGES);
+            xr = xr_store;
             x_store(kb + RL_STAGES);
         }
     }
