@@ -63,6 +63,7 @@ SYMBOLS = [
     "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
+    "apus_cuda_fused_timeline",
     "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
     "apus_cuda_ep_finish_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
@@ -321,6 +322,14 @@ class Backend:
         if n < 0:
             raise BackendError("apus_cuda_last_stage_ms failed")
         return dict(zip(STAGES, (float(v) for v in ms)))
+
+    def fused_timeline(self):
+        """[n_cta, 8] global-timer stamps of the one-kernel path's phases."""
+        buf = (C.c_ulonglong * (256 * 8))()
+        n = self.lib.apus_cuda_fused_timeline(buf, 256 * 8)
+        if n < 0:
+            return None
+        return np.array(buf[:n], dtype=np.uint64).reshape(-1, 8)
 
     def last_block_launches(self):
         return int(self.lib.apus_cuda_last_block_launches())

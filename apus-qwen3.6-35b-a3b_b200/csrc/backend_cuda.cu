@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "decode_fused.cuh"
 #include "decode_gemv.cuh"
 #include "dispatch.cuh"
 #include "misc_kernels.cuh"
@@ -80,7 +81,16 @@ struct Ctx {
     unsigned int *d_scratch_u32 = nullptr;
     unsigned int *d_router_counters = nullptr;   /* [ROUTER_SMALL_MAX_T], self-resetting */
     float *d_router_logits = nullptr;            /* [ROUTER_SMALL_MAX_T][1024] */
-    int decode_max_t = 64;
+    int decode_max_t = 4;        /* above this the tcgen05 grouped GEMM runs */
+    int fused_max_t = 4;         /* up to this the one-kernel decode path runs */
+    /* scratch of the fused decode kernel */
+    float *d_df_logits = nullptr, *d_df_approx = nullptr;
+    int df_speculate = 1;
+    uint16_t *d_df_sgl = nullptr, *d_df_act = nullptr, *d_df_sa = nullptr;
+    unsigned int *d_df_sync = nullptr;
+    unsigned long long *d_df_timeline = nullptr;   /* [sm_count][DF_MARKS] */
+    bool df_timeline_valid = false;
+    size_t df_act_elems = 0, df_sa_elems = 0;
     int last_block_launches = 0;
     bool hooks_filled = false;
     /* optional per-stage CUDA events inside the block (benchmarks) */
@@ -165,7 +175,17 @@ static int ctx_init() {
                      (size_t)ROUTER_SMALL_MAX_T * 1024 * sizeof(float)));
     long mb = env_long("APUS_CUDA_DENSE_MB", -1);
     c->budget = mb < 0 ? ~0ull : (uint64_t)mb << 20;
-    c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 64);
+    c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 4);
+    c->fused_max_t = (int)env_long("APUS_CUDA_FUSED_MAX_T", DF_MAX_T);
+    if (c->fused_max_t > DF_MAX_T) c->fused_max_t = DF_MAX_T;
+    CU_OK(cudaMalloc(&c->d_df_logits, (size_t)DF_MAX_T * 1024 * sizeof(float)));
+    CU_OK(cudaMalloc(&c->d_df_approx, (size_t)DF_MAX_T * 1024 * sizeof(float)));
+    c->df_speculate = (int)env_long("APUS_CUDA_SPECULATE", 1);
+    CU_OK(cudaMalloc(&c->d_df_sgl, 64));
+    CU_OK(cudaMalloc(&c->d_df_sync, 64));
+    CU_OK(cudaMemset(c->d_df_sync, 0, 64));
+    CU_OK(cudaMalloc(&c->d_df_timeline,
+                     (size_t)c->sm_count * DF_MARKS * sizeof(unsigned long long)));
     g_apus_use_pdl = env_long("APUS_CUDA_PDL", 1) != 0;
     g_ctx = c;
     return 0;
@@ -271,6 +291,13 @@ extern "C" void apus_cuda_disable(void) {
     if (c->io.base) cudaFree(c->io.base);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_router_counters) cudaFree(c->d_router_counters);
+    if (c->d_df_logits) cudaFree(c->d_df_logits);
+    if (c->d_df_approx) cudaFree(c->d_df_approx);
+    if (c->d_df_sgl) cudaFree(c->d_df_sgl);
+    if (c->d_df_sync) cudaFree(c->d_df_sync);
+    if (c->d_df_timeline) cudaFree(c->d_df_timeline);
+    if (c->d_df_act) cudaFree(c->d_df_act);
+    if (c->d_df_sa) cudaFree(c->d_df_sa);
     if (c->d_router_logits) cudaFree(c->d_router_logits);
     if (c->stream) cudaStreamDestroy(c->stream);
     g_ctx = nullptr;
@@ -886,6 +913,89 @@ static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T,
     return 0;
 }
 
+
+/* The one-kernel path for a handful of tokens (cooperative launch). */
+static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
+                            uint16_t *d_out, int T, const ApusCudaMoeTrace *tr,
+                            cudaStream_t st) {
+    const ApusCudaMoeCfg &cfg = L->cfg;
+    const int H = (int)cfg.hidden, I = (int)cfg.moe_inter,
+              Is = (int)cfg.shared_inter, E = (int)cfg.experts,
+              TK = (int)cfg.top_k;
+    const size_t need_act = (size_t)DF_MAX_A * I, need_sa = (size_t)DF_MAX_T * Is;
+    if (c->df_act_elems < need_act || c->df_sa_elems < need_sa) {
+        CU_OK(cudaDeviceSynchronize());
+        if (c->d_df_act) cudaFree(c->d_df_act);
+        if (c->d_df_sa) cudaFree(c->d_df_sa);
+        CU_OK(cudaMalloc(&c->d_df_act, need_act * 2));
+        CU_OK(cudaMalloc(&c->d_df_sa, need_sa * 2));
+        c->df_act_elems = need_act;
+        c->df_sa_elems = need_sa;
+    }
+    FusedArgs a;
+    memset(&a, 0, sizeof a);
+    a.T = T; a.H = H; a.I = I; a.Is = Is; a.E = E; a.TK = TK;
+    a.stages = 3;
+    size_t smem = decode_fused_smem(T, H, I, Is, E, TK, 3);
+    if (smem > (size_t)c->smem_optin) {
+        a.stages = 2;
+        smem = decode_fused_smem(T, H, I, Is, E, TK, 2);
+    }
+    a.wmin = L->wmin;
+    a.x = d_ln2;
+    a.rtr_w = L->rtr_w; a.exp_gu = L->exp_gu; a.exp_d = L->exp_d;
+    a.sh_g = L->sh_g; a.sh_u = L->sh_u; a.sh_d = L->sh_d; a.sh_gate = L->sh_gate;
+    a.logits_ws = c->d_df_logits; a.sgl_ws = c->d_df_sgl;
+    a.approx_ws = c->d_df_approx;
+    /* one token: the likely experts (top_k + 2 of them, 60 MB at the real
+     * dimensions) fit L2, so they are prefetched while the router runs */
+    a.speculate = (c->df_speculate && T == 1 &&
+                   (size_t)(TK + DF_SPEC_EXTRA) * (size_t)3 * I * H * 2 <=
+                       (size_t)96 << 20) ? 1 : 0;
+    a.act_ws = c->d_df_act; a.sa_ws = c->d_df_sa; a.sync = c->d_df_sync;
+    a.out = d_out;
+    a.idx_out = tr ? tr->rtr_idx : nullptr;
+    a.w_out = tr ? tr->rtr_w : nullptr;
+    a.tr_routed = tr ? tr->moe_routed : nullptr;
+    a.tr_shared = tr ? tr->moe_shared : nullptr;
+    a.tr_out = tr ? tr->moe_out : nullptr;
+    a.status = c->d_status;
+    a.timeline = c->stage_timing ? c->d_df_timeline : nullptr;
+    c->df_timeline_valid = c->stage_timing;
+    static size_t set_smem = 0;
+    if (smem > set_smem) {
+        CU_OK(cudaFuncSetAttribute(decode_fused_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+        set_smem = smem;
+    }
+    cudaLaunchConfig_t cfgl = {};
+    cfgl.gridDim = dim3(c->sm_count);
+    cfgl.blockDim = dim3(DF_THREADS);
+    cfgl.dynamicSmemBytes = smem;
+    cfgl.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfgl.attrs = attr;
+    cfgl.numAttrs = 1;
+    CU_OK(cudaLaunchKernelEx(&cfgl, decode_fused_kernel, a));
+    LAUNCHED();
+    return 0;
+}
+
+static bool fused_supported(Ctx *c, const ApusCudaMoeCfg &cfg, size_t T) {
+    if ((int)T > c->fused_max_t || T * cfg.top_k > DF_MAX_A) return false;
+    if (cfg.experts > 1024 || cfg.hidden / 8 > 2 * (size_t)c->sm_count) return false;
+    if (cfg.moe_inter * 2 > DF_STAGE_BYTES / 8 || cfg.shared_inter * 2 > DF_STAGE_BYTES / 8)
+        return false;                      /* eight down rows per stage */
+    if (cfg.hidden * 4 > DF_STAGE_BYTES) return false;   /* a gate+up row pair */
+    size_t smem = decode_fused_smem((int)T, (int)cfg.hidden, (int)cfg.moe_inter,
+                                    (int)cfg.shared_inter, (int)cfg.experts,
+                                    (int)cfg.top_k, 2);
+    return smem <= (size_t)c->smem_optin;
+}
+
 static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
                             uint16_t *d_out, size_t T,
                             const ApusCudaMoeTrace *d_tr, cudaStream_t st) {
@@ -895,6 +1005,9 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
         return fail("moe_block needs all experts resident; use the "
                     "expert-parallel entry points for a partial layer");
     c->last_block_launches = 0;
+    c->df_timeline_valid = false;
+    if (fused_supported(c, cfg, T))
+        return run_fused_decode(c, L, d_ln2, d_out, (int)T, d_tr, st);
     const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
     BlockBufs b;
     block_layout(cfg, T, nullptr, &b, prefill);
@@ -965,6 +1078,34 @@ extern "C" int apus_cuda_last_stage_ms(float *ms, int cap) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!g_ctx || !ms) return -1;
     for (int i = 0; i < cap; i++) ms[i] = 0.0f;
+    if (g_ctx->df_timeline_valid) {
+        /* the one-kernel path: phase boundaries from the device's global
+         * timer, each taken as the latest CTA to reach it */
+        if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+        const int G = g_ctx->sm_count;
+        std::vector<unsigned long long> tl((size_t)G * DF_MARKS);
+        if (cudaMemcpy(tl.data(), g_ctx->d_df_timeline,
+                       tl.size() * sizeof(unsigned long long),
+                       cudaMemcpyDeviceToHost) != cudaSuccess)
+            return -1;
+        unsigned long long t0 = ~0ull, end[DF_MARKS] = {};
+        for (int b = 0; b < G; b++) {
+            if (tl[(size_t)b * DF_MARKS] < t0) t0 = tl[(size_t)b * DF_MARKS];
+            for (int k = 1; k < DF_MARKS; k++)
+                if (tl[(size_t)b * DF_MARKS + k] > end[k])
+                    end[k] = tl[(size_t)b * DF_MARKS + k];
+        }
+        auto span = [&](int k0, int k1) {
+            unsigned long long a0 = k0 == 0 ? t0 : end[k0];
+            return end[k1] > a0 ? (float)((end[k1] - a0) * 1e-6) : 0.0f;
+        };
+        if (cap > APUS_CUDA_STAGE_ROUTER) ms[APUS_CUDA_STAGE_ROUTER] = span(0, 3);
+        if (cap > APUS_CUDA_STAGE_GATE_UP) ms[APUS_CUDA_STAGE_GATE_UP] = span(3, 4);
+        if (cap > APUS_CUDA_STAGE_DISPATCH) ms[APUS_CUDA_STAGE_DISPATCH] = span(4, 5);
+        if (cap > APUS_CUDA_STAGE_DOWN) ms[APUS_CUDA_STAGE_DOWN] = span(5, 6);
+        if (cap > APUS_CUDA_STAGE_FINALIZE) ms[APUS_CUDA_STAGE_FINALIZE] = span(6, 7);
+        return DF_MARKS - 1;
+    }
     if (g_ctx->n_ev < 2) return 0;
     if (cudaEventSynchronize(g_ctx->ev[g_ctx->n_ev - 1]) != cudaSuccess)
         return -1;
@@ -975,6 +1116,18 @@ extern "C" int apus_cuda_last_stage_ms(float *ms, int cap) {
         if (sidx >= 0 && sidx < cap) ms[sidx] += t;
     }
     return g_ctx->n_ev - 1;
+}
+
+extern "C" int apus_cuda_fused_timeline(unsigned long long *out, int cap) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_ctx || !out || !g_ctx->df_timeline_valid) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    int n = g_ctx->sm_count * DF_MARKS;
+    if (n > cap) n = cap;
+    if (cudaMemcpy(out, g_ctx->d_df_timeline, (size_t)n * sizeof(unsigned long long),
+                   cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -1;
+    return n;
 }
 
 extern "C" int apus_cuda_last_block_launches(void) {

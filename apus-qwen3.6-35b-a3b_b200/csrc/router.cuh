@@ -150,6 +150,81 @@ __device__ __forceinline__ void router_softmax_topk(float *p, int E, int topk,
     if (lane < topk) idx_out[lane] = my_e;
 }
 
+/* The same arithmetic as router_softmax_topk, spread over a 256-thread CTA
+ * for one token when latency matters (E <= 256): one expert per thread for the
+ * exponentials, the division and the selection rounds; the denominator is
+ * still the single ascending chain of c/moe.h:328-332 (thread 0).  Every
+ * thread of the CTA must call it; results land in idx_out / w_out (shared or
+ * global).  scratch: >= 2*16 ints of shared memory. */
+__device__ __forceinline__ void router_softmax_topk_cta256(
+    float *p /* [E] shared */, int E, int topk, int *scratch,
+    int32_t *idx_out, uint16_t *w_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *fs = reinterpret_cast<float *>(scratch);
+    /* max (value only) */
+    float m = tid < E ? p[tid] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) fs[warp] = m;
+    __syncthreads();
+    m = fs[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) m = fmaxf(m, fs[w]);
+    __syncthreads();
+    float q = 0.0f;
+    if (tid < E) {
+        q = (float)exp((double)__fsub_rn(p[tid], m));
+        p[tid] = q;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int e = 0; e < E; e++) s = __fadd_rn(s, p[e]);
+        fs[0] = s;
+    }
+    __syncthreads();
+    const float s = fs[0];
+    const float pr = tid < E ? __fdiv_rn(q, s) : -INFINITY;
+    int myv = __float_as_int(pr);            /* >= 0 for a probability */
+    if (tid >= E) myv = -1;
+    __syncthreads();
+    /* selection rounds: warp maxima to shared, everyone resolves the winner */
+    float my_p = 0.0f;
+    int my_e = 0;
+    for (int i = 0; i < topk; i++) {
+        const int wb = __reduce_max_sync(0xffffffffu, myv);
+        const unsigned we = __reduce_min_sync(0xffffffffu,
+                                              myv == wb ? (unsigned)tid : 0x7fffffffu);
+        int *buf = scratch + (i & 1) * 16;
+        if (lane == 0) {
+            buf[warp] = wb;
+            buf[8 + warp] = (int)we;
+        }
+        __syncthreads();
+        int bb = buf[0], be = buf[8];
+#pragma unroll
+        for (int w = 1; w < 8; w++) {
+            const int vb = buf[w], ve = buf[8 + w];
+            if (vb > bb || (vb == bb && ve < be)) { bb = vb; be = ve; }
+        }
+        if (bb < 0) { be = 0; }              /* nothing left: CPU leaves best = 0 */
+        if (tid == i) { my_e = be; my_p = __int_as_float(bb); }
+        if (tid == be) myv = -1;
+    }
+    /* renormalisation in selection order (thread i holds pick i) */
+    float *pk = fs;                           /* reuse: picks' probabilities */
+    __syncthreads();
+    if (tid < topk) pk[tid] = my_p;
+    __syncthreads();
+    if (tid < topk) {
+        float sw = 0.0f;
+        for (int i = 0; i < topk; i++) sw = __fadd_rn(sw, pk[i]);
+        if (w_out) w_out[tid] = bf16_bits(__fdiv_rn(my_p, sw));
+        idx_out[tid] = my_e;
+    }
+    __syncthreads();
+}
+
 /*
  * grid = ceil(T / TT); block = 256.  Dynamic shared memory:
  *   xs   float [TT][K]

@@ -218,6 +218,11 @@ enum {
 };
 int apus_cuda_stage_timing(int enable);
 int apus_cuda_last_stage_ms(float *ms, int cap);
+/* Diagnostic for the one-kernel path (T <= 4): with stage timing enabled each
+ * CTA stamps the device's global timer (ns) at its eight phase boundaries;
+ * this copies out[cta*8 + mark] for the last call and returns the number of
+ * values written, or -1 if the last call did not take that path. */
+int apus_cuda_fused_timeline(unsigned long long *out, int cap);
 
 /* Device-side status word of the last block call: 0 = ok; nonzero = a
  * bounded wait inside a kernel gave up (the context stays usable). */
