@@ -45,12 +45,16 @@
 namespace apus {
 
 constexpr int PG_BM = 128;        /* weight rows per tile (MMA M) */
-constexpr int PG_BN = 128;        /* token rows per tile (MMA N, max) */
+constexpr int PG_BN_GU = 128;     /* token rows per gate_up tile (MMA N, max) */
+constexpr int PG_BN_DN = 256;     /* token rows per down tile: one accumulator
+                                   * per tile, so twice the columns fit TMEM and
+                                   * every weight tile is fetched half as often */
+constexpr int PG_BN = PG_BN_GU;   /* sizing of the tile lists (the finer one) */
 constexpr int PG_BK = 64;         /* K elements per stage = one 128B swizzle row */
-constexpr int PG_THREADS = 192;
+constexpr int PG_EPI_WARPS = 8;   /* two per TMEM lane quarter */
+constexpr int PG_THREADS = 64 + PG_EPI_WARPS * 32;
 constexpr int PG_TILE_BYTES = PG_BM * PG_BK * 2;   /* 16 KB */
-constexpr int PG_STAGES_GU = 4;   /* 3 tiles per stage: Wg, Wu, X */
-constexpr int PG_STAGES_DN = 6;   /* 2 tiles per stage: Wd, ACT */
+constexpr int PG_STAGES = 4;      /* 48 KB per stage in both kernels */
 constexpr int PG_TMEM_COLS = 512;
 
 static char g_prefill_err[256] = "";
@@ -190,50 +194,53 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
                    const int32_t *__restrict__ offsets, int E, int T, int m_gu,
                    int m_gu_sh, int m_dn, TileLists tl) {
     pdl_enter();
-    __shared__ int warp_tot[32];
+    __shared__ int warp_tot[2][32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cnt = tid < E ? counts[tid] : 0;
-    const int nt = (cnt + PG_BN - 1) / PG_BN;
-    int inc = nt;
+    const int nt_a = (cnt + PG_BN_GU - 1) / PG_BN_GU;
+    const int nt_b = (cnt + PG_BN_DN - 1) / PG_BN_DN;
+    int inc_a = nt_a, inc_b = nt_b;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        int v = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += v;
+        int va = __shfl_up_sync(0xffffffffu, inc_a, d);
+        int vb = __shfl_up_sync(0xffffffffu, inc_b, d);
+        if (lane >= d) { inc_a += va; inc_b += vb; }
     }
-    if (lane == 31) warp_tot[warp] = inc;
+    if (lane == 31) { warp_tot[0][warp] = inc_a; warp_tot[1][warp] = inc_b; }
     __syncthreads();
-    int base = 0, total = 0;
+    int base_a = 0, total_a = 0, base_b = 0, total_b = 0;
     for (int w = 0; w < 32; w++) {
-        if (w < warp) base += warp_tot[w];
-        total += warp_tot[w];
+        if (w < warp) { base_a += warp_tot[0][w]; base_b += warp_tot[1][w]; }
+        total_a += warp_tot[0][w];
+        total_b += warp_tot[1][w];
     }
-    const int first = base + inc - nt;   /* token tiles before this expert */
-    if (tid < E && nt > 0) {
+    const int first_a = base_a + inc_a - nt_a, first_b = base_b + inc_b - nt_b;
+    if (tid < E && cnt > 0) {
         const int off = offsets[tid];
         for (int m = 0; m < m_gu; m++)
-            for (int n = 0; n < nt; n++)
-                tl.gu[(size_t)first * m_gu + (size_t)m * nt + n] =
-                    make_int4(tid, m, off + n * PG_BN, min(PG_BN, cnt - n * PG_BN));
+            for (int n = 0; n < nt_a; n++)
+                tl.gu[(size_t)first_a * m_gu + (size_t)m * nt_a + n] = make_int4(
+                    tid, m, off + n * PG_BN_GU, min(PG_BN_GU, cnt - n * PG_BN_GU));
         for (int m = 0; m < m_dn; m++)
-            for (int n = 0; n < nt; n++)
-                tl.dn[(size_t)first * m_dn + (size_t)m * nt + n] =
-                    make_int4(tid, m, off + n * PG_BN, min(PG_BN, cnt - n * PG_BN));
+            for (int n = 0; n < nt_b; n++)
+                tl.dn[(size_t)first_b * m_dn + (size_t)m * nt_b + n] = make_int4(
+                    tid, m, off + n * PG_BN_DN, min(PG_BN_DN, cnt - n * PG_BN_DN));
     }
     /* shared expert: dense over all T tokens */
-    const int nts = (T + PG_BN - 1) / PG_BN;
-    for (int i = tid; i < nts * m_gu_sh; i += blockDim.x) {
-        int m = i / nts, n = i - m * nts;
-        tl.gu[(size_t)total * m_gu + i] =
-            make_int4(E, m, n * PG_BN, min(PG_BN, T - n * PG_BN));
+    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
+    for (int i = tid; i < nts_a * m_gu_sh; i += blockDim.x) {
+        int m = i / nts_a, n = i - m * nts_a;
+        tl.gu[(size_t)total_a * m_gu + i] =
+            make_int4(E, m, n * PG_BN_GU, min(PG_BN_GU, T - n * PG_BN_GU));
     }
-    for (int i = tid; i < nts * m_dn; i += blockDim.x) {
-        int m = i / nts, n = i - m * nts;
-        tl.dn[(size_t)total * m_dn + i] =
-            make_int4(E, m, n * PG_BN, min(PG_BN, T - n * PG_BN));
+    for (int i = tid; i < nts_b * m_dn; i += blockDim.x) {
+        int m = i / nts_b, n = i - m * nts_b;
+        tl.dn[(size_t)total_b * m_dn + i] =
+            make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
     }
     if (tid == 0) {
-        *tl.n_gu = total * m_gu + nts * m_gu_sh;
-        *tl.n_dn = total * m_dn + nts * m_dn;
+        *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
+        *tl.n_dn = total_b * m_dn + nts_b * m_dn;
     }
 }
 
@@ -279,9 +286,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
                     GemmParams p) {
     pdl_enter();
-    constexpr int STAGES = GATE_UP ? PG_STAGES_GU : PG_STAGES_DN;
-    constexpr int TILES_PER_STAGE = GATE_UP ? 3 : 2;
-    constexpr int STAGE_BYTES = TILES_PER_STAGE * PG_TILE_BYTES;
+    constexpr int STAGES = PG_STAGES;
+    constexpr int BN = GATE_UP ? PG_BN_GU : PG_BN_DN;
+    constexpr int A_TILES = GATE_UP ? 2 : 1;
+    constexpr int B_OFF = A_TILES * PG_TILE_BYTES;        /* B tile offset */
+    constexpr int B_BYTES = BN * PG_BK * 2;
+    constexpr int STAGE_BYTES = B_OFF + B_BYTES;           /* 48 KB */
 
     extern __shared__ unsigned char pg_smem_raw[];
     /* 1024-byte alignment for the swizzled tiles */
@@ -301,7 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(&tfull[a], 1);
-            mbar_init(&tempty[a], 128);
+            mbar_init(&tempty[a], PG_EPI_WARPS * 32);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -342,8 +352,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     if (GATE_UP)
                         tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
                                     &full[s]);
-                    tma_load_2d(st + (TILES_PER_STAGE - 1) * PG_TILE_BYTES, mb,
-                                kb * PG_BK, t.z, &full[s]);
+                    tma_load_2d(st + B_OFF, mb, kb * PG_BK, t.z, &full[s]);
                 }
             }
         }
@@ -378,8 +387,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
                     const uint64_t da = umma_smem_desc(sa);
-                    const uint64_t db = umma_smem_desc(
-                        sa + (TILES_PER_STAGE - 1) * PG_TILE_BYTES);
+                    const uint64_t db = umma_smem_desc(sa + B_OFF);
 #pragma unroll
                     for (int k = 0; k < PG_BK / 16; k++) {
                         const uint32_t accum = (kb | k) ? 1u : 0u;
@@ -397,8 +405,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             }
         }
     } else {
-        /* ---------------- epilogue (warps 2..5) ---------------- */
+        /* ---------------- epilogue (warps 2..9) ---------------- */
+        /* A warp may only touch the TMEM lanes of its quarter (warp % 4); two
+         * warps share a quarter and split the 32-column chunks between them. */
         const int q = warp & 3;                 /* TMEM lane quarter */
+        const int half = (warp - 2) >> 2;       /* which chunks of the tile */
         const int row = q * 32 + lane;          /* row inside the tile */
         bool alive = true;
         int it = 0;
@@ -419,7 +430,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             uint16_t *out = shared ? p.out_shared : p.out_routed;
             const int ld = shared ? p.ld_shared : p.ld_routed;
             const int col = t.y * PG_BM + row;
-            for (int c0 = 0; c0 < t.w; c0 += 32) {
+            for (int c0 = half * 32; c0 < t.w; c0 += 64) {
                 uint32_t g[32];
                 tmem_ld32(taddr + (uint32_t)c0, g);
                 if (GATE_UP) {
@@ -438,16 +449,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                         }
                     }
                 } else {
+                    /* output row of each of this chunk's 32 columns: one load
+                     * per lane, handed round by shuffle */
+                    int my_orow = 0;
+                    if (c0 + lane < t.w)
+                        my_orow = shared ? t.z + c0 + lane
+                                         : __ldg(&p.perm[t.z + c0 + lane]);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const int n = c0 + j;
-                        if (n < t.w) {
-                            const int orow =
-                                shared ? t.z + n : __ldg(&p.perm[t.z + n]);
+                        const int orow = __shfl_sync(0xffffffffu, my_orow, j);
+                        if (c0 + j < t.w)
                             out[(size_t)orow * ld + col] =
                                 bf16_bits(__uint_as_float(g[j]));
-                        }
                     }
                 }
             }
@@ -503,10 +517,10 @@ inline bool prefill_supported(const ApusCudaMoeCfg &c) {
 
 /* rows x cols BF16, row-major; box = 128 rows x 64 columns, 128B swizzle */
 inline int encode_2d(PFN_encodeTiled_local enc, CUtensorMap *m, const void *base,
-                     size_t rows, size_t cols) {
+                     size_t rows, size_t cols, int box_rows = PG_BM) {
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)PG_BK, (cuuint32_t)PG_BM};
+    cuuint32_t box[2] = {(cuuint32_t)PG_BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base),
                      dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -553,9 +567,9 @@ inline PrefillMaps *prefill_maps_create(const ApusCudaMoeCfg &c,
 inline void prefill_maps_free(PrefillMaps *m) { delete m; }
 
 inline int pg_smem_bytes(bool gate_up) {
-    int stages = gate_up ? PG_STAGES_GU : PG_STAGES_DN;
-    int per = (gate_up ? 3 : 2) * PG_TILE_BYTES;
-    return stages * per + 1024 /* alignment slack */ + 256 /* barriers */;
+    (void)gate_up;
+    return PG_STAGES * 3 * PG_TILE_BYTES + 1024 /* alignment slack */ +
+           256 /* barriers */;
 }
 
 /* Routed + shared experts through the tensor-core path.  x [T,H] is the block
@@ -610,9 +624,9 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                      (size_t)(A > 0 ? A : 1), H);
     bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H);
     bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
-                     (size_t)(A > 0 ? A : 1), I);
+                     (size_t)(A > 0 ? A : 1), I, PG_BN_DN);
     bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
-                     (size_t)(do_shared && T > 0 ? T : 1), Is);
+                     (size_t)(do_shared && T > 0 ? T : 1), Is, PG_BN_DN);
     if (bad) return 1;
 
     cudaFuncSetAttribute(grouped_gemm_kernel<true>,
