@@ -1021,6 +1021,13 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
                       b.logits, L->sh_gate, b.sgl, st))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_ROUTER, st);
+    if (prefill) {
+        /* token groups feed the grouped-GEMV kernels only */
+        b.d.grp_expert = nullptr;
+        b.d.grp_first = nullptr;
+        b.d.grp_n = nullptr;
+        b.d.n_groups = nullptr;
+    }
     if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (prefill) {
@@ -1313,6 +1320,12 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     block_layout(cx, R, nullptr, &b, prefill);
     if (arena_reserve(c->ws, b.total)) return 1;
     if (block_layout(cx, R, &c->ws, &b, prefill)) return 1;
+    if (prefill) {
+        b.d.grp_expert = nullptr;
+        b.d.grp_first = nullptr;
+        b.d.grp_n = nullptr;
+        b.d.n_groups = nullptr;
+    }
     if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
                         DispatchKey{(int)L->e_begin, 1}))
         return 1;

@@ -177,19 +177,58 @@ dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
     }
 }
 
-/* pass 2: one block.  For each expert, exclusive prefix over units (in
- * place), totals -> counts; exclusive scan over experts -> offsets; token
- * groups. */
+/* pass 2: one block of 1024 threads.  For each expert, exclusive prefix over
+ * units (in place), totals -> counts; exclusive scan over experts -> offsets;
+ * token groups.  Thread (part, e) first sums its quarter of the units, the
+ * four partial sums meet in shared memory, then each thread rewrites its
+ * quarter with running prefixes — four short chains of loads instead of one
+ * long one.  E <= 256 takes this route; larger E the single-chain form. */
 __global__ void __launch_bounds__(1024)
 dispatch_scan_kernel(int32_t *__restrict__ unit_hist, int n_units, int E,
                      DispatchOut o) {
     pdl_enter();
     __shared__ int warp_tot[32];
     __shared__ int s_ngroups;
+    __shared__ int part_sum[4][256];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) s_ngroups = 0;
     int total = 0;
-    if (tid < E) {
+    if (E <= 256) {
+        const int e = tid & 255, part = tid >> 8;
+        const int per = (n_units + 3) / 4;
+        const int u_lo = part * per, u_hi = min(n_units, u_lo + per);
+        int sum = 0;
+        if (e < E) {
+            for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    v[j] = (u0 + j < u_hi) ? unit_hist[(size_t)(u0 + j) * E + e] : 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) sum += v[j];
+            }
+        }
+        part_sum[part][e] = sum;
+        __syncthreads();
+        int run = 0;
+        for (int q = 0; q < part; q++) run += part_sum[q][e];
+        if (e < E) {
+            for (int u0 = u_lo; u0 < u_hi; u0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    v[j] = (u0 + j < u_hi) ? unit_hist[(size_t)(u0 + j) * E + e] : 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (u0 + j < u_hi) unit_hist[(size_t)(u0 + j) * E + e] = run;
+                    run += v[j];
+                }
+            }
+        }
+        if (tid < E)
+            total = part_sum[0][tid] + part_sum[1][tid] + part_sum[2][tid] +
+                    part_sum[3][tid];
+    } else if (tid < E) {
         for (int u0 = 0; u0 < n_units; u0 += 8) {
             int v[8];
 #pragma unroll

@@ -304,15 +304,52 @@ def main():
         "host-pointer and device-pointer entry points disagree"
 
     pk = peaks()
-    dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
     slab_gu = 2 * cfg["moe_inter"] * H * 2
     slab_d = H * cfg["moe_inter"] * 2
     A = T * cfg["top_k"]
-    if dom == "gate_up":
-        kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * cfg["moe_inter"] * 2
+    I = cfg["moe_inter"]
+    hbm_ideal = algorithmic_bytes(cfg, T, uniq) / (pk["hbm_gbs"] * 1e9)
+    tc_ideal = flops(cfg, T) / (pk["bf16_tflops"] * 1e12)
+    if launches_per_step == 1:
+        # the one-kernel decode path: the kernel IS the block; its duration is
+        # the device-timeline sum of its phases
+        dom = "decode_fused_kernel"
+        kbytes = algorithmic_bytes(cfg, T, uniq)
+        kms = sum(stage_ms.values())
+        roof = {"bound": "hbm", "kernel": dom,
+                "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
+                "algorithmic_bytes_per_launch": kbytes}
     else:
-        kbytes = (uniq + 1) * slab_d + (A + T) * cfg["moe_inter"] * 2 + (A + T) * H * 2
-    achieved = kbytes / (stage_ms[dom] * 1e-3) / 1e9 if stage_ms.get(dom) else None
+        dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
+        kname = ("grouped_gemm_kernel<gate_up>" if dom == "gate_up"
+                 else "grouped_gemm_kernel<down>")
+        if T <= 4:
+            kname = "decode_" + dom + "_kernel"
+        if dom == "gate_up":
+            kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * I * 2
+            kflops = 2 * (A + T) * 2 * I * H
+        else:
+            kbytes = (uniq + 1) * slab_d + (A + T) * I * 2 + (A + T) * H * 2
+            kflops = 2 * (A + T) * H * I
+        kms = stage_ms.get(dom, 0.0)
+        if tc_ideal > hbm_ideal:
+            roof = {"bound": "tensor", "kernel": kname,
+                    "achieved": kflops / (kms * 1e-3) / 1e12 if kms else None,
+                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "traffic": None,
+                    "algorithmic_flops_per_launch": kflops}
+        else:
+            # ncu dram__bytes_read+write of this launch at the default workload
+            # (profiles/grouped_gemm_t512_prefill.md); other sizes not captured
+            traffic = None
+            if T == 512 and uniq == 256:
+                traffic = 1.1005e9 + 7.5e6 if dom == "gate_up" else 0.5439e9 + 17.2e6
+            roof = {"bound": "hbm", "kernel": kname,
+                    "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": traffic,
+                    "algorithmic_bytes_per_launch": kbytes}
+    roof["peak_source"] = pk["_source"]
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof["achieved"] else None
     block_bytes = algorithmic_bytes(cfg, T, uniq)
     line = {
         "metric": METRIC, "value": T / (ms * 1e-3), "unit": UNIT,
@@ -325,12 +362,7 @@ def main():
                 "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
                 "ms_per_step": e2e_ms},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved,
-                     "peak": pk["hbm_gbs"], "peak_source": pk["_source"],
-                     "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"] if achieved else None,
-                     "traffic": None,
-                     "algorithmic_bytes_per_launch": kbytes},
+        "roofline": roof,
         "block": {"algorithmic_bytes": block_bytes,
                   "hbm_frac_of_measured": block_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
                   "tensor_frac_of_measured": flops(cfg, T) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
