@@ -148,6 +148,165 @@ def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth):
               f"best of {steps}")
     return Ts / best, ref.threads(), sample, best * 1e3
 
+L2_BYTES = 126 << 20
+
+
+def run_stack(args, cfg, config, pkg, synth, L):
+    """A stack of L MoE layers with independent seeded weights, generated in
+    place in HBM.  Every step runs every layer's block once, so nothing a step
+    needs is left in L2 by the previous one.  Layer l reads its own seeded
+    token batch; with --chain the layers are chained as the engine chains them
+    (c/layer.h:386-388): ln2 = rmsnorm(h); h = rnd(h + moe_l(ln2)), and the
+    two elementwise kernels are inside the timed region."""
+    import numpy as np
+    import torch
+    torch.cuda.set_device(0)
+    be = pkg.Backend()
+    be.enable()
+    T, H, TK = args.tokens, cfg["hidden"], cfg["top_k"]
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    sp = stream.cuda_stream
+    layers = []
+    for l in range(L):
+        h = be.layer_create(cfg, None)
+        synth.device_weights(be, h, cfg, seed=args.seed, layer=l, stream=sp)
+        layers.append(h)
+    be.reserve(cfg, T)
+    chain = args.chain
+    n_in = 1 if chain else L
+    x_host = np.stack([synth.host_x(be, T, H, seed=args.seed, layer=l)
+                       for l in range(n_in)])
+    d_x = torch.from_numpy(x_host.view(np.int16)).cuda()      # [n_in, T, H]
+    d_h = torch.empty_like(d_x)                               # chain state / outputs
+    d_ln = torch.empty((T, H), dtype=torch.int16, device="cuda")
+    d_moe = torch.empty((T, H), dtype=torch.int16, device="cuda")
+    d_idx = torch.empty((T, TK), dtype=torch.int32, device="cuda")
+    row = T * H * 2
+
+    def one_pass(trace_uniq=None, timing=None):
+        if chain:
+            d_h.copy_(d_x)
+        for l, lay in enumerate(layers):
+            tr = {"idx": d_idx.data_ptr()} if trace_uniq is not None else None
+            if chain:
+                be.rmsnorm_dev(d_h.data_ptr(), None, d_ln.data_ptr(), T, H, stream=sp)
+                be.moe_block_dev(lay, d_ln.data_ptr(), d_moe.data_ptr(), T,
+                                 stream=sp, d_trace=tr)
+            else:
+                be.moe_block_dev(lay, d_x.data_ptr() + l * row,
+                                 d_h.data_ptr() + l * row, T, stream=sp, d_trace=tr)
+            if timing is not None:
+                for k, v in be.last_stage_ms().items():
+                    timing[k] = timing.get(k, 0.0) + v
+            if trace_uniq is not None:
+                torch.cuda.synchronize()
+                trace_uniq.append(int(torch.unique(d_idx).numel()))
+            if chain:
+                be.resadd_dev(d_h.data_ptr(), d_moe.data_ptr(), d_h.data_ptr(),
+                              T * H, stream=sp)
+
+    uniq = []
+    one_pass(trace_uniq=uniq)
+    torch.cuda.synchronize()
+    launches_per_layer = be.last_block_launches() + (2 if chain else 0)
+    step = one_pass
+    launch_mode = "host launches"
+    if not args.no_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                one_pass()
+            step = g.replay
+            launch_mode = "cuda graph replay"
+        except Exception as e:
+            launch_mode = f"host launches (graph capture failed: {e})"
+            torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    status = be.last_block_status()
+    # stage times (host launches, events / device timeline per layer)
+    be.stage_timing(True)
+    acc = {}
+    one_pass(timing=acc)
+    be.stage_timing(False)
+    stage_ms = {k: v / L for k, v in acc.items()}
+    # end to end: pinned host tokens in, result back to host, every step
+    xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
+    hout = torch.empty_like(xin).pin_memory()
+    for _ in range(3):
+        d_x.copy_(xin, non_blocking=True); step(); hout.copy_(d_h, non_blocking=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        d_x.copy_(xin, non_blocking=True)
+        step()
+        hout.copy_(d_h, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    sampler.stop_flag = True
+    sampler.join()
+
+    pk = peaks()
+    bytes_pass = sum(algorithmic_bytes(cfg, T, u) for u in uniq)
+    tok_layers = T * L
+    cfgline = dict(config)
+    cfgline.update({
+        "workload": f"stack of {L} MoE layers (independent weights"
+                    + (", chained x <- x + moe(rmsnorm(x))" if chain else
+                       ", one token batch per layer")
+                    + f"), {T} tokens per layer per step, uniform router, "
+                    f"seed {args.seed}, H2048 E256 top8 I512",
+        "layers": L, "launch": launch_mode,
+        "l2_policy": f"inputs larger than L2: one pass reads "
+                     f"{bytes_pass / 1e6:.0f} MB of weights across {L} layers"})
+    kms = sum(stage_ms.values())
+    fused = be.last_block_launches() == 1
+    line = {
+        "metric": METRIC, "value": tok_layers / (ms * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 storage, fp32 accumulate",
+        "data": "synthetic", "config": cfgline, "clocks": sampler.summary(),
+        "e2e": {"value": tok_layers / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": n_in * T * H * 2,
+                "d2h_bytes_per_step": n_in * T * H * 2,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches_per_layer * L * args.steps,
+        "roofline": {"bound": "hbm",
+                     "kernel": "decode_fused_kernel" if fused else "whole layer (all kernels)",
+                     "achieved": bytes_pass / L / (kms * 1e-3) / 1e9 if kms else None,
+                     "peak": pk["hbm_gbs"], "peak_source": pk["_source"],
+                     "unit": "GB/s",
+                     "frac": (bytes_pass / L / (kms * 1e-3) / 1e9 / pk["hbm_gbs"]) if kms else None,
+                     "traffic": None,
+                     "algorithmic_bytes_per_launch": bytes_pass / L},
+        "block": {"algorithmic_bytes_per_layer": bytes_pass / L,
+                  "hbm_frac_of_measured": bytes_pass / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                  "unique_experts_mean": sum(uniq) / L, "stage_ms_per_layer": stage_ms,
+                  "us_per_token_layer": ms * 1e3 / tok_layers,
+                  "device_status": status},
+    }
+    if not args.no_cpu_baseline:
+        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth)
+        if r is not None:
+            v, threads, sample, _ = r
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
+                                    "kind": "reference",
+                                    "sample": sample + " (one layer of the stack)"}
+    print(json.dumps(line))
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -158,6 +317,14 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="run a stack of this many MoE layers with independent "
+                         "weights, chained as x <- x + moe(rmsnorm(x)); default: "
+                         "1, or as many as it takes for one pass to read more "
+                         "than four times the L2 capacity (small token counts)")
+    ap.add_argument("--chain", action="store_true",
+                    help="with a layer stack: chain the layers through rmsnorm "
+                         "and the residual add instead of one batch per layer")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from the host instead of "
                          "replaying a captured CUDA graph")
@@ -203,6 +370,17 @@ def main():
     if world > 1:
         from apus_b200 import ep_bench
         ep_bench.run(args, cfg, config, pkg, synth, METRIC, UNIT, peaks())
+        return
+
+    # small token counts touch few experts: one layer's working set would sit
+    # in L2 from step to step, so they run as a stack of independent layers
+    L = args.layers
+    if L <= 0:
+        est_uniq = min(cfg["experts"], T * cfg["top_k"])
+        per_layer = algorithmic_bytes(cfg, T, est_uniq)
+        L = 1 if per_layer >= 4 * L2_BYTES else -(-4 * L2_BYTES // per_layer)
+    if L > 1:
+        run_stack(args, cfg, config, pkg, synth, L)
         return
 
     torch.cuda.set_device(0)
