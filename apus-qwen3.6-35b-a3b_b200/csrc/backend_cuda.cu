@@ -62,6 +62,7 @@ struct ApusCudaLayer {
     uint16_t *sh_g = nullptr, *sh_u = nullptr, *sh_d = nullptr,
              *sh_gate = nullptr;
     float wmin = 0.0f;          /* smallest nonzero |rtr_w| (0 = unknown) */
+    float wmin_gate = 0.0f;     /* the same for the shared-gate row */
     size_t bytes = 0;
     PrefillMaps *maps = nullptr; /* tensor maps for the tcgen05 path */
 };
@@ -84,8 +85,7 @@ struct Ctx {
     int decode_max_t = 4;        /* above this the tcgen05 grouped GEMM runs */
     int fused_max_t = 4;         /* up to this the one-kernel decode path runs */
     /* scratch of the fused decode kernel */
-    float *d_df_logits = nullptr, *d_df_approx = nullptr;
-    int df_speculate = 1;
+    float *d_df_logits = nullptr;
     uint16_t *d_df_sgl = nullptr, *d_df_act = nullptr, *d_df_sa = nullptr;
     unsigned int *d_df_sync = nullptr;
     unsigned long long *d_df_timeline = nullptr;   /* [sm_count][DF_MARKS] */
@@ -179,8 +179,6 @@ static int ctx_init() {
     c->fused_max_t = (int)env_long("APUS_CUDA_FUSED_MAX_T", DF_MAX_T);
     if (c->fused_max_t > DF_MAX_T) c->fused_max_t = DF_MAX_T;
     CU_OK(cudaMalloc(&c->d_df_logits, (size_t)DF_MAX_T * 1024 * sizeof(float)));
-    CU_OK(cudaMalloc(&c->d_df_approx, (size_t)DF_MAX_T * 1024 * sizeof(float)));
-    c->df_speculate = (int)env_long("APUS_CUDA_SPECULATE", 1);
     CU_OK(cudaMalloc(&c->d_df_sgl, 64));
     CU_OK(cudaMalloc(&c->d_df_sync, 64));
     CU_OK(cudaMemset(c->d_df_sync, 0, 64));
@@ -292,7 +290,6 @@ extern "C" void apus_cuda_disable(void) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_router_counters) cudaFree(c->d_router_counters);
     if (c->d_df_logits) cudaFree(c->d_df_logits);
-    if (c->d_df_approx) cudaFree(c->d_df_approx);
     if (c->d_df_sgl) cudaFree(c->d_df_sgl);
     if (c->d_df_sync) cudaFree(c->d_df_sync);
     if (c->d_df_timeline) cudaFree(c->d_df_timeline);
@@ -699,7 +696,8 @@ extern "C" int apus_cuda_layer_create(const ApusCudaMoeCfg *cfg,
     c->bytes_resident += L->bytes;
     L->maps = nullptr;
     if (w && w->rtr_w) {
-        if (min_nonzero(c, L->rtr_w, E * H, &L->wmin, c->stream)) {
+        if (min_nonzero(c, L->rtr_w, E * H, &L->wmin, c->stream) ||
+            min_nonzero(c, L->sh_gate, H, &L->wmin_gate, c->stream)) {
             layer_free(L);
             return 1;
         }
@@ -741,8 +739,11 @@ extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
     if (ctx_init()) return 1;
     /* set-up call: whatever stream filled the tensor, wait for it */
     CU_OK(cudaDeviceSynchronize());
-    return min_nonzero(g_ctx, L->rtr_w, L->cfg.experts * L->cfg.hidden,
-                       &L->wmin, g_ctx->stream);
+    if (min_nonzero(g_ctx, L->rtr_w, L->cfg.experts * L->cfg.hidden, &L->wmin,
+                    g_ctx->stream))
+        return 1;
+    return min_nonzero(g_ctx, L->sh_gate, L->cfg.hidden, &L->wmin_gate,
+                       g_ctx->stream);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -942,16 +943,11 @@ static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
         smem = decode_fused_smem(T, H, I, Is, E, TK, 2);
     }
     a.wmin = L->wmin;
+    a.wmin_gate = L->wmin_gate;
     a.x = d_ln2;
     a.rtr_w = L->rtr_w; a.exp_gu = L->exp_gu; a.exp_d = L->exp_d;
     a.sh_g = L->sh_g; a.sh_u = L->sh_u; a.sh_d = L->sh_d; a.sh_gate = L->sh_gate;
     a.logits_ws = c->d_df_logits; a.sgl_ws = c->d_df_sgl;
-    a.approx_ws = c->d_df_approx;
-    /* one token: the likely experts (top_k + 2 of them, 60 MB at the real
-     * dimensions) fit L2, so they are prefetched while the router runs */
-    a.speculate = (c->df_speculate && T == 1 &&
-                   (size_t)(TK + DF_SPEC_EXTRA) * (size_t)3 * I * H * 2 <=
-                       (size_t)96 << 20) ? 1 : 0;
     a.act_ws = c->d_df_act; a.sa_ws = c->d_df_sa; a.sync = c->d_df_sync;
     a.out = d_out;
     a.idx_out = tr ? tr->rtr_idx : nullptr;

@@ -45,7 +45,7 @@ constexpr int DF_STAGE_BYTES = 8192;    /* a gate+up row pair, or 8 down rows */
 
 struct FusedArgs {
     int T, H, I, Is, E, TK, stages;
-    float wmin;
+    float wmin, wmin_gate;              /* smallest nonzero |w|: router, shared-gate row */
     const uint16_t *x;                  /* [T, H] */
     const uint16_t *rtr_w, *exp_gu, *exp_d, *sh_g, *sh_u, *sh_d, *sh_gate;
     /* global scratch owned by the backend */
@@ -53,10 +53,7 @@ struct FusedArgs {
     uint16_t *sgl_ws;                   /* [DF_MAX_T] */
     uint16_t *act_ws;                   /* [DF_MAX_A][I] */
     uint16_t *sa_ws;                    /* [DF_MAX_T][Is] */
-    float *approx_ws;                   /* [DF_MAX_T][E] fast (inexact) logits */
-    unsigned int *sync;                 /* [0] router done, [1] barrier, [2] exits,
-                                         * [3] approximate logits published */
-    int speculate;                      /* 1: prefetch the likely experts to L2 */
+    unsigned int *sync;                 /* [0] router done, [1] barrier, [2] exits */
     /* outputs */
     uint16_t *out;                      /* [T, H] */
     int32_t *idx_out;                   /* [T, TK] (optional) */
@@ -91,37 +88,6 @@ __device__ __forceinline__ bool spin_until(const unsigned int *p,
         if (i > 32) __nanosleep(40);
     }
     return false;
-}
-
-/* dot products of one weight row (shared memory) against up to four staged
- * activation rows selected by `mask` */
-template <int NT>
-__device__ __forceinline__ void df_dots(const uint16_t *wrow, const uint16_t *xs,
-                                        int stride, const int *rows, int K,
-                                        int lane, float (&acc)[4]) {
-    for (int k = lane * 8; k < K; k += 256) {
-        float wf[8];
-        unpack8(*reinterpret_cast<const uint4 *>(wrow + k), wf);
-#pragma unroll
-        for (int n = 0; n < NT; n++) {
-            float xf[8];
-            unpack8(*reinterpret_cast<const uint4 *>(xs + (size_t)rows[n] * stride + k),
-                    xf);
-#pragma unroll
-            for (int j = 0; j < 8; j++) acc[n] = fmaf(wf[j], xf[j], acc[n]);
-        }
-    }
-}
-__device__ __forceinline__ void df_dots_n(int nt, const uint16_t *wrow,
-                                          const uint16_t *xs, int stride,
-                                          const int *rows, int K, int lane,
-                                          float (&acc)[4]) {
-    switch (nt) {
-        case 1: df_dots<1>(wrow, xs, stride, rows, K, lane, acc); break;
-        case 2: df_dots<2>(wrow, xs, stride, rows, K, lane, acc); break;
-        case 3: df_dots<3>(wrow, xs, stride, rows, K, lane, acc); break;
-        default: df_dots<4>(wrow, xs, stride, rows, K, lane, acc); break;
-    }
 }
 
 /* butterfly-reduce N independent values at once (the shuffles of different
@@ -223,90 +189,6 @@ __device__ __forceinline__ void df_down8_n(int nt, const uint16_t *ws,
 }
 
 
-/* order-preserving integer key of a float (larger float -> larger int) */
-__device__ __forceinline__ int float_key(float f) {
-    const int b = __float_as_int(f);
-    return b >= 0 ? b : (b ^ 0x7fffffff);
-}
-__device__ __forceinline__ void named_bar(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-constexpr int DF_SPEC_EXTRA = 0;        /* candidates beyond top_k */
-constexpr int DF_SPEC_PIECE = 2048;     /* bytes per L2 prefetch instruction */
-
-/*
- * Speculation (one token): while the exact router chains are still running
- * (~5 us of dependent adds), rank the FAST logits — plain tree-reduced dot
- * products published by the router CTAs within the first microseconds — and
- * ask the memory system to pull this CTA's slice of the top_k + 2 likeliest
- * experts' weights into L2.  The exact result decides what is computed; a
- * wrong guess costs a wasted prefetch and one expert read from HBM instead of
- * L2, never a wrong answer.  Run by `team` threads (a multiple of 32) that
- * synchronise on named barrier 1; `tt` is the thread's index in the team.
- */
-__device__ __forceinline__ void df_speculate(const FusedArgs &a, float *ps,
-                                             int *cand, int tt, int team) {
-    const int E = a.E, TK = a.TK;
-    __shared__ int s_spec_ok;
-    if (tt == 0) {
-        int ok = 0;
-        for (uint32_t i = 0; i < (1u << 19); i++) {
-            if (ld_acquire(&a.sync[3]) >= (unsigned)E) { ok = 1; break; }
-            if (i > 16) __nanosleep(40);
-        }
-        s_spec_ok = ok;
-    }
-    named_bar(1, team);
-    if (!s_spec_ok) return;              /* uniform over the team */
-    for (int e = tt; e < E; e += team) ps[e] = __ldcg(&a.approx_ws[e]);
-    named_bar(1, team);
-    const int nc = min(TK + DF_SPEC_EXTRA, E);
-    if (tt < 32) {
-        for (int i = 0; i < nc; i++) {
-            int bk = INT_MIN, be = 0x7fffffff;
-            for (int e = tt; e < E; e += 32) {
-                const int k = float_key(ps[e]);
-                if (k > bk) { bk = k; be = e; }
-            }
-            const int wk = __reduce_max_sync(0xffffffffu, bk);
-            const int we = (int)__reduce_min_sync(0xffffffffu,
-                                                  bk == wk ? (unsigned)be : 0x7fffffffu);
-            if (tt == 0) cand[i] = we;
-            if (tt == (we & 31)) ps[we] = -INFINITY;
-            __syncwarp();
-        }
-    }
-    named_bar(1, team);
-    /* this CTA's slice of every candidate's gate_up and down matrices */
-    const size_t gu_bytes = (size_t)2 * a.I * a.H * 2, d_bytes = (size_t)a.H * a.I * 2;
-    const size_t G = gridDim.x, b = blockIdx.x;
-    const size_t gu_lo = (gu_bytes * b / G) & ~(size_t)15;
-    const size_t gu_hi = (gu_bytes * (b + 1) / G) & ~(size_t)15;
-    const size_t d_lo = (d_bytes * b / G) & ~(size_t)15;
-    const size_t d_hi = (d_bytes * (b + 1) / G) & ~(size_t)15;
-    const int gu_p = (int)((gu_hi - gu_lo + DF_SPEC_PIECE - 1) / DF_SPEC_PIECE);
-    const int d_p = (int)((d_hi - d_lo + DF_SPEC_PIECE - 1) / DF_SPEC_PIECE);
-    const int per = gu_p + d_p;
-    for (int i = tt; i < nc * per; i += team) {
-        const int ci = i / per, pi = i - ci * per;
-        const int e = cand[ci];
-        const unsigned char *base;
-        size_t lo, hi;
-        if (pi < gu_p) {
-            base = reinterpret_cast<const unsigned char *>(a.exp_gu) + (size_t)e * gu_bytes;
-            lo = gu_lo + (size_t)pi * DF_SPEC_PIECE;
-            hi = gu_hi;
-        } else {
-            base = reinterpret_cast<const unsigned char *>(a.exp_d) + (size_t)e * d_bytes;
-            lo = d_lo + (size_t)(pi - gu_p) * DF_SPEC_PIECE;
-            hi = d_hi;
-        }
-        const size_t n = hi - lo < (size_t)DF_SPEC_PIECE ? hi - lo : (size_t)DF_SPEC_PIECE;
-        if (n >= 16) bulk_prefetch_l2(base + lo, (uint32_t)n);
-    }
-}
-
 /* A warp's private ring of bulk copies.  issue() is called by lane 0 only. */
 struct WarpRing {
     unsigned char *base;     /* stages * DF_STAGE_BYTES */
@@ -366,7 +248,6 @@ decode_fused_kernel(FusedArgs a) {
     __shared__ int s_uexp[DF_MAX_A];               /* unique experts */
     __shared__ unsigned int s_umask[DF_MAX_A];     /* assignments of each */
     __shared__ int s_U;
-    __shared__ int s_cand[DF_MAX_A + DF_SPEC_EXTRA];
     __shared__ int s_dead;
     __shared__ unsigned int s_xmin;
 
@@ -428,9 +309,12 @@ decode_fused_kernel(FusedArgs a) {
             xmin = min(xmin, __shfl_xor_sync(0xffffffffu, xmin, o));
         if (lane == 0) atomicMin(&s_xmin, xmin);
         __syncthreads();
-        const bool use_fma =
-            (a.wmin > 0.0f) &&
-            ((double)a.wmin * (double)__uint_as_float(s_xmin) >= 7.52316384526264e-37);
+        /* the fused form is exact while the smallest product is a normal
+         * number; the shared-gate row has its own smallest weight */
+        const double xmn = (double)__uint_as_float(s_xmin);
+        const bool use_fma = (a.wmin > 0.0f) && ((double)a.wmin * xmn >= 7.52316384526264e-37);
+        const bool use_fma_gate =
+            (a.wmin_gate > 0.0f) && ((double)a.wmin_gate * xmn >= 7.52316384526264e-37);
         const bool arrived = mbar_wait(rbar, 0);      /* every warp waits */
         if (!arrived) {
             set_status(a.status, ST_MBAR_TIMEOUT);
@@ -441,7 +325,7 @@ decode_fused_kernel(FusedArgs a) {
             if (arrived && r < nrows) {
                 const uint16_t *wrow =
                     reinterpret_cast<const uint16_t *>(rows_s + (size_t)r * pitch);
-                const bool fma_row = use_fma && (r0 + r != E);
+                const bool fma_row = (r0 + r != E) ? use_fma : use_fma_gate;
                 const float acc =
                     fma_row ? small_chain<true>(wrow, xf + (size_t)t * xpitch, H)
                             : small_chain<false>(wrow, xf + (size_t)t * xpitch, H);
@@ -456,35 +340,6 @@ decode_fused_kernel(FusedArgs a) {
                 __threadfence();
                 red_release_add(&a.sync[0], 1u);
             }
-        } else if (a.speculate) {
-            /* warps 1..7: fast logits of this CTA's rows (token 0), published
-             * at once; then the speculative prefetch, all while warp 0 walks
-             * the exact chains */
-            if (arrived) {
-                for (int r = warp - 1; r < nrows; r += DF_WARPS - 1) {
-                    if (r0 + r >= E) continue;
-                    const uint16_t *wrow =
-                        reinterpret_cast<const uint16_t *>(rows_s + (size_t)r * pitch);
-                    float acc = 0.f;
-                    for (int k = lane * 8; k < H; k += 256) {
-                        float wf[8];
-                        unpack8(*reinterpret_cast<const uint4 *>(wrow + k), wf);
-                        const float4 xa = *reinterpret_cast<const float4 *>(xf + k);
-                        const float4 xb = *reinterpret_cast<const float4 *>(xf + k + 4);
-                        acc = fmaf(wf[0], xa.x, acc); acc = fmaf(wf[1], xa.y, acc);
-                        acc = fmaf(wf[2], xa.z, acc); acc = fmaf(wf[3], xa.w, acc);
-                        acc = fmaf(wf[4], xb.x, acc); acc = fmaf(wf[5], xb.y, acc);
-                        acc = fmaf(wf[6], xb.z, acc); acc = fmaf(wf[7], xb.w, acc);
-                    }
-                    acc = warp_sum(acc);
-                    if (lane == 0) {
-                        a.approx_ws[r0 + r] = acc;
-                        __threadfence();
-                        red_release_add(&a.sync[3], 1u);
-                    }
-                }
-            }
-            df_speculate(a, ps, s_cand, tid - 32, DF_THREADS - 32);
         }
         fence_proxy_async();  /* generic writes above, bulk copies next */
         __syncthreads();      /* the ring region is free again */
@@ -538,10 +393,6 @@ decode_fused_kernel(FusedArgs a) {
         }
     }
 
-    if (a.speculate && !is_router) {
-        __syncthreads();
-        df_speculate(a, ps, s_cand, tid, DF_THREADS);
-    }
     df_mark(a, 2);                          /* shared gate/up done */
     /* ---------------- routing result ---------------- */
     if (tid == 0 && !s_dead) {
@@ -812,7 +663,6 @@ decode_fused_kernel(FusedArgs a) {
         if (old == (unsigned)G - 1) {
             a.sync[0] = 0;
             a.sync[1] = 0;
-            a.sync[3] = 0;
             __threadfence();
             a.sync[2] = 0;
         }

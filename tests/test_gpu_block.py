@@ -77,6 +77,26 @@ def test_block_qwen_dims(gpu, orc, be, synth, qwen_weights, T):
     assert gpu.last_block_status() == 0
 
 
+FUSED_SMALL = dict(hidden=512, experts=64, moe_inter=128, shared_inter=64,
+                   top_k=8)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("cfgname", ["small", "qwen"])
+def test_block_one_kernel_path(gpu, orc, be, synth, qwen_weights, cfgname, T):
+    """One to four tokens run as ONE cooperative launch; two calls in a row
+    (the second reuses the self-resetting counters)."""
+    cfg = FUSED_SMALL if cfgname == "small" else synth.QWEN_CFG
+    W = (synth.host_weights(be, cfg, seed=5, sigma=0.05) if cfgname == "small"
+         else qwen_weights)
+    for seed in (11, 12):
+        x = synth.host_x(be, T, cfg["hidden"], seed=seed + T)
+        got = gpu.moe_block(cfg, W, x)
+        assert gpu.last_block_launches() == 1
+        assert gpu.last_block_status() == 0
+        check_block(got, orc.moe_block(cfg, W, x), f"{cfgname} T={T}")
+
+
 def test_block_batched_equals_per_token(gpu, be, synth):
     """tests/m9c of the reference: the batched body equals the per-token body.
     Here: selected ids are identical and outputs agree to BF16 tolerance when
