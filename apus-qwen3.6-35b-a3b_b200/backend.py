@@ -63,7 +63,7 @@ SYMBOLS = [
     "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
-    "apus_cuda_fused_timeline",
+    "apus_cuda_fused_timeline", "apus_cuda_router_exact_chains",
     "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
     "apus_cuda_ep_finish_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
@@ -330,6 +330,10 @@ class Backend:
         if n < 0:
             return None
         return np.array(buf[:n], dtype=np.uint64).reshape(-1, 8)
+
+    def router_exact_chains(self):
+        self.lib.apus_cuda_router_exact_chains.restype = C.c_long
+        return int(self.lib.apus_cuda_router_exact_chains())
 
     def last_block_launches(self):
         return int(self.lib.apus_cuda_last_block_launches())

@@ -23,6 +23,7 @@
 
 #include "common.cuh"
 #include "decode_fused.cuh"
+#include "router_certify.cuh"
 #include "decode_gemv.cuh"
 #include "dispatch.cuh"
 #include "misc_kernels.cuh"
@@ -63,6 +64,7 @@ struct ApusCudaLayer {
              *sh_gate = nullptr;
     float wmin = 0.0f;          /* smallest nonzero |rtr_w| (0 = unknown) */
     float wmin_gate = 0.0f;     /* the same for the shared-gate row */
+    float *d_wnorm = nullptr;   /* [E + 1] router row norms (rounded up), [E] = max */
     size_t bytes = 0;
     PrefillMaps *maps = nullptr; /* tensor maps for the tcgen05 path */
 };
@@ -82,6 +84,8 @@ struct Ctx {
     unsigned int *d_scratch_u32 = nullptr;
     unsigned int *d_router_counters = nullptr;   /* [ROUTER_SMALL_MAX_T], self-resetting */
     float *d_router_logits = nullptr;            /* [ROUTER_SMALL_MAX_T][1024] */
+    int router_certify = 1;      /* many tokens: fast logits + exact chains for candidates */
+    unsigned int *d_rc_stats = nullptr;          /* [0] exact chains run so far */
     int decode_max_t = 4;        /* above this the tcgen05 grouped GEMM runs */
     int fused_max_t = 4;         /* up to this the one-kernel decode path runs */
     /* scratch of the fused decode kernel */
@@ -176,6 +180,9 @@ static int ctx_init() {
     long mb = env_long("APUS_CUDA_DENSE_MB", -1);
     c->budget = mb < 0 ? ~0ull : (uint64_t)mb << 20;
     c->decode_max_t = (int)env_long("APUS_CUDA_DECODE_MAX_T", 4);
+    c->router_certify = (int)env_long("APUS_CUDA_ROUTER_CERTIFY", 1);
+    CU_OK(cudaMalloc(&c->d_rc_stats, 64));
+    CU_OK(cudaMemset(c->d_rc_stats, 0, 64));
     c->fused_max_t = (int)env_long("APUS_CUDA_FUSED_MAX_T", DF_MAX_T);
     if (c->fused_max_t > DF_MAX_T) c->fused_max_t = DF_MAX_T;
     CU_OK(cudaMalloc(&c->d_df_logits, (size_t)DF_MAX_T * 1024 * sizeof(float)));
@@ -269,6 +276,7 @@ static void layer_free(ApusCudaLayer *L) {
                     L->sh_u,  L->sh_d,   L->sh_gate};
     for (void *p : ptrs)
         if (p) cudaFree(p);
+    if (L->d_wnorm) cudaFree(L->d_wnorm);
     if (L->maps) prefill_maps_free(L->maps);
     if (g_ctx && g_ctx->bytes_resident >= L->bytes)
         g_ctx->bytes_resident -= L->bytes;
@@ -289,6 +297,7 @@ extern "C" void apus_cuda_disable(void) {
     if (c->io.base) cudaFree(c->io.base);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_router_counters) cudaFree(c->d_router_counters);
+    if (c->d_rc_stats) cudaFree(c->d_rc_stats);
     if (c->d_df_logits) cudaFree(c->d_df_logits);
     if (c->d_df_sgl) cudaFree(c->d_df_sgl);
     if (c->d_df_sync) cudaFree(c->d_df_sync);
@@ -414,13 +423,64 @@ static int launch_router_tt(Ctx *c, const uint16_t *dx, const uint16_t *dwr,
     return 0;
 }
 
+/* optional inputs of the certified many-token path */
+struct RouterAux {
+    const float *wnorm;     /* [E + 1] row norms of the router matrix */
+    float wmin_extra;       /* smallest nonzero |extra_row| */
+    float *approx_ws;       /* [T, E] fp32 workspace */
+};
+
 static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
                          int E, int K, int topk, float wmin, int32_t *didx,
                          uint16_t *dw, uint16_t *dlogits,
                          const uint16_t *extra_row, uint16_t *extra_out,
-                         cudaStream_t st) {
+                         cudaStream_t st, const RouterAux *aux = nullptr) {
     if (E < 1 || E > 1024 || topk < 1 || topk > 32 || topk > E || K < 1)
         return fail("router: unsupported E=%d topk=%d K=%d", E, topk, K);
+    /* many tokens: fast logits on the tensor cores, exact chains only for the
+     * experts that can still reach the top_k (router_certify.cuh) */
+    if (c->router_certify && aux && aux->wnorm && aux->approx_ws && dlogits &&
+        T > ROUTER_SMALL_MAX_T && E % PG_BM == 0 && K % 256 == 0 &&
+        (((uintptr_t)dwr | (uintptr_t)dx | (uintptr_t)extra_row) & 15) == 0 &&
+        router_certify_smem(E, K) <= (size_t)c->smem_optin) {
+        if (run_dense_logits(c->sm_count, c->smem_optin, dwr, dx, T, E, K,
+                             aux->approx_ws, c->d_status, st,
+                             &c->last_block_launches))
+            return fail("%s", prefill_last_error());
+        c->launches++;
+        CertifyArgs ca;
+        memset(&ca, 0, sizeof ca);
+        ca.approx = aux->approx_ws;
+        ca.x = dx;
+        ca.w = dwr;
+        ca.extra_row = extra_row;
+        ca.wnorm = aux->wnorm;
+        ca.T = T; ca.E = E; ca.K = K; ca.topk = topk;
+        ca.wmin = wmin;
+        ca.wmin_extra = aux->wmin_extra;
+        /* the sequential chain errs by at most (K-1)u times the sum of the
+         * term magnitudes; the tensor cores are granted eight times that */
+        ca.cbound = 9.1f * (float)K * 5.9604645e-8f;
+        ca.logits = dlogits;
+        ca.extra_out = extra_out;
+        ca.status = c->d_status;
+        ca.stats = c->d_rc_stats;
+        const size_t smem = router_certify_smem(E, K);
+        static size_t set_smem = 0;
+        if (smem > set_smem) {
+            CU_OK(cudaFuncSetAttribute(router_certify_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+            set_smem = smem;
+        }
+        launch_k(router_certify_kernel, dim3((T + RC_TT - 1) / RC_TT), dim3(RC_THREADS),
+                 smem, st, ca);
+        LAUNCHED();
+        launch_k(router_select_kernel, dim3((T + 7) / 8), dim3(256),
+                 (size_t)8 * E * sizeof(float), st, dlogits, T, E, topk, didx, dw);
+        LAUNCHED();
+        return 0;
+    }
     /* few tokens: rows spread over many small CTAs, everything in flight at
      * once (latency path) */
     if (T <= ROUTER_SMALL_MAX_T && (K & 7) == 0 &&
@@ -543,6 +603,23 @@ static int min_nonzero(Ctx *c, const uint16_t *d, size_t n, float *out,
     float f;
     memcpy(&f, &bits, 4);
     *out = (bits >= 0x7f800000u) ? 0.0f : f;
+    return 0;
+}
+
+/* what the router kernels need to know about a layer's router weights: the
+ * smallest nonzero magnitudes (fused multiply-add guard) and the row norms
+ * (error bound of the fast logits) */
+static int layer_router_stats(Ctx *c, ApusCudaLayer *L) {
+    const size_t E = L->cfg.experts, H = L->cfg.hidden;
+    if (min_nonzero(c, L->rtr_w, E * H, &L->wmin, c->stream) ||
+        min_nonzero(c, L->sh_gate, H, &L->wmin_gate, c->stream))
+        return 1;
+    if (!L->d_wnorm) CU_OK(cudaMalloc(&L->d_wnorm, (E + 1) * sizeof(float)));
+    CU_OK(cudaMemsetAsync(L->d_wnorm, 0, (E + 1) * sizeof(float), c->stream));
+    row_norm_kernel<<<(unsigned)((E * 32 + 255) / 256), 256, 0, c->stream>>>(
+        L->rtr_w, (int)E, (int)H, L->d_wnorm);
+    LAUNCHED();
+    CU_OK(cudaStreamSynchronize(c->stream));
     return 0;
 }
 
@@ -696,8 +773,7 @@ extern "C" int apus_cuda_layer_create(const ApusCudaMoeCfg *cfg,
     c->bytes_resident += L->bytes;
     L->maps = nullptr;
     if (w && w->rtr_w) {
-        if (min_nonzero(c, L->rtr_w, E * H, &L->wmin, c->stream) ||
-            min_nonzero(c, L->sh_gate, H, &L->wmin_gate, c->stream)) {
+        if (layer_router_stats(c, L)) {
             layer_free(L);
             return 1;
         }
@@ -739,11 +815,7 @@ extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
     if (ctx_init()) return 1;
     /* set-up call: whatever stream filled the tensor, wait for it */
     CU_OK(cudaDeviceSynchronize());
-    if (min_nonzero(g_ctx, L->rtr_w, L->cfg.experts * L->cfg.hidden, &L->wmin,
-                    g_ctx->stream))
-        return 1;
-    return min_nonzero(g_ctx, L->sh_gate, L->cfg.hidden, &L->wmin_gate,
-                       g_ctx->stream);
+    return layer_router_stats(g_ctx, L);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -1013,8 +1085,11 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
               TK = (int)cfg.top_k;
     c->n_ev = 0;
     stage_mark(c, -1, st);
+    /* the fast logits live in the combine buffer, which is written much later */
+    RouterAux aux = {L->d_wnorm, L->wmin_gate, reinterpret_cast<float *>(b.eo)};
     if (launch_router(c, d_ln2, L->rtr_w, Ti, E, H, TK, L->wmin, b.idx, b.rw,
-                      b.logits, L->sh_gate, b.sgl, st))
+                      b.logits, L->sh_gate, b.sgl, st,
+                      (size_t)E * 4 <= (size_t)TK * H * 2 ? &aux : nullptr))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_ROUTER, st);
     if (prefill) {
@@ -1133,6 +1208,17 @@ extern "C" int apus_cuda_fused_timeline(unsigned long long *out, int cap) {
     return n;
 }
 
+extern "C" long apus_cuda_router_exact_chains(void) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_ctx) return -1;
+    unsigned int n = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(&n, g_ctx->d_rc_stats, sizeof n, cudaMemcpyDeviceToHost) !=
+        cudaSuccess)
+        return -1;
+    return (long)n;
+}
+
 extern "C" int apus_cuda_last_block_launches(void) {
     return g_ctx ? g_ctx->last_block_launches : 0;
 }
@@ -1237,12 +1323,13 @@ extern "C" int apus_cuda_ep_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t E = L->cfg.experts;
-    if (arena_reserve(c->ws, T * E * 2 + 4096)) return 1;
+    if (arena_reserve(c->ws, T * E * 6 + 8192)) return 1;
     c->ws.reset();
     uint16_t *logits = (uint16_t *)c->ws.take(T * E * 2);
+    RouterAux aux = {L->d_wnorm, L->wmin_gate, (float *)c->ws.take(T * E * 4)};
     return launch_router(c, d_x, L->rtr_w, (int)T, (int)E, (int)L->cfg.hidden,
                          (int)L->cfg.top_k, L->wmin, d_idx, d_w, logits,
-                         L->sh_gate, d_sgl, st);
+                         L->sh_gate, d_sgl, st, &aux);
 }
 
 /* gather kernel for the pack step: send_e[p] = idx[perm[p]] */
@@ -1392,11 +1479,17 @@ extern "C" int apus_cuda_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     if (!L || !d_x || !d_idx || !T) return fail("route_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
-    g_ctx->last_block_launches = 0;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
-    return launch_router(g_ctx, d_x, L->rtr_w, (int)T, (int)L->cfg.experts,
-                         (int)L->cfg.hidden, (int)L->cfg.top_k, L->wmin, d_idx,
-                         d_w, nullptr, nullptr, nullptr, st);
+    const size_t E = L->cfg.experts;
+    if (arena_reserve(c->ws, T * E * 6 + 8192)) return 1;
+    c->ws.reset();
+    uint16_t *logits = (uint16_t *)c->ws.take(T * E * 2);
+    RouterAux aux = {L->d_wnorm, 0.0f, (float *)c->ws.take(T * E * 4)};
+    return launch_router(c, d_x, L->rtr_w, (int)T, (int)E, (int)L->cfg.hidden,
+                         (int)L->cfg.top_k, L->wmin, d_idx, d_w, logits, nullptr,
+                         nullptr, st, &aux);
 }
 
 extern "C" int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T,

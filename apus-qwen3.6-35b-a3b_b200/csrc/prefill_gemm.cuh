@@ -275,9 +275,25 @@ struct GemmParams {
     int ld_routed, ld_shared;
     const int32_t *perm;   /* down: sorted position -> flat assignment */
     int *status;
+    /* MODE 2 (one dense weight matrix against every token row, fp32 out):
+     * tiles are generated from the index, no list */
+    int dense_T, dense_mt, dense_ntiles;
+    float *out_f32;        /* [dense_T, ld_f32] */
+    int ld_f32;
 };
 
-template <bool GATE_UP>
+/* the tile with this index: from the list, or (MODE 2) token tile major,
+ * weight-row tile minor, so tiles that share token rows are neighbours */
+template <int MODE>
+__device__ __forceinline__ int4 pg_tile(const GemmParams &p, int tile) {
+    if (MODE != 2) return __ldg(&p.tiles[tile]);
+    const int n = tile / p.dense_mt, m = tile - n * p.dense_mt;
+    return make_int4(p.E, m, n * PG_BN_GU, min(PG_BN_GU, p.dense_T - n * PG_BN_GU));
+}
+
+/* MODE 0: gate_up + SwiGLU;  1: down;  2: dense, fp32 accumulators stored as
+ * they are (the router's fast logits) */
+template <int MODE>
 __global__ void __launch_bounds__(PG_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapAs,    /* shared g | d */
@@ -286,8 +302,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
                     GemmParams p) {
     pdl_enter();
+    constexpr bool GATE_UP = MODE == 0;
     constexpr int STAGES = PG_STAGES;
-    constexpr int BN = GATE_UP ? PG_BN_GU : PG_BN_DN;
+    constexpr int BN = MODE == 1 ? PG_BN_DN : PG_BN_GU;
     constexpr int A_TILES = GATE_UP ? 2 : 1;
     constexpr int B_OFF = A_TILES * PG_TILE_BYTES;        /* B tile offset */
     constexpr int B_BYTES = BN * PG_BK * 2;
@@ -321,7 +338,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    const int n_tiles = *p.n_tiles;
+    const int n_tiles = MODE == 2 ? p.dense_ntiles : *p.n_tiles;
     const int num_kb = p.K / PG_BK;
 
     if (warp == 0) {
@@ -330,7 +347,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             uint32_t kiter = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
-                const int4 t = __ldg(&p.tiles[tile]);
+                const int4 t = pg_tile<MODE>(p, tile);
                 const bool shared = t.x == p.E;
                 const CUtensorMap *ma = shared ? &mapAs : &mapA;
                 const CUtensorMap *ma2 = shared ? &mapAs2 : &mapA;
@@ -364,7 +381,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             int it = 0;
             for (int tile = blockIdx.x; alive && tile < n_tiles;
                  tile += gridDim.x, it++) {
-                const int4 t = __ldg(&p.tiles[tile]);
+                const int4 t = pg_tile<MODE>(p, tile);
                 const int acc = it & 1;
                 const uint32_t aph = (uint32_t)(it >> 1) & 1u;
                 const int n = ((t.w + 15) >> 4) << 4;
@@ -415,7 +432,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         int it = 0;
         for (int tile = blockIdx.x; alive && tile < n_tiles;
              tile += gridDim.x, it++) {
-            const int4 t = __ldg(&p.tiles[tile]);
+            const int4 t = pg_tile<MODE>(p, tile);
             const bool shared = t.x == p.E;
             const int acc = it & 1;
             const uint32_t aph = (uint32_t)(it >> 1) & 1u;
@@ -448,6 +465,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                                        : silu_act_bits(gv, uv);
                         }
                     }
+                } else if (MODE == 2) {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (c0 + j < t.w)
+                            p.out_f32[(size_t)(t.z + c0 + j) * p.ld_f32 + col] =
+                                __uint_as_float(g[j]);
                 } else {
                     /* output row of each of this chunk's 32 columns: one load
                      * per lane, handed round by shuffle */
@@ -629,9 +653,9 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                      (size_t)(do_shared && T > 0 ? T : 1), Is, PG_BN_DN);
     if (bad) return 1;
 
-    cudaFuncSetAttribute(grouped_gemm_kernel<true>,
+    cudaFuncSetAttribute(grouped_gemm_kernel<0>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
-    cudaFuncSetAttribute(grouped_gemm_kernel<false>,
+    cudaFuncSetAttribute(grouped_gemm_kernel<1>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, s2);
     GemmParams p1;
     memset(&p1, 0, sizeof p1);
@@ -647,7 +671,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_routed = I;
     p1.ld_shared = Is;
     p1.status = status;
-    launch_k(grouped_gemm_kernel<true>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
+    launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
     GemmParams p2 = p1;
@@ -666,7 +690,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                  "tensor-core path needs shared_inter == moe_inter");
         return 1;
     }
-    launch_k(grouped_gemm_kernel<false>, dim3(sm_count), dim3(PG_THREADS), s2, st, maps->w_d, maps->sh_d, maps->sh_d, m_act, m_sa, p2);
+    launch_k(grouped_gemm_kernel<1>, dim3(sm_count), dim3(PG_THREADS), s2, st, maps->w_d, maps->sh_d, maps->sh_d, m_act, m_sa, p2);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_DOWN);
     cudaError_t e = cudaGetLastError();
@@ -675,6 +699,46 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                  cudaGetErrorString(e));
         return 1;
     }
+    return 0;
+}
+
+/* approx[T, E] = x[T, K] . w[E, K]^T on the tensor cores, fp32, any summation
+ * order: the router's fast logits.  E % 128 == 0, K % 64 == 0. */
+inline int run_dense_logits(int sm_count, int smem_optin, const uint16_t *w,
+                            const uint16_t *x, int T, int E, int K, float *out,
+                            int *status, cudaStream_t st, int *launches) {
+    PFN_encodeTiled_local enc = tensor_map_encoder();
+    if (!enc) return 1;
+    const int smem = PG_STAGES * 2 * PG_TILE_BYTES + 1024 + 256;
+    if (smem > smem_optin || E % PG_BM || K % PG_BK) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "dense logits GEMM: unsupported shape E=%d K=%d", E, K);
+        return 1;
+    }
+    CUtensorMap m_w, m_x;
+    if (encode_2d(enc, &m_w, w, (size_t)E, (size_t)K) ||
+        encode_2d(enc, &m_x, x, (size_t)T, (size_t)K))
+        return 1;
+    static bool set_ = false;
+    if (!set_) {
+        cudaFuncSetAttribute(grouped_gemm_kernel<2>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        set_ = true;
+    }
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.K = K;
+    p.E = E;
+    p.dense_T = T;
+    p.dense_mt = E / PG_BM;
+    p.dense_ntiles = ((T + PG_BN_GU - 1) / PG_BN_GU) * p.dense_mt;
+    p.out_f32 = out;
+    p.ld_f32 = E;
+    p.status = status;
+    const int grid = p.dense_ntiles < sm_count ? p.dense_ntiles : sm_count;
+    launch_k(grouped_gemm_kernel<2>, dim3(grid), dim3(PG_THREADS), (size_t)smem, st,
+             m_w, m_w, m_w, m_x, m_x, p);
+    (*launches)++;
     return 0;
 }
 

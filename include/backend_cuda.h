@@ -223,6 +223,13 @@ int apus_cuda_last_stage_ms(float *ms, int cap);
  * this copies out[cta*8 + mark] for the last call and returns the number of
  * values written, or -1 if the last call did not take that path. */
 int apus_cuda_fused_timeline(unsigned long long *out, int cap);
+/* Diagnostic for the many-token router: it scores every expert with a fast
+ * tensor-core product and walks the engine's exact sequential chain
+ * (c/moe.h:289-291) only for the experts whose fast logit, widened by a proven
+ * error bound, can still reach the top_k.  Returns how many exact chains have
+ * run since enable (256 per token would be the plain exact router), -1 when
+ * not enabled.  APUS_CUDA_ROUTER_CERTIFY=0 selects the plain exact router. */
+long apus_cuda_router_exact_chains(void);
 
 /* Device-side status word of the last block call: 0 = ok; nonzero = a
  * bounded wait inside a kernel gave up (the context stays usable). */

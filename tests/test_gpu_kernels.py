@@ -148,3 +148,72 @@ def test_dispatch_rejects_bad_expert_id(gpu):
     # the context stays usable
     c, o, p = gpu.moe_dispatch(np.array([[3, 1, 2, 0]], np.int32), 16)
     assert p.tolist() == [3, 1, 2, 0]
+
+
+# --- many-token router: fast logits + exact chains for the candidates ---------
+def _route_dev(gpu, synth, cfg, W, x):
+    """idx [T, TK], w [T, TK] from apus_cuda_route_dev on a resident layer."""
+    import torch
+    T = x.shape[0]
+    layer = gpu.layer_create(cfg, W)
+    d_x = torch.from_numpy(x.view(np.int16)).cuda()
+    d_idx = torch.full((T, cfg["top_k"]), -1, dtype=torch.int32, device="cuda")
+    d_w = torch.zeros((T, cfg["top_k"]), dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+    gpu.route_dev(layer, d_x.data_ptr(), T, d_idx.data_ptr(), d_w.data_ptr(),
+                  stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return d_idx.cpu().numpy(), d_w.cpu().numpy().view(np.uint16)
+
+
+CERT_CFG = dict(hidden=512, experts=128, moe_inter=128, shared_inter=128,
+                top_k=8)
+
+
+@pytest.mark.parametrize("T", [65, 257, 1000])
+@pytest.mark.parametrize("case", ["plain", "tied_rows", "tiny_logits", "skewed"])
+def test_router_certified_selection_is_exact(gpu, orc, be, synth, T, case):
+    """Above 64 tokens the router scores all experts on the tensor cores and
+    walks the exact chain only for experts that can still reach the top_k.
+    The selection must equal the exact router's bit for bit, also when rows of
+    the router matrix are identical (every logit tied with its neighbour), when
+    all logits are tiny, and when a few experts dominate."""
+    cfg = CERT_CFG
+    W = synth.host_weights(be, cfg, seed=900 + T, sigma=0.05)
+    x = synth.host_x(be, T, cfg["hidden"], seed=900 + T)
+    rtr = W["rtr_w"]
+    if case == "tied_rows":
+        rtr[1::2] = rtr[0::2]
+    elif case == "tiny_logits":
+        rtr[:] = synth.f32_to_bf16(synth.bf16_to_f32(rtr) * 2.0 ** -20)
+    elif case == "skewed":
+        W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=3))
+        rtr = W["rtr_w"]
+    before = gpu.router_exact_chains()
+    idx, w = _route_dev(gpu, synth, cfg, W, x)
+    chains = gpu.router_exact_chains() - before
+    assert gpu.last_block_status() == 0          # includes the error-bound check
+    eidx, ew = orc.route_batch(x, rtr, cfg["top_k"])
+    assert np.array_equal(idx, eidx)
+    d = np.abs(w.astype(np.int32) - ew.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() <= 0.002
+    # the certified path ran, and it ran far fewer chains than E per token
+    assert cfg["top_k"] * T <= chains
+    if case in ("plain", "skewed"):
+        assert chains <= 4 * cfg["top_k"] * T
+
+
+def test_router_certified_can_be_switched_off(be, orc, synth, monkeypatch):
+    monkeypatch.setenv("APUS_CUDA_ROUTER_CERTIFY", "0")
+    be.enable()
+    try:
+        cfg = CERT_CFG
+        W = synth.host_weights(be, cfg, seed=77, sigma=0.05)
+        x = synth.host_x(be, 130, cfg["hidden"], seed=77)
+        before = be.router_exact_chains()
+        idx, w = _route_dev(be, synth, cfg, W, x)
+        assert be.router_exact_chains() == before
+        eidx, _ = orc.route_batch(x, W["rtr_w"], cfg["top_k"])
+        assert np.array_equal(idx, eidx)
+    finally:
+        be.disable()
