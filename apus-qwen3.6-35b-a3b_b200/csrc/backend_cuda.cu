@@ -427,7 +427,8 @@ static int launch_router_tt(Ctx *c, const uint16_t *dx, const uint16_t *dwr,
 struct RouterAux {
     const float *wnorm;     /* [E + 1] row norms of the router matrix */
     float wmin_extra;       /* smallest nonzero |extra_row| */
-    float *approx_ws;       /* [T, E] fp32 workspace */
+    float *approx_ws;       /* fp32 workspace, at least T*E*4 bytes */
+    size_t approx_bytes;    /* its size: up to four [T, E] slabs are used */
 };
 
 static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
@@ -443,7 +444,9 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         T > ROUTER_SMALL_MAX_T && E % PG_BM == 0 && K % 256 == 0 &&
         (((uintptr_t)dwr | (uintptr_t)dx | (uintptr_t)extra_row) & 15) == 0 &&
         router_certify_smem(E, K) <= (size_t)c->smem_optin) {
-        if (run_dense_logits(c->sm_count, c->smem_optin, dwr, dx, T, E, K,
+        int ksplit = dense_logits_ksplit(c->sm_count, T, E, K);
+        while (ksplit > 1 && (size_t)ksplit * T * E * 4 > aux->approx_bytes) ksplit /= 2;
+        if (run_dense_logits(c->sm_count, c->smem_optin, dwr, dx, T, E, K, ksplit,
                              aux->approx_ws, c->d_status, st,
                              &c->last_block_launches))
             return fail("%s", prefill_last_error());
@@ -451,6 +454,7 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         CertifyArgs ca;
         memset(&ca, 0, sizeof ca);
         ca.approx = aux->approx_ws;
+        ca.nslab = ksplit;
         ca.x = dx;
         ca.w = dwr;
         ca.extra_row = extra_row;
@@ -1086,7 +1090,8 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     c->n_ev = 0;
     stage_mark(c, -1, st);
     /* the fast logits live in the combine buffer, which is written much later */
-    RouterAux aux = {L->d_wnorm, L->wmin_gate, reinterpret_cast<float *>(b.eo)};
+    RouterAux aux = {L->d_wnorm, L->wmin_gate, reinterpret_cast<float *>(b.eo),
+                     (size_t)Ti * TK * H * 2};
     if (launch_router(c, d_ln2, L->rtr_w, Ti, E, H, TK, L->wmin, b.idx, b.rw,
                       b.logits, L->sh_gate, b.sgl, st,
                       (size_t)E * 4 <= (size_t)TK * H * 2 ? &aux : nullptr))
@@ -1323,10 +1328,11 @@ extern "C" int apus_cuda_ep_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t E = L->cfg.experts;
-    if (arena_reserve(c->ws, T * E * 6 + 8192)) return 1;
+    if (arena_reserve(c->ws, T * E * 18 + 8192)) return 1;
     c->ws.reset();
     uint16_t *logits = (uint16_t *)c->ws.take(T * E * 2);
-    RouterAux aux = {L->d_wnorm, L->wmin_gate, (float *)c->ws.take(T * E * 4)};
+    RouterAux aux = {L->d_wnorm, L->wmin_gate, (float *)c->ws.take(T * E * 16),
+                     T * E * 16};
     return launch_router(c, d_x, L->rtr_w, (int)T, (int)E, (int)L->cfg.hidden,
                          (int)L->cfg.top_k, L->wmin, d_idx, d_w, logits,
                          L->sh_gate, d_sgl, st, &aux);
@@ -1483,10 +1489,10 @@ extern "C" int apus_cuda_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t E = L->cfg.experts;
-    if (arena_reserve(c->ws, T * E * 6 + 8192)) return 1;
+    if (arena_reserve(c->ws, T * E * 18 + 8192)) return 1;
     c->ws.reset();
     uint16_t *logits = (uint16_t *)c->ws.take(T * E * 2);
-    RouterAux aux = {L->d_wnorm, 0.0f, (float *)c->ws.take(T * E * 4)};
+    RouterAux aux = {L->d_wnorm, 0.0f, (float *)c->ws.take(T * E * 16), T * E * 16};
     return launch_router(c, d_x, L->rtr_w, (int)T, (int)E, (int)L->cfg.hidden,
                          (int)L->cfg.top_k, L->wmin, d_idx, d_w, logits, nullptr,
                          nullptr, st, &aux);

@@ -277,18 +277,19 @@ struct GemmParams {
     int *status;
     /* MODE 2 (one dense weight matrix against every token row, fp32 out):
      * tiles are generated from the index, no list */
-    int dense_T, dense_mt, dense_ntiles;
-    float *out_f32;        /* [dense_T, ld_f32] */
+    int dense_T, dense_mt, dense_ntiles, dense_ksplit;
+    float *out_f32;        /* [dense_ksplit][dense_T, ld_f32]: one slab per K slice */
     int ld_f32;
 };
 
-/* the tile with this index: from the list, or (MODE 2) token tile major,
- * weight-row tile minor, so tiles that share token rows are neighbours */
+/* the tile with this index: from the list, or (MODE 2) generated: token tile
+ * major, then weight-row tile, then K slice (in .x); p.K is the slice length */
 template <int MODE>
 __device__ __forceinline__ int4 pg_tile(const GemmParams &p, int tile) {
     if (MODE != 2) return __ldg(&p.tiles[tile]);
-    const int n = tile / p.dense_mt, m = tile - n * p.dense_mt;
-    return make_int4(p.E, m, n * PG_BN_GU, min(PG_BN_GU, p.dense_T - n * PG_BN_GU));
+    const int ks = tile % p.dense_ksplit, r = tile / p.dense_ksplit;
+    const int n = r / p.dense_mt, m = r - n * p.dense_mt;
+    return make_int4(ks, m, n * PG_BN_GU, min(PG_BN_GU, p.dense_T - n * PG_BN_GU));
 }
 
 /* MODE 0: gate_up + SwiGLU;  1: down;  2: dense, fp32 accumulators stored as
@@ -348,7 +349,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
                 const int4 t = pg_tile<MODE>(p, tile);
-                const bool shared = t.x == p.E;
+                const bool shared = MODE == 2 || t.x == p.E;
+                const int kb0 = MODE == 2 ? t.x * num_kb : 0;   /* K slice */
                 const CUtensorMap *ma = shared ? &mapAs : &mapA;
                 const CUtensorMap *ma2 = shared ? &mapAs2 : &mapA;
                 const CUtensorMap *mb = shared ? &mapBs : &mapB;
@@ -365,11 +367,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(st, ma, kb * PG_BK, arow, &full[s]);
+                    tma_load_2d(st, ma, (kb0 + kb) * PG_BK, arow, &full[s]);
                     if (GATE_UP)
                         tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
                                     &full[s]);
-                    tma_load_2d(st + B_OFF, mb, kb * PG_BK, t.z, &full[s]);
+                    tma_load_2d(st + B_OFF, mb, (kb0 + kb) * PG_BK, t.z, &full[s]);
                 }
             }
         }
@@ -433,7 +435,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         for (int tile = blockIdx.x; alive && tile < n_tiles;
              tile += gridDim.x, it++) {
             const int4 t = pg_tile<MODE>(p, tile);
-            const bool shared = t.x == p.E;
+            const bool shared = MODE == 2 || t.x == p.E;
             const int acc = it & 1;
             const uint32_t aph = (uint32_t)(it >> 1) & 1u;
             if (!pg_wait(&tfull[acc], aph, abort_flag, p.status,
@@ -470,8 +472,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
 #pragma unroll
                     for (int j = 0; j < 32; j++)
                         if (c0 + j < t.w)
-                            p.out_f32[(size_t)(t.z + c0 + j) * p.ld_f32 + col] =
-                                __uint_as_float(g[j]);
+                            p.out_f32[((size_t)t.x * p.dense_T + t.z + c0 + j) * p.ld_f32 +
+                                      col] = __uint_as_float(g[j]);
                 } else {
                     /* output row of each of this chunk's 32 columns: one load
                      * per lane, handed round by shuffle */
@@ -702,11 +704,21 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     return 0;
 }
 
-/* approx[T, E] = x[T, K] . w[E, K]^T on the tensor cores, fp32, any summation
- * order: the router's fast logits.  E % 128 == 0, K % 64 == 0. */
+/* How many K slices the dense logits GEMM uses for T tokens: few token tiles
+ * would leave most SMs idle behind a long serial K loop. */
+inline int dense_logits_ksplit(int sm_count, int T, int E, int K) {
+    const int tiles = ((T + PG_BN_GU - 1) / PG_BN_GU) * (E / PG_BM);
+    int s = 1;
+    while (s < 4 && tiles * s * 2 <= sm_count && (K / PG_BK) % (s * 2) == 0) s *= 2;
+    return s;
+}
+
+/* out[s][T, E] = x[T, Ks] . w[E, Ks]^T per K slice s on the tensor cores, fp32,
+ * any summation order: the router's fast logits are the sum of the slabs.
+ * E % 128 == 0, K % 64 == 0. */
 inline int run_dense_logits(int sm_count, int smem_optin, const uint16_t *w,
-                            const uint16_t *x, int T, int E, int K, float *out,
-                            int *status, cudaStream_t st, int *launches) {
+                            const uint16_t *x, int T, int E, int K, int ksplit,
+                            float *out, int *status, cudaStream_t st, int *launches) {
     PFN_encodeTiled_local enc = tensor_map_encoder();
     if (!enc) return 1;
     const int smem = PG_STAGES * 2 * PG_TILE_BYTES + 1024 + 256;
@@ -727,11 +739,12 @@ inline int run_dense_logits(int sm_count, int smem_optin, const uint16_t *w,
     }
     GemmParams p;
     memset(&p, 0, sizeof p);
-    p.K = K;
+    p.K = K / ksplit;
     p.E = E;
     p.dense_T = T;
     p.dense_mt = E / PG_BM;
-    p.dense_ntiles = ((T + PG_BN_GU - 1) / PG_BN_GU) * p.dense_mt;
+    p.dense_ksplit = ksplit;
+    p.dense_ntiles = ((T + PG_BN_GU - 1) / PG_BN_GU) * p.dense_mt * ksplit;
     p.out_f32 = out;
     p.ld_f32 = E;
     p.status = status;

@@ -50,9 +50,11 @@ constexpr int RC_AHEAD = 3;         /* row blocks requested ahead of the one in 
 constexpr int RC_NBUF = RC_AHEAD + 1;
 constexpr int RC_WPITCH = RC_BLK * 2 + 16;   /* bytes per staged row block */
 constexpr int ST_BOUND_VIOLATED = 5;
+constexpr int RC_MAX_SLABS = 4;     /* K slices of the fast-logit GEMM */
 
 struct CertifyArgs {
-    const float *approx;            /* [T, E] fast logits */
+    const float *approx;            /* [nslab][T, E]: the fast logits are the sum */
+    int nslab;
     const uint16_t *x, *w;          /* [T, K], [E, K] */
     const uint16_t *extra_row;      /* [K] shared-gate row (optional) */
     const float *wnorm;             /* [E + 1]: ||w_e||_2 rounded up; [E] = their max */
@@ -261,7 +263,13 @@ router_certify_kernel(CertifyArgs a) {
 #pragma unroll
             for (int c = 0; c < 8; c++) {
                 const int e = e0 + c * 32 + lane;
-                av[c] = e < E ? __ldg(&a.approx[(size_t)t * E + e]) : 0.0f;
+                float part[RC_MAX_SLABS];
+#pragma unroll
+                for (int sl = 0; sl < RC_MAX_SLABS; sl++)
+                    part[sl] = (e < E && sl < a.nslab)
+                                   ? __ldg(&a.approx[((size_t)sl * T + t) * E + e])
+                                   : 0.0f;
+                av[c] = (part[0] + part[1]) + (part[2] + part[3]);
             }
 #pragma unroll
             for (int c = 0; c < 8; c++) {
