@@ -73,10 +73,26 @@ rmsnorm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
     for (int i = lane; i < N; i += 32)
         row[i] = bf16_f32(x[(size_t)t * N + i]);
     __syncwarp();
+    /* the reference's sum of squares is one ascending fp32 chain; the dependent
+     * add is the critical path, so operands come in vectors, sixteen steps per
+     * iteration, and the next iteration's loads are hoisted above the adds */
     float ss = 0.0f;
-    if (lane == 0)
-        for (int i = 0; i < N; i++)
-            ss = __fadd_rn(ss, __fmul_rn(row[i], row[i]));
+    if (lane == 0) {
+        int i = 0;
+        const float4 *r4 = reinterpret_cast<const float4 *>(row);
+#pragma unroll 2
+        for (; (N & 3) == 0 && i + 16 <= N; i += 16) {   /* rows stay 16-byte aligned */
+            const float4 v[4] = {r4[i / 4], r4[i / 4 + 1], r4[i / 4 + 2], r4[i / 4 + 3]};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                ss = __fadd_rn(ss, __fmul_rn(v[q].x, v[q].x));
+                ss = __fadd_rn(ss, __fmul_rn(v[q].y, v[q].y));
+                ss = __fadd_rn(ss, __fmul_rn(v[q].z, v[q].z));
+                ss = __fadd_rn(ss, __fmul_rn(v[q].w, v[q].w));
+            }
+        }
+        for (; i < N; i++) ss = __fadd_rn(ss, __fmul_rn(row[i], row[i]));
+    }
     ss = __shfl_sync(0xffffffffu, ss, 0);
     const float rs = __fdiv_rn(
         1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)N), 1e-6f)));

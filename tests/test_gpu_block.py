@@ -125,6 +125,36 @@ def test_block_skewed_router(gpu, orc, be, synth):
     assert load.max() > 4 * load.mean()
 
 
+@pytest.mark.parametrize("skew", [False, True])
+def test_block_full_size_rows_match_the_checker(gpu, orc, be, synth,
+                                                qwen_weights, skew):
+    """Benchmark configuration 3's shape on one GPU: 8192 tokens at the real
+    dimensions, uniform and Zipf(1.1)-skewed routing.  Every token's result
+    depends on that token alone, so the CPU checker runs on a seeded sample of
+    rows (the full batch would take it minutes) and must agree with the rows of
+    the full-size GPU call; the dispatch of the full batch is checked through
+    its defining property."""
+    cfg = synth.QWEN_CFG
+    T = 8192
+    W = qwen_weights
+    x = synth.host_x(be, T, cfg["hidden"], seed=31)
+    if skew:
+        W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=31))
+    got = gpu.moe_block(cfg, W, x)
+    assert gpu.last_block_status() == 0
+    rows = np.sort(np.random.default_rng(31).choice(T, 96, replace=False))
+    exp = orc.moe_block(cfg, W, x[rows])
+    check_block({k: got[k][rows] for k in ("idx", "w", "routed", "shared", "out")},
+                exp, f"T={T} skew={skew}")
+    load = np.bincount(got["idx"].ravel(), minlength=cfg["experts"])
+    assert load.sum() == T * cfg["top_k"]
+    if skew:
+        assert load.max() > 8 * load.mean()
+    counts, offsets, perm = gpu.moe_dispatch(got["idx"], cfg["experts"])
+    assert np.array_equal(perm, np.argsort(got["idx"].ravel(), kind="stable"))
+    assert np.array_equal(counts, load)
+
+
 def test_block_rejects_bad_arguments(gpu, be, synth):
     cfg = dict(synth.MINI_CFG)
     W = synth.host_weights(be, cfg, seed=1, sigma=0.08)

@@ -217,3 +217,30 @@ def test_router_certified_can_be_switched_off(be, orc, synth, monkeypatch):
         assert np.array_equal(idx, eidx)
     finally:
         be.disable()
+
+
+# --- the callers either side of the block: rmsnorm before, residual add after ---
+@pytest.mark.parametrize("T,N", [(1, 2048), (5, 2048), (33, 512), (3, 130), (2, 24)])
+def test_rmsnorm_and_residual_add_bitwise(gpu, orc, be, synth, T, N):
+    """apus_cuda_rmsnorm_dev / apus_cuda_resadd_dev against the checker
+    (c/attn.h:175-186 with its sequential sum of squares; c/layer.h:230-234):
+    bit for bit, with and without a gain vector, rows that are not a multiple
+    of the vector width included."""
+    import torch
+    x = synth.f32_to_bf16(
+        synth.bf16_to_f32(be.synth_fill_host(T * N, 5, 0, 0, 1.0)).reshape(T, N) * 3.0)
+    gw = be.synth_fill_host(N, 5, 1, 1, 0.3)
+    sp = torch.cuda.current_stream().cuda_stream
+    d_x = torch.from_numpy(x.view(np.int16)).cuda()
+    d_w = torch.from_numpy(gw.view(np.int16)).cuda()
+    d_y = torch.empty_like(d_x)
+    for w_dev, w_host in ((d_w, gw), (None, None)):
+        gpu.rmsnorm_dev(d_x.data_ptr(), w_dev.data_ptr() if w_dev is not None else None,
+                        d_y.data_ptr(), T, N, stream=sp)
+        torch.cuda.synchronize()
+        assert np.array_equal(d_y.cpu().numpy().view(np.uint16), orc.rmsnorm(x, w_host))
+    b = be.synth_fill_host(T * N, 6, 0, 0, 1.0).reshape(T, N)
+    d_b = torch.from_numpy(b.view(np.int16)).cuda()
+    gpu.resadd_dev(d_x.data_ptr(), d_b.data_ptr(), d_y.data_ptr(), T * N, stream=sp)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_y.cpu().numpy().view(np.uint16), orc.resadd(x, b))
