@@ -49,7 +49,8 @@ constexpr int PG_BN_GU = 128;     /* token rows per gate_up tile (MMA N, max) */
 constexpr int PG_BN_DN = 256;     /* token rows per down tile: one accumulator
                                    * per tile, so twice the columns fit TMEM and
                                    * every weight tile is fetched half as often */
-constexpr int PG_BN = PG_BN_GU;   /* sizing of the tile lists (the finer one) */
+constexpr int PG_BN_MIN = 32;     /* narrowest token box of a routed tile */
+constexpr int PG_BN = PG_BN_MIN;  /* sizing of the tile lists (the finest one) */
 constexpr int PG_BK = 64;         /* K elements per stage = one 128B swizzle row */
 constexpr int PG_EPI_WARPS = 8;   /* two per TMEM lane quarter */
 constexpr int PG_THREADS = 64 + PG_EPI_WARPS * 32;
@@ -179,7 +180,7 @@ struct TileLists {
 };
 
 inline size_t prefill_max_ntiles(size_t A, size_t T, size_t E) {
-    return A / PG_BN + E + (T + PG_BN - 1) / PG_BN + 1;
+    return A / PG_BN + E + (T + PG_BN_GU - 1) / PG_BN_GU + 1;
 }
 inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
                                       size_t T) {
@@ -192,13 +193,13 @@ inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
 __global__ void __launch_bounds__(1024)
 build_tiles_kernel(const int32_t *__restrict__ counts,
                    const int32_t *__restrict__ offsets, int E, int T, int m_gu,
-                   int m_gu_sh, int m_dn, TileLists tl) {
+                   int m_gu_sh, int m_dn, int bn_gu, int bn_dn, TileLists tl) {
     pdl_enter();
     __shared__ int warp_tot[2][32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cnt = tid < E ? counts[tid] : 0;
-    const int nt_a = (cnt + PG_BN_GU - 1) / PG_BN_GU;
-    const int nt_b = (cnt + PG_BN_DN - 1) / PG_BN_DN;
+    const int nt_a = (cnt + bn_gu - 1) / bn_gu;
+    const int nt_b = (cnt + bn_dn - 1) / bn_dn;
     int inc_a = nt_a, inc_b = nt_b;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -220,13 +221,14 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
         for (int m = 0; m < m_gu; m++)
             for (int n = 0; n < nt_a; n++)
                 tl.gu[(size_t)first_a * m_gu + (size_t)m * nt_a + n] = make_int4(
-                    tid, m, off + n * PG_BN_GU, min(PG_BN_GU, cnt - n * PG_BN_GU));
+                    tid, m, off + n * bn_gu, min(bn_gu, cnt - n * bn_gu));
         for (int m = 0; m < m_dn; m++)
             for (int n = 0; n < nt_b; n++)
                 tl.dn[(size_t)first_b * m_dn + (size_t)m * nt_b + n] = make_int4(
-                    tid, m, off + n * PG_BN_DN, min(PG_BN_DN, cnt - n * PG_BN_DN));
+                    tid, m, off + n * bn_dn, min(bn_dn, cnt - n * bn_dn));
     }
     /* shared expert: dense over all T tokens */
+    /* the shared expert is dense over the tokens: always full-width tiles */
     const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
     for (int i = tid; i < nts_a * m_gu_sh; i += blockDim.x) {
         int m = i / nts_a, n = i - m * nts_a;
@@ -275,6 +277,9 @@ struct GemmParams {
     int ld_routed, ld_shared;
     const int32_t *perm;   /* down: sorted position -> flat assignment */
     int *status;
+    int bn_rows;           /* token rows a routed tile's TMA box fetches (<= BN):
+                            * experts with a handful of rows should not pull a
+                            * full-width box of their neighbours' rows through L2 */
     /* MODE 2 (one dense weight matrix against every token row, fp32 out):
      * tiles are generated from the index, no list */
     int dense_T, dense_mt, dense_ntiles, dense_ksplit;
@@ -357,6 +362,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                 const int arow =
                     (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) + t.y * PG_BM;
                 const int arow2 = shared ? arow : arow + p.up_off;
+                const int brows = (MODE == 2 || shared) ? BN : p.bn_rows;   /* box of mb */
                 for (int kb = 0; kb < num_kb; kb++, kiter++) {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
@@ -366,7 +372,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                         break;
                     }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    mbar_expect_tx(&full[s], (uint32_t)(B_OFF + brows * PG_BK * 2));
                     tma_load_2d(st, ma, (kb0 + kb) * PG_BK, arow, &full[s]);
                     if (GATE_UP)
                         tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
@@ -629,9 +635,16 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     tl.dn = tl.gu + nt * m1;
     tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * m_dn);
     tl.n_dn = tl.n_gu + 1;
+    /* token box of the routed tiles: about twice the mean row count of an
+     * expert, so that nearly every expert is one tile and a tile does not pull
+     * rows it will not use through L2 */
+    int want = PG_BN_MIN;
+    while (want < PG_BN_DN && (long)want * E < 2L * A) want *= 2;
+    const int bn_gu = want < PG_BN_GU ? want : PG_BN_GU;
+    const int bn_dn = want < PG_BN_DN ? want : PG_BN_DN;
     launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, d.counts, d.offsets, E,
                                            do_shared ? T : 0, m_gu, m_gu_sh, m_dn,
-                                           tl);
+                                           bn_gu, bn_dn, tl);
     (*launches)++;
     /* permuted activation rows */
     if (A > 0) {
@@ -647,10 +660,10 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     CUtensorMap m_xg, m_x, m_act, m_sa;
     int bad = 0;
     bad |= encode_2d(maps->encode, &m_xg, A > 0 ? (const void *)xg : (const void *)x,
-                     (size_t)(A > 0 ? A : 1), H);
+                     (size_t)(A > 0 ? A : 1), H, bn_gu);
     bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H);
     bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
-                     (size_t)(A > 0 ? A : 1), I, PG_BN_DN);
+                     (size_t)(A > 0 ? A : 1), I, bn_dn);
     bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
                      (size_t)(do_shared && T > 0 ? T : 1), Is, PG_BN_DN);
     if (bad) return 1;
@@ -673,6 +686,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_routed = I;
     p1.ld_shared = Is;
     p1.status = status;
+    p1.bn_rows = bn_gu;
     launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
@@ -687,6 +701,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_routed = H;
     p2.ld_shared = H;
     p2.perm = d.perm;
+    p2.bn_rows = bn_dn;
     if (Is != I) {
         snprintf(g_prefill_err, sizeof g_prefill_err,
                  "tensor-core path needs shared_inter == moe_inter");

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 
 
-def run(args, cfg, config, pkg, synth, metric, unit, peaks):
+def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     from . import ep
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -42,6 +42,10 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks):
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+    sampler = None
+    if rank == 0 and clock_sampler is not None:
+        sampler = clock_sampler(local)       # SM clock and throttle reasons of GPU 0
+        sampler.start()
     dist.barrier()
     torch.cuda.synchronize()
     e0 = torch.cuda.Event(enable_timing=True)
@@ -77,6 +81,9 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks):
                         dtype=torch.float64, device="cuda")
     dist.all_reduce(rows, op=dist.ReduceOp.SUM)
     dist.all_reduce(launches, op=dist.ReduceOp.SUM)
+    if sampler is not None:
+        sampler.stop_flag = True
+        sampler.join()
     if rank == 0:
         Tg = T * world
         cfgline = dict(config)
@@ -101,5 +108,19 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks):
                          "collective": "all_to_all_single (NCCL), rows as bytes"},
             "block": {"device_status": status},
         }
+        if sampler is not None:
+            line["clocks"] = sampler.summary()
+        # what one GPU must read per step: its experts (all touched at these
+        # sizes), the shared expert, the router, its token slice in and out
+        I, Is = cfg["moe_inter"], cfg["shared_inter"]
+        per_gpu = ((per * 3 * I * H + 3 * Is * H + E * H + H) * 2
+                   + 2 * T * H * 2 + 2 * float(rows[0]) / world * H * 2)
+        ach = per_gpu / (ms * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "whole step on one GPU (all "
+                            "kernels + NCCL all-to-all)", "achieved": ach,
+                            "peak": peaks["hbm_gbs"], "peak_source": peaks["_source"],
+                            "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                            "traffic": None,
+                            "algorithmic_bytes_per_launch": per_gpu}
         print(json.dumps(line))
     dist.destroy_process_group()

@@ -369,7 +369,7 @@ def main():
     import torch
     if world > 1:
         from apus_b200 import ep_bench
-        ep_bench.run(args, cfg, config, pkg, synth, METRIC, UNIT, peaks())
+        ep_bench.run(args, cfg, config, pkg, synth, METRIC, UNIT, peaks(), ClockSampler)
         return
 
     # small token counts touch few experts: one layer's working set would sit
