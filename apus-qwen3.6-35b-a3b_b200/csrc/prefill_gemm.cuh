@@ -23,13 +23,17 @@
  *             epilogue: y = rnd(D), stored at row perm[r] of the flat
  *             assignment-ordered buffer (the engine's eo, c/layer.h:618)
  *
- * One persistent CTA per SM, 6 warps: warp 0 issues TMA loads into a
+ * One persistent CTA per SM, 10 warps: warp 0 issues TMA loads into a
  * shared-memory ring (128B-swizzled K-major tiles, no multicast), warp 1
  * issues the MMAs and owns the 512 TMEM columns (two accumulator stages), warps
- * 2-5 drain accumulators (tcgen05.ld) and run the epilogue while the next
- * tile's MMAs proceed.  Every wait is bounded; a wait that runs out raises an
- * abort flag, records a status code, and every role falls through to the
- * common exit where TMEM is released.
+ * 2-9 drain accumulators (tcgen05.ld, two warps per TMEM lane quarter) and run
+ * the epilogue while the next tile's MMAs proceed.  Every wait is bounded; a
+ * wait that runs out raises an abort flag, records a status code, and every
+ * role falls through to the common exit where TMEM is released.
+ *
+ * A third mode of the same kernel multiplies one dense weight matrix with
+ * every token row and stores the fp32 accumulators as they are: the router's
+ * fast logits (router_certify.cuh).
  */
 #pragma once
 #include <cuda.h>
