@@ -197,8 +197,7 @@ inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
 __global__ void __launch_bounds__(1024)
 build_tiles_kernel(const int32_t *__restrict__ counts,
                    const int32_t *__restrict__ offsets, int E, int T, int m_gu,
-                   int m_gu_sh, int m_dn, int bn_gu, int bn_dn, int bn_dn_sh,
-                   TileLists tl) {
+                   int m_gu_sh, int m_dn, int bn_gu, int bn_dn, TileLists tl) {
     pdl_enter();
     __shared__ int warp_tot[2][32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -234,7 +233,7 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
     }
     /* shared expert: dense over all T tokens */
     /* the shared expert is dense over the tokens: always full-width tiles */
-    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + bn_dn_sh - 1) / bn_dn_sh;
+    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
     for (int i = tid; i < nts_a * m_gu_sh; i += blockDim.x) {
         int m = i / nts_a, n = i - m * nts_a;
         tl.gu[(size_t)total_a * m_gu + i] =
@@ -243,7 +242,7 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
     for (int i = tid; i < nts_b * m_dn; i += blockDim.x) {
         int m = i / nts_b, n = i - m * nts_b;
         tl.dn[(size_t)total_b * m_dn + i] =
-            make_int4(E, m, n * bn_dn_sh, min(bn_dn_sh, T - n * bn_dn_sh));
+            make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
     }
     if (tid == 0) {
         *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
@@ -282,11 +281,6 @@ struct GemmParams {
     int ld_routed, ld_shared;
     const int32_t *perm;   /* down: sorted position -> flat assignment */
     int *status;
-    int nacc;              /* accumulator stages in TMEM: 2 of 256 columns, or (down,
-                            * no tile wider than 128 token rows) 4 of 128 — a down
-                            * tile is only eight k-blocks long, and with two stages
-                            * its epilogue holds up the MMAs of the tile after next */
-    int bn_shared;         /* token rows of a shared-expert tile's TMA box */
     int bn_rows;           /* token rows a routed tile's TMA box fetches (<= BN):
                             * experts with a handful of rows should not pull a
                             * full-width box of their neighbours' rows through L2 */
@@ -332,8 +326,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         (reinterpret_cast<uintptr_t>(pg_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
     uint64_t *full = bars, *empty = bars + STAGES;
-    uint64_t *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 4;
-    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 8);
+    uint64_t *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -342,7 +336,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int a = 0; a < 4; a++) {
+        for (int a = 0; a < 2; a++) {
             mbar_init(&tfull[a], 1);
             mbar_init(&tempty[a], PG_EPI_WARPS * 32);
         }
@@ -355,8 +349,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
     const int n_tiles = MODE == 2 ? p.dense_ntiles : *p.n_tiles;
-    const int nacc = (MODE == 1 && p.nacc == 4) ? 4 : 2;
-    const uint32_t acc_cols = 512u / (uint32_t)nacc;
     const int num_kb = p.K / PG_BK;
 
     if (warp == 0) {
@@ -374,7 +366,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                 const int arow =
                     (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) + t.y * PG_BM;
                 const int arow2 = shared ? arow : arow + p.up_off;
-                const int brows = MODE == 2 ? BN : (shared ? p.bn_shared : p.bn_rows);
+                const int brows = (MODE == 2 || shared) ? BN : p.bn_rows;   /* box of mb */
                 for (int kb = 0; kb < num_kb; kb++, kiter++) {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
@@ -402,8 +394,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             for (int tile = blockIdx.x; alive && tile < n_tiles;
                  tile += gridDim.x, it++) {
                 const int4 t = pg_tile<MODE>(p, tile);
-                const int acc = it % nacc;
-                const uint32_t aph = (uint32_t)(it / nacc) & 1u;
+                const int acc = it & 1;
+                const uint32_t aph = (uint32_t)(it >> 1) & 1u;
                 const int n = ((t.w + 15) >> 4) << 4;
                 const uint32_t idesc = umma_idesc(n);
                 if (!pg_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status,
@@ -412,7 +404,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d0 = tmem_base + (uint32_t)acc * acc_cols;
+                const uint32_t d0 = tmem_base + (uint32_t)acc * 256u;
                 for (int kb = 0; kb < num_kb; kb++, kiter++) {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
@@ -454,8 +446,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
              tile += gridDim.x, it++) {
             const int4 t = pg_tile<MODE>(p, tile);
             const bool shared = MODE == 2 || t.x == p.E;
-            const int acc = it % nacc;
-            const uint32_t aph = (uint32_t)(it / nacc) & 1u;
+            const int acc = it & 1;
+            const uint32_t aph = (uint32_t)(it >> 1) & 1u;
             if (!pg_wait(&tfull[acc], aph, abort_flag, p.status,
                          ST_TMEM_TIMEOUT)) {
                 alive = false;
@@ -463,7 +455,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             }
             tc_fence_after();
             const uint32_t taddr =
-                tmem_base + (uint32_t)acc * acc_cols + ((uint32_t)(q * 32) << 16);
+                tmem_base + (uint32_t)acc * 256u + ((uint32_t)(q * 32) << 16);
             uint16_t *out = shared ? p.out_shared : p.out_routed;
             const int ld = shared ? p.ld_shared : p.ld_routed;
             const int col = t.y * PG_BM + row;
@@ -654,12 +646,9 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     while (want < PG_BN_DN && (long)want * E < 2L * A) want *= 2;
     const int bn_gu = want < PG_BN_GU ? want : PG_BN_GU;
     const int bn_dn = want < PG_BN_DN ? want : PG_BN_DN;
-    /* down: no tile wider than 128 rows -> four accumulator stages */
-    const bool dn_four = bn_dn <= 128;
-    const int bn_dn_sh = dn_four ? 128 : PG_BN_DN;
     launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, d.counts, d.offsets, E,
                                            do_shared ? T : 0, m_gu, m_gu_sh, m_dn,
-                                           bn_gu, bn_dn, bn_dn_sh, tl);
+                                           bn_gu, bn_dn, tl);
     (*launches)++;
     /* permuted activation rows */
     if (A > 0) {
@@ -680,7 +669,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
                      (size_t)(A > 0 ? A : 1), I, bn_dn);
     bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
-                     (size_t)(do_shared && T > 0 ? T : 1), Is, bn_dn_sh);
+                     (size_t)(do_shared && T > 0 ? T : 1), Is, PG_BN_DN);
     if (bad) return 1;
 
     cudaFuncSetAttribute(grouped_gemm_kernel<0>,
@@ -702,8 +691,6 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_shared = Is;
     p1.status = status;
     p1.bn_rows = bn_gu;
-    p1.bn_shared = PG_BN_GU;
-    p1.nacc = 2;
     launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
@@ -719,8 +706,6 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_shared = H;
     p2.perm = d.perm;
     p2.bn_rows = bn_dn;
-    p2.bn_shared = bn_dn_sh;
-    p2.nacc = dn_four ? 4 : 2;
     if (Is != I) {
         snprintf(g_prefill_err, sizeof g_prefill_err,
                  "tensor-core path needs shared_inter == moe_inter");
