@@ -40,6 +40,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "../../include/backend_cuda.h"
 #include "common.cuh"
@@ -181,6 +182,9 @@ struct TileLists {
     int4 *gu;        /* gate_up tiles */
     int4 *dn;        /* down tiles */
     int *n_gu, *n_dn;
+    /* per expert (index E: the shared expert): gate_up tiles finished so far
+     * (counted once per epilogue warp) and how many there are */
+    int *done, *need;
 };
 
 inline size_t prefill_max_ntiles(size_t A, size_t T, size_t E) {
@@ -191,7 +195,7 @@ inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
     size_t nt = prefill_max_ntiles(A, T, c.experts);
     size_t m1 = (c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter) / PG_BM;
     size_t m2 = c.hidden / PG_BM;
-    return (nt * m1 + nt * m2) * sizeof(int4) + 256;
+    return (nt * m1 + nt * m2) * sizeof(int4) + 256 + 2 * (c.experts + 2) * sizeof(int);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -244,7 +248,15 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
         tl.dn[(size_t)total_b * m_dn + i] =
             make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
     }
+    if (tid < E) {
+        tl.done[tid] = 0;
+        tl.need[tid] = nt_a * m_gu;
+    }
     if (tid == 0) {
+        tl.done[E] = 0;
+        tl.need[E] = nts_a * m_gu_sh;
+        tl.done[E + 1] = 0;                               /* all of them together */
+        tl.need[E + 1] = total_a * m_gu + nts_a * m_gu_sh;
         *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
         *tl.n_dn = total_b * m_dn + nts_b * m_dn;
     }
@@ -281,6 +293,16 @@ struct GemmParams {
     int ld_routed, ld_shared;
     const int32_t *perm;   /* down: sorted position -> flat assignment */
     int *status;
+    /* Overlap of the two expert kernels.  When `done` is set, every epilogue
+     * warp of the gate_up kernel counts a finished tile on done[expert] after
+     * its stores, and the down kernel does not wait for the whole gate_up
+     * kernel (programmatic dependent launch lets its CTAs start on SMs whose
+     * gate_up CTA has run out of tiles) but, tile by tile, for done[expert] to
+     * reach need[expert] * (epilogue warps).  The gate_up kernel never waits
+     * on the down kernel, and all of its CTAs are resident before the first
+     * down CTA can be, so the wait cannot hold up what it waits for. */
+    int *done;
+    const int *need;
     int bn_rows;           /* token rows a routed tile's TMA box fetches (<= BN):
                             * experts with a handful of rows should not pull a
                             * full-width box of their neighbours' rows through L2 */
@@ -311,7 +333,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapB,     /* xg | act */
                     const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
                     GemmParams p) {
-    pdl_enter();
+    if (MODE == 1 && p.done)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    else
+        pdl_enter();
     constexpr bool GATE_UP = MODE == 0;
     constexpr int STAGES = PG_STAGES;
     constexpr int BN = MODE == 1 ? PG_BN_DN : PG_BN_GU;
@@ -356,6 +381,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         if (lane == 0) {
             uint32_t kiter = 0;
             bool alive = true;
+            bool all_ready = false;
             for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
                 const int4 t = pg_tile<MODE>(p, tile);
                 const bool shared = MODE == 2 || t.x == p.E;
@@ -367,6 +393,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) + t.y * PG_BM;
                 const int arow2 = shared ? arow : arow + p.up_off;
                 const int brows = (MODE == 2 || shared) ? BN : p.bn_rows;   /* box of mb */
+                if (MODE == 1 && p.done && !all_ready) {
+                    /* This expert's activations must be complete and visible.
+                     * Once the whole gate_up kernel is through, no tile asks
+                     * again (a look at the counter is an L2 round trip). */
+                    const int e = shared ? p.E : t.x;
+                    const int need = __ldg(&p.need[e]) * PG_EPI_WARPS;
+                    const int need_all = __ldg(&p.need[p.E + 1]) * PG_EPI_WARPS;
+                    bool ready = false;
+                    for (uint32_t i = 0; i < APUS_WAIT_LIMIT && !*abort_flag; i++) {
+                        int v, va;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];"
+                                     : "=r"(va)
+                                     : "l"(p.done + p.E + 1)
+                                     : "memory");
+                        if (va >= need_all) { all_ready = true; ready = true; break; }
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];"
+                                     : "=r"(v)
+                                     : "l"(p.done + e)
+                                     : "memory");
+                        if (v >= need) { ready = true; break; }
+                        __nanosleep(100);
+                    }
+                    if (!ready) {
+                        *abort_flag = 1;
+                        set_status(p.status, ST_SCHED_TIMEOUT);
+                        alive = false;
+                        break;
+                    }
+                    /* generic-proxy writes of other SMs, then TMA (async proxy) reads */
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
                 for (int kb = 0; kb < num_kb; kb++, kiter++) {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
@@ -503,6 +560,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             }
             tc_fence_before();
             mbar_arrive(&tempty[acc]);
+            if (MODE == 0 && p.done) {
+                /* this warp's share of the tile is stored: make it visible, count it */
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    atomicAdd(p.done + (shared ? p.E : t.x), 1);
+                    atomicAdd(p.done + p.E + 1, 1);
+                }
+            }
         }
     }
     tc_fence_before();
@@ -639,6 +705,12 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     tl.dn = tl.gu + nt * m1;
     tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * m_dn);
     tl.n_dn = tl.n_gu + 1;
+    tl.done = tl.n_gu + 16;
+    tl.need = tl.done + (E + 2);
+    static const bool overlap = [] {
+        const char *e = getenv("APUS_CUDA_GEMM_OVERLAP");
+        return !(e && e[0] == '0');
+    }();
     /* token box of the routed tiles: about twice the mean row count of an
      * expert, so that nearly every expert is one tile and a tile does not pull
      * rows it will not use through L2 */
@@ -691,6 +763,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_shared = Is;
     p1.status = status;
     p1.bn_rows = bn_gu;
+    p1.done = overlap ? tl.done : nullptr;
+    p1.need = tl.need;
     launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
