@@ -465,7 +465,9 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         /* the sequential chain errs by at most (K-1)u times the sum of the
          * term magnitudes; the tensor cores are granted eight times that */
         ca.cbound = 9.1f * (float)K * 5.9604645e-8f;
-        ca.logits = dlogits;
+        ca.logits = nullptr;        /* nobody reads the merged logits */
+        ca.idx_out = didx;
+        ca.w_out = dw;
         ca.extra_out = extra_out;
         ca.status = c->d_status;
         ca.stats = c->d_rc_stats;
@@ -479,9 +481,6 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         }
         launch_k(router_certify_kernel, dim3((T + RC_TT - 1) / RC_TT), dim3(RC_THREADS),
                  smem, st, ca);
-        LAUNCHED();
-        launch_k(router_select_kernel, dim3((T + 7) / 8), dim3(256),
-                 (size_t)8 * E * sizeof(float), st, dlogits, T, E, topk, didx, dw);
         LAUNCHED();
         return 0;
     }

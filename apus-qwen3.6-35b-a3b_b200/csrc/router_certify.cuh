@@ -28,15 +28,16 @@
  *   5. the kernel checks |a - z| <= B on every pair it evaluates exactly and
  *      records ST_BOUND_VIOLATED if the assumption ever fails.
  *
- * The selection kernel (router_select_kernel) then runs unchanged on the
- * merged logits: ids are bit-exact by construction, weights see exact logits
- * for every selected expert.
+ * The engine's softmax / top-k (router_softmax_topk, one warp per token) then
+ * runs in the same kernel on the merged logits: ids are bit-exact by
+ * construction, weights see exact logits for every selected expert.
  */
 #pragma once
 #include <climits>
 
 #include "common.cuh"
 #include "decode_gemv.cuh"
+#include "router.cuh"
 
 namespace apus {
 
@@ -61,7 +62,9 @@ struct CertifyArgs {
     int T, E, K, topk;
     float wmin, wmin_extra;         /* smallest nonzero |w| (0 = unknown) */
     float cbound;                   /* see above */
-    uint16_t *logits;               /* [T, E] BF16 codes out */
+    uint16_t *logits;               /* [T, E] merged BF16 logit codes out (optional) */
+    int32_t *idx_out;               /* [T, topk] selection */
+    uint16_t *w_out;                /* [T, topk] renormalised weights (optional) */
     uint16_t *extra_out;            /* [T] */
     int *status;
     unsigned int *stats;            /* [0] += exact chains run (optional) */
@@ -276,7 +279,8 @@ router_certify_kernel(CertifyArgs a) {
                 const int e = e0 + c * 32 + lane;
                 if (e >= E) continue;
                 af[(size_t)tl * E + e] = av[c];
-                a.logits[(size_t)t * E + e] = bf16_bits(av[c]);   /* unless replaced below */
+                if (a.logits)
+                    a.logits[(size_t)t * E + e] = bf16_bits(av[c]);   /* unless replaced below */
             }
         }
         __syncwarp();
@@ -343,15 +347,27 @@ router_certify_kernel(CertifyArgs a) {
                 if (e == E) {
                     a.extra_out[t] = bf16_bits(z);
                 } else {
-                    a.logits[(size_t)t * E + e] = bf16_bits(z);
+                    if (a.logits) a.logits[(size_t)t * E + e] = bf16_bits(z);
                     const float bound = a.cbound * s_xnorm[tl] * wn[e];
                     if (!(fabsf(z - af[(size_t)tl * E + e]) <= bound))
                         set_status(a.status, ST_BOUND_VIOLATED);
+                    af[(size_t)tl * E + e] = bf16_round(z);    /* the exact logit */
                 }
             }
         }
     }
     if (a.stats && tid == 0) atomicAdd(&a.stats[0], (unsigned)npairs);
+
+    /* ---- softmax / top-k on the merged logits, one warp per token ---- */
+    __syncthreads();
+    for (int tl = warp; tl < nt; tl += RC_THREADS / 32) {
+        float *pt = af + (size_t)tl * E;
+        for (int e = lane; e < E; e += 32) pt[e] = bf16_round(pt[e]);
+        __syncwarp();
+        const int t = t0 + tl;
+        router_softmax_topk(pt, E, a.topk, lane, a.idx_out + (size_t)t * a.topk,
+                            a.w_out ? a.w_out + (size_t)t * a.topk : nullptr);
+    }
 }
 
 inline size_t router_certify_smem(int E, int K) {
