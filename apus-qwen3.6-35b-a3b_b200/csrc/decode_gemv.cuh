@@ -437,15 +437,33 @@ moe_finalize_kernel(FinalizeArgs a) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[j] = 0.0f;
-        for (int s = 0; s < a.TK; s++) {
-            const float w = bf16_f32(a.rw[(size_t)t * a.TK + s]);
-            const size_t flat = (size_t)t * a.TK + s;
-            const size_t row = a.pos ? (size_t)a.pos[flat] : flat;
-            float y[8];
-            unpack8(ldg16(a.eo + row * a.H + (size_t)c * 8), y);
+        /* eight slots' rows are requested before the first is added (the sum
+         * itself stays in slot order) */
+        for (int s0 = 0; s0 < a.TK; s0 += 8) {
+            uint4 yv[8];
+            float wv[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-                acc[j] = __fadd_rn(acc[j], __fmul_rn(w, y[j]));
+            for (int q = 0; q < 8; q++) {
+                const int s = s0 + q;
+                if (s < a.TK) {
+                    const size_t flat = (size_t)t * a.TK + s;
+                    const size_t row = a.pos ? (size_t)a.pos[flat] : flat;
+                    yv[q] = ldg16(a.eo + row * a.H + (size_t)c * 8);
+                    wv[q] = bf16_f32(a.rw[flat]);
+                } else {
+                    yv[q] = make_uint4(0, 0, 0, 0);
+                    wv[q] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                if (s0 + q >= a.TK) break;
+                float y[8];
+                unpack8(yv[q], y);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    acc[j] = __fadd_rn(acc[j], __fmul_rn(wv[q], y[j]));
+            }
         }
         float routed[8], shared[8], outv[8];
 #pragma unroll
