@@ -166,3 +166,54 @@ def test_block_rejects_bad_arguments(gpu, be, synth):
         gpu.moe_block(dict(cfg, top_k=64), W, x)
     # still usable afterwards
     gpu.moe_block(cfg, W, x)
+
+
+@pytest.mark.parametrize("T", [1, 3, 64, 300])
+def test_block_replays_from_a_cuda_graph(gpu, orc, be, synth, qwen_weights, T):
+    """The block on device pointers captured once and replayed: every counter
+    the kernels hand work over with (decode barrier, per-expert completion
+    counts of the expert GEMMs, router tickets) must be back in its initial
+    state after a run, so the third replay equals the eager call bit for bit
+    and the checker within tolerance."""
+    import torch
+    cfg = synth.QWEN_CFG
+    x = synth.host_x(be, T, cfg["hidden"], seed=70 + T)
+    layer = gpu.layer_create(cfg, qwen_weights)
+    gpu.reserve(cfg, T)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        d_x = torch.from_numpy(x.view(np.int16)).cuda()
+        d_eager = torch.empty_like(d_x)
+        d_out = torch.empty_like(d_x)
+        sp = stream.cuda_stream
+        gpu.moe_block_dev(layer, d_x.data_ptr(), d_eager.data_ptr(), T, stream=sp)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            gpu.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T,
+                              stream=torch.cuda.current_stream().cuda_stream)
+        for _ in range(3):
+            d_out.zero_()
+            g.replay()
+        torch.cuda.synchronize()
+    assert gpu.last_block_status() == 0
+    assert torch.equal(d_out, d_eager)
+    exp = orc.moe_block(cfg, qwen_weights, x)
+    a, b = f32(d_out.cpu().numpy().view(np.uint16)), f32(exp["out"])
+    assert np.abs(a - b).max() <= MAX_ABS and rel_l2(a, b) <= REL_L2
+
+
+@pytest.mark.parametrize("knob", ["APUS_CUDA_GEMM_OVERLAP", "APUS_CUDA_PDL"])
+def test_block_with_overlap_knobs_off(be, orc, synth, qwen_weights, knob, monkeypatch):
+    """The plain kernel boundary between the two expert GEMMs, and no
+    programmatic dependent launches at all, give the same block."""
+    monkeypatch.setenv(knob, "0")
+    be.enable()
+    try:
+        cfg = synth.QWEN_CFG
+        x = synth.host_x(be, 200, cfg["hidden"], seed=91)
+        check_block(be.moe_block(cfg, qwen_weights, x),
+                    orc.moe_block(cfg, qwen_weights, x), knob + "=0")
+        assert be.last_block_status() == 0
+    finally:
+        be.disable()
