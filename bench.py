@@ -118,10 +118,11 @@ class ClockSampler(threading.Thread):
                     samples=len(s))
 
 
-def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth):
+def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth, min_seconds=0.0):
     """Times the reference's own MoE block (apus_layer_moe_batch, AVX2 rows
     over its pthread pool) on this host.  Returns (tokens/s, threads,
-    sample-description, ms_per_step)."""
+    sample-description, ms_per_step).  With min_seconds the timed loop keeps
+    going (up to 64 steps) until that much CPU time has been sampled."""
     from oracle import oracle
     if not oracle.Reference.available():
         return None
@@ -138,14 +139,16 @@ def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth):
     xs = x[:Ts]
     for _ in range(warmup):
         ref.moe_block(cfg, W, xs)
-    best = None
-    for _ in range(steps):
+    best, spent, done = None, 0.0, 0
+    while done < steps or (spent < min_seconds and done < 64):
         t0 = time.perf_counter()
         ref.moe_block(cfg, W, xs)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
+        spent += dt
+        done += 1
     sample = (f"{Ts} of {T} tokens, one layer, apus_layer_moe_batch, "
-              f"best of {steps}")
+              f"best of {done} ({spent:.1f} s sampled)")
     return Ts / best, ref.threads(), sample, best * 1e3
 
 L2_BYTES = 126 << 20
@@ -299,7 +302,7 @@ def run_stack(args, cfg, config, pkg, synth, L):
                   "device_status": status},
     }
     if not args.no_cpu_baseline:
-        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth)
+        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth, min_seconds=10.0)
         if r is not None:
             v, threads, sample, _ = r
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
@@ -548,7 +551,7 @@ def main():
                   "us_per_token": ms * 1e3 / T, "device_status": status},
     }
     if not args.no_cpu_baseline:
-        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth)
+        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth, min_seconds=10.0)
         if r is not None:
             v, threads, sample, _ = r
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
