@@ -364,22 +364,32 @@ __device__ __forceinline__ float small_chain(const uint16_t *__restrict__ wrow,
 }
 
 /*
- * Latency path for few tokens.  grid = (ceil(rows / 8), T), block = 32: a CTA
- * pulls eight router rows into shared memory with one bulk copy each (all in
- * flight at once, so the 1 MiB router matrix arrives spread over 32 SMs instead
- * of trickling through one), lanes 0..7 walk one exact chain each, and the
- * BF16 logits go to global memory.  The CTA that arrives last for its token
- * (one atomic counter per token, which it resets for the next call) runs the
- * softmax / top-k warp.  No CTA ever waits on another.
- * Requires K % 8 == 0 and a 16-byte-aligned router matrix.
- * Dynamic shared memory: 8 * (K*2 + 16) + K*4 + E*4 bytes.
+ * Latency path for few tokens.  grid = (ceil(rows / 8), ceil(T / TOK)), block
+ * = 128: a CTA pulls eight router rows into shared memory with one bulk copy
+ * each (all in flight at once, so the 1 MiB router matrix arrives spread over
+ * 32 SMs instead of trickling through one) and stages TOK tokens as fp32;
+ * the lanes of TOK/4 warps walk one exact chain each (lane = row * 4 + token),
+ * and the BF16 logits go to global memory.  The CTA that arrives last for a
+ * token (one atomic counter per token, which it resets for the next call) runs
+ * that token's softmax / top-k on one of its warps.  No CTA ever waits on
+ * another.  Requires K % 8 == 0 and a 16-byte-aligned router matrix.
+ * Dynamic shared memory: 8 * (K*2 + 16) + TOK * ((K + 4) + E) * 4 bytes.
  */
 constexpr int ROUTER_SMALL_ROWS = 8;
+constexpr int ROUTER_SMALL_THREADS = 128;
 
-__global__ void __launch_bounds__(32)
+/* TOK tokens per CTA: 4 (one chain warp) or 8 (two, on different schedulers) */
+inline size_t router_small_smem(int E, int K, int tok) {
+    return (size_t)ROUTER_SMALL_ROWS * (K * 2 + 16) + (size_t)tok * (K + 4) * 4 +
+           (size_t)tok * E * 4;
+}
+
+template <int ROUTER_SMALL_TOK>
+__global__ void __launch_bounds__(ROUTER_SMALL_THREADS)
 router_small_kernel(const uint16_t *__restrict__ x,
                     const uint16_t *__restrict__ wr, int T, int E, int K,
-                    int topk, float wmin, int32_t *__restrict__ idx_out,
+                    int topk, float wmin, float wmin_extra,
+                    int32_t *__restrict__ idx_out,
                     uint16_t *__restrict__ w_out,
                     uint16_t *__restrict__ logits_out,
                     const uint16_t *__restrict__ extra_row,
@@ -390,23 +400,25 @@ router_small_kernel(const uint16_t *__restrict__ x,
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int pitch = K * 2 + 16;                 /* bytes; de-conflicts banks */
+    const int xpitch = K + 4;                     /* floats; likewise for the tokens */
     unsigned char *rows_s = smem_raw;
     float *xs = reinterpret_cast<float *>(smem_raw + ROUTER_SMALL_ROWS * pitch);
-    float *ps = xs + K;
+    float *ps = xs + (size_t)ROUTER_SMALL_TOK * xpitch;
     __shared__ __align__(8) uint64_t bar;
+    __shared__ unsigned int s_xmin;
+    __shared__ int s_last[ROUTER_SMALL_TOK];
 
-    const int lane = threadIdx.x;
-    const int t = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = blockIdx.y * ROUTER_SMALL_TOK;
+    const int nt = min(ROUTER_SMALL_TOK, T - t0);
     const int rows_total = E + (extra_row ? 1 : 0);
     const int r0 = blockIdx.x * ROUTER_SMALL_ROWS;
     const int nrows = min(ROUTER_SMALL_ROWS, rows_total - r0);
 
-    if (lane == 0) {
+    if (tid == 0) {
         mbar_init(&bar, 1);
         mbar_fence_init();
-    }
-    __syncwarp();
-    if (lane == 0) {
+        s_xmin = 0x7f800000u;
         mbar_expect_tx(&bar, (uint32_t)nrows * (uint32_t)K * 2u);
         for (int r = 0; r < nrows; r++) {
             const uint16_t *src = (r0 + r == E) ? extra_row
@@ -414,12 +426,15 @@ router_small_kernel(const uint16_t *__restrict__ x,
             bulk_g2s(rows_s + (size_t)r * pitch, src, (uint32_t)K * 2u, &bar);
         }
     }
+    if (tid < ROUTER_SMALL_TOK) s_last[tid] = 0;
+    __syncthreads();
     unsigned int xmin = 0x7f800000u;
-#pragma unroll 4
-    for (int c = lane; c < K / 8; c += 32) {
-        const uint4 v = ldg16(x + (size_t)t * K + (size_t)c * 8);
+    const int c8 = K / 8;
+    for (int c = tid; c < nt * c8; c += ROUTER_SMALL_THREADS) {
+        const int tt = c / c8, cc = c - tt * c8;
+        const uint4 v = ldg16(x + (size_t)(t0 + tt) * K + (size_t)cc * 8);
         const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
-        float4 *d = reinterpret_cast<float4 *>(xs + c * 8);
+        float4 *d = reinterpret_cast<float4 *>(xs + (size_t)tt * xpitch + cc * 8);
         d[0] = make_float4(bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y));
         d[1] = make_float4(bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w));
 #pragma unroll
@@ -433,40 +448,52 @@ router_small_kernel(const uint16_t *__restrict__ x,
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
         xmin = min(xmin, __shfl_xor_sync(0xffffffffu, xmin, o));
-    __syncwarp();
-    const bool use_fma =
-        (wmin > 0.0f) &&
-        ((double)wmin * (double)__uint_as_float(xmin) >= 7.52316384526264e-37);
-    const bool arrived = mbar_wait(&bar, 0);
-    if (!arrived) set_status(status, ST_MBAR_TIMEOUT);
-    if (arrived && lane < nrows) {
-        const uint16_t *wrow =
-            reinterpret_cast<const uint16_t *>(rows_s + (size_t)lane * pitch);
-        const bool fma_row = use_fma && (r0 + lane != E);
-        const float acc = fma_row ? small_chain<true>(wrow, xs, K)
-                                  : small_chain<false>(wrow, xs, K);
-        const uint16_t code = bf16_bits(acc);
-        if (r0 + lane == E) {
-            extra_out[t] = code;
-        } else {
-            logits_ws[(size_t)t * E + r0 + lane] = bf16_f32(code);
-            if (logits_out) logits_out[(size_t)t * E + r0 + lane] = code;
+    if (lane == 0) atomicMin(&s_xmin, xmin);
+    __syncthreads();
+    if (warp < ROUTER_SMALL_TOK / 4) {
+        const double xmn = (double)__uint_as_float(s_xmin);
+        const bool use_fma = (wmin > 0.0f) && ((double)wmin * xmn >= 7.52316384526264e-37);
+        const bool use_fma_x =
+            (wmin_extra > 0.0f) && ((double)wmin_extra * xmn >= 7.52316384526264e-37);
+        const bool arrived = mbar_wait(&bar, 0);
+        if (!arrived) set_status(status, ST_MBAR_TIMEOUT);
+        const int r = lane >> 2, tt = warp * 4 + (lane & 3);
+        if (arrived && r < nrows && tt < nt) {
+            const uint16_t *wrow =
+                reinterpret_cast<const uint16_t *>(rows_s + (size_t)r * pitch);
+            const float *xr = xs + (size_t)tt * xpitch;
+            const bool fma_row = (r0 + r != E) ? use_fma : use_fma_x;
+            const float acc = fma_row ? small_chain<true>(wrow, xr, K)
+                                      : small_chain<false>(wrow, xr, K);
+            const uint16_t code = bf16_bits(acc);
+            const int t = t0 + tt;
+            if (r0 + r == E) {
+                extra_out[t] = code;
+            } else {
+                logits_ws[(size_t)t * E + r0 + r] = bf16_f32(code);
+                if (logits_out) logits_out[(size_t)t * E + r0 + r] = code;
+            }
         }
+        /* the last CTA of a token finishes that token */
+        __threadfence();
+        __syncwarp();
+        if (lane < 4 && warp * 4 + lane < nt)
+            s_last[warp * 4 + lane] =
+                atomicAdd(&counters[t0 + warp * 4 + lane], 1u) == gridDim.x - 1;
     }
-    /* last CTA of this token finishes the job */
-    __threadfence();
-    __syncwarp();
-    unsigned int old = 0;
-    if (lane == 0) old = atomicAdd(&counters[t], 1u);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old != gridDim.x - 1) return;
-    __threadfence();
-    for (int e = lane; e < E; e += 32)
-        ps[e] = __ldcg(&logits_ws[(size_t)t * E + e]);
-    __syncwarp();
-    if (lane == 0) counters[t] = 0;
-    router_softmax_topk(ps, E, topk, lane, idx_out + (size_t)t * topk,
-                        w_out ? w_out + (size_t)t * topk : nullptr);
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += ROUTER_SMALL_THREADS / 32) {
+        if (!s_last[tt]) continue;
+        const int t = t0 + tt;
+        float *p = ps + (size_t)tt * E;
+        __threadfence();
+        for (int e = lane; e < E; e += 32)
+            p[e] = __ldcg(&logits_ws[(size_t)t * E + e]);
+        __syncwarp();
+        if (lane == 0) counters[t] = 0;
+        router_softmax_topk(p, E, topk, lane, idx_out + (size_t)t * topk,
+                            w_out ? w_out + (size_t)t * topk : nullptr);
+    }
 }
 
 constexpr int RL_STAGES = 3;
