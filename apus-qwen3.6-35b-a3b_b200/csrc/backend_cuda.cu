@@ -192,6 +192,8 @@ static int ctx_init() {
     CU_OK(cudaMalloc(&c->d_df_timeline,
                      (size_t)c->sm_count * DF_MARKS * sizeof(unsigned long long)));
     g_apus_use_pdl = env_long("APUS_CUDA_PDL", 1) != 0;
+    g_pg_overlap = (int)env_long("APUS_CUDA_GEMM_OVERLAP", 1);
+    g_pg_dynamic = (int)env_long("APUS_CUDA_GEMM_DYNAMIC", 3);
     g_ctx = c;
     return 0;
 }

@@ -23,7 +23,7 @@
  *             epilogue: y = rnd(D), stored at row perm[r] of the flat
  *             assignment-ordered buffer (the engine's eo, c/layer.h:618)
  *
- * One persistent CTA per SM, 10 warps: warp 0 issues TMA loads into a
+ * One persistent CTA per SM, 10 warps: warp 0 picks tiles and issues TMA loads into a
  * shared-memory ring (128B-swizzled K-major tiles, no multicast), warp 1
  * issues the MMAs and owns the 512 TMEM columns (two accumulator stages), warps
  * 2-9 drain accumulators (tcgen05.ld, two warps per TMEM lane quarter) and run
@@ -60,6 +60,8 @@ constexpr int PG_BK = 64;         /* K elements per stage = one 128B swizzle row
 constexpr int PG_EPI_WARPS = 8;   /* two per TMEM lane quarter */
 constexpr int PG_THREADS = 64 + PG_EPI_WARPS * 32;
 constexpr int PG_TILE_BYTES = PG_BM * PG_BK * 2;   /* 16 KB */
+constexpr int PG_CLAIM_KB = 8;     /* k-blocks before a tile's end at which the next is claimed */
+constexpr int PG_TQ = 4;          /* tile queue entries */
 constexpr int PG_STAGES = 4;      /* 48 KB per stage in both kernels */
 constexpr int PG_TMEM_COLS = 512;
 
@@ -185,6 +187,8 @@ struct TileLists {
     /* per expert (index E: the shared expert): gate_up tiles finished so far
      * (counted once per epilogue warp) and how many there are */
     int *done, *need;
+    /* next tile to hand out, one counter per expert kernel (gate_up, down) */
+    int *sched;
 };
 
 inline size_t prefill_max_ntiles(size_t A, size_t T, size_t E) {
@@ -195,7 +199,7 @@ inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
     size_t nt = prefill_max_ntiles(A, T, c.experts);
     size_t m1 = (c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter) / PG_BM;
     size_t m2 = c.hidden / PG_BM;
-    return (nt * m1 + nt * m2) * sizeof(int4) + 256 + 2 * (c.experts + 2) * sizeof(int);
+    return (nt * m1 + nt * m2) * sizeof(int4) + 256 + (2 * (c.experts + 2) + 2) * sizeof(int);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -255,6 +259,8 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
     if (tid == 0) {
         tl.done[E] = 0;
         tl.need[E] = nts_a * m_gu_sh;
+        tl.sched[0] = 0;
+        tl.sched[1] = 0;
         tl.done[E + 1] = 0;                               /* all of them together */
         tl.need[E + 1] = total_a * m_gu + nts_a * m_gu_sh;
         *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
@@ -303,6 +309,11 @@ struct GemmParams {
      * down CTA can be, so the wait cannot hold up what it waits for. */
     int *done;
     const int *need;
+    /* Tiles are handed out in list order by an atomic counter when `sched` is
+     * set (CTA i starts with tile i): a CTA that starts late, because its SM
+     * was still busy with the tail of the kernel before, simply takes fewer
+     * tiles.  Null: tile i + k * gridDim.x belongs to CTA i. */
+    int *sched;
     int bn_rows;           /* token rows a routed tile's TMA box fetches (<= BN):
                             * experts with a handful of rows should not pull a
                             * full-width box of their neighbours' rows through L2 */
@@ -354,6 +365,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
     uint64_t *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    /* tile queue: the producer warp decides which tile comes next and tells
+     * the MMA warp and the epilogue warps through a small ring */
+    uint64_t *tqf = bars + 2 * STAGES + 5, *tqe = tqf + PG_TQ;
+    volatile int *tq = reinterpret_cast<volatile int *>(tqe + PG_TQ);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -364,6 +379,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         for (int a = 0; a < 2; a++) {
             mbar_init(&tfull[a], 1);
             mbar_init(&tempty[a], PG_EPI_WARPS * 32);
+        }
+        for (int s = 0; s < PG_TQ; s++) {
+            mbar_init(&tqf[s], 1);
+            mbar_init(&tqe[s], 1 + PG_EPI_WARPS);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -382,7 +401,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             uint32_t kiter = 0;
             bool alive = true;
             bool all_ready = false;
-            for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
+            /* Which tile comes next: the counter is asked while the last
+             * k-blocks of the current tile are being requested — late, so that
+             * a CTA claims no tile long before it can start it, yet early
+             * enough for the answer (an L2 round trip) to be there.  Nothing
+             * reads `claim` until the tile's loads are all out: the first
+             * instruction that does would stall this lane for the round trip. */
+            const bool dyn = MODE != 2 && p.sched != nullptr;
+            const int kclaim = num_kb > PG_CLAIM_KB ? num_kb - PG_CLAIM_KB : 0;
+            int tile = blockIdx.x;
+            for (uint32_t qi = 0; alive; qi++) {
+                const int qs = qi % PG_TQ;
+                if (!pg_wait(&tqe[qs], ((qi / PG_TQ) & 1u) ^ 1u, abort_flag, p.status,
+                             ST_MBAR_TIMEOUT))
+                    break;
+                tq[qs] = tile;
+                mbar_arrive(&tqf[qs]);
+                if (tile >= n_tiles) break;
                 const int4 t = pg_tile<MODE>(p, tile);
                 const bool shared = MODE == 2 || t.x == p.E;
                 const int kb0 = MODE == 2 ? t.x * num_kb : 0;   /* K slice */
@@ -424,14 +459,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     /* generic-proxy writes of other SMs, then TMA (async proxy) reads */
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
-                for (int kb = 0; kb < num_kb; kb++, kiter++) {
+                int claim = tile;
+                auto request = [&](int kb) -> bool {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
                     if (!pg_wait(&empty[s], ph ^ 1u, abort_flag, p.status,
-                                 ST_MBAR_TIMEOUT)) {
-                        alive = false;
-                        break;
-                    }
+                                 ST_MBAR_TIMEOUT))
+                        return false;
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], (uint32_t)(B_OFF + brows * PG_BK * 2));
                     tma_load_2d(st, ma, (kb0 + kb) * PG_BK, arow, &full[s]);
@@ -439,7 +473,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                         tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
                                     &full[s]);
                     tma_load_2d(st + B_OFF, mb, (kb0 + kb) * PG_BK, t.z, &full[s]);
-                }
+                    kiter++;
+                    return true;
+                };
+                int kb = 0;
+                for (; alive && kb <= kclaim; kb++) alive = request(kb);
+                if (dyn) claim = atomicAdd(p.sched, 1);
+                for (; alive && kb < num_kb; kb++) alive = request(kb);
+                tile = claim + (int)gridDim.x;
             }
         }
     } else if (warp == 1) {
@@ -447,9 +488,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         if (lane == 0) {
             uint32_t kiter = 0;
             bool alive = true;
-            int it = 0;
-            for (int tile = blockIdx.x; alive && tile < n_tiles;
-                 tile += gridDim.x, it++) {
+            for (int it = 0; alive; it++) {
+                const int qs = it % PG_TQ;
+                if (!pg_wait(&tqf[qs], (uint32_t)(it / PG_TQ) & 1u, abort_flag, p.status,
+                             ST_MBAR_TIMEOUT))
+                    break;
+                const int tile = tq[qs];
+                mbar_arrive(&tqe[qs]);
+                if (tile >= n_tiles) break;
                 const int4 t = pg_tile<MODE>(p, tile);
                 const int acc = it & 1;
                 const uint32_t aph = (uint32_t)(it >> 1) & 1u;
@@ -498,9 +544,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
         const int half = (warp - 2) >> 2;       /* which chunks of the tile */
         const int row = q * 32 + lane;          /* row inside the tile */
         bool alive = true;
-        int it = 0;
-        for (int tile = blockIdx.x; alive && tile < n_tiles;
-             tile += gridDim.x, it++) {
+        for (int it = 0; alive; it++) {
+            const int qs = it % PG_TQ;
+            if (!pg_wait(&tqf[qs], (uint32_t)(it / PG_TQ) & 1u, abort_flag, p.status,
+                         ST_MBAR_TIMEOUT))
+                break;
+            const int tile = tq[qs];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tqe[qs]);
+            if (tile >= n_tiles) break;
             const int4 t = pg_tile<MODE>(p, tile);
             const bool shared = MODE == 2 || t.x == p.E;
             const int acc = it & 1;
@@ -668,6 +720,12 @@ inline PrefillMaps *prefill_maps_create(const ApusCudaMoeCfg &c,
 }
 inline void prefill_maps_free(PrefillMaps *m) { delete m; }
 
+/* Set when the backend is enabled: the two expert kernels overlap through
+ * per-expert counters (0: plain kernel boundary); tiles handed out by an atomic
+ * counter (bit 0: gate_up kernel, bit 1: down kernel). */
+inline int g_pg_overlap = 1;
+inline int g_pg_dynamic = 3;
+
 inline int pg_smem_bytes(bool gate_up) {
     (void)gate_up;
     return PG_STAGES * 3 * PG_TILE_BYTES + 1024 /* alignment slack */ +
@@ -707,10 +765,9 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     tl.n_dn = tl.n_gu + 1;
     tl.done = tl.n_gu + 16;
     tl.need = tl.done + (E + 2);
-    static const bool overlap = [] {
-        const char *e = getenv("APUS_CUDA_GEMM_OVERLAP");
-        return !(e && e[0] == '0');
-    }();
+    tl.sched = tl.need + (E + 2);
+    const bool overlap = g_pg_overlap != 0;
+    const int dynamic = g_pg_dynamic;
     /* token box of the routed tiles: about twice the mean row count of an
      * expert, so that nearly every expert is one tile and a tile does not pull
      * rows it will not use through L2 */
@@ -765,6 +822,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.bn_rows = bn_gu;
     p1.done = overlap ? tl.done : nullptr;
     p1.need = tl.need;
+    p1.sched = (dynamic & 1) ? tl.sched : nullptr;
     launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
@@ -780,6 +838,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_shared = H;
     p2.perm = d.perm;
     p2.bn_rows = bn_dn;
+    p2.sched = (dynamic & 2) ? tl.sched + 1 : nullptr;
     if (Is != I) {
         snprintf(g_prefill_err, sizeof g_prefill_err,
                  "tensor-core path needs shared_inter == moe_inter");

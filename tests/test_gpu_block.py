@@ -203,10 +203,12 @@ def test_block_replays_from_a_cuda_graph(gpu, orc, be, synth, qwen_weights, T):
     assert np.abs(a - b).max() <= MAX_ABS and rel_l2(a, b) <= REL_L2
 
 
-@pytest.mark.parametrize("knob", ["APUS_CUDA_GEMM_OVERLAP", "APUS_CUDA_PDL"])
+@pytest.mark.parametrize("knob", ["APUS_CUDA_GEMM_OVERLAP", "APUS_CUDA_GEMM_DYNAMIC",
+                                  "APUS_CUDA_PDL"])
 def test_block_with_overlap_knobs_off(be, orc, synth, qwen_weights, knob, monkeypatch):
-    """The plain kernel boundary between the two expert GEMMs, and no
-    programmatic dependent launches at all, give the same block."""
+    """The plain kernel boundary between the two expert GEMMs, tiles assigned
+    to CTAs by index instead of by an atomic counter, and no programmatic
+    dependent launches at all, give the same block."""
     monkeypatch.setenv(knob, "0")
     be.enable()
     try:
