@@ -66,6 +66,12 @@ SYMBOLS = [
     "apus_cuda_fused_timeline", "apus_cuda_router_exact_chains",
     "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
     "apus_cuda_ep_finish_dev",
+    "apus_cuda_ep_window_create", "apus_cuda_ep_window_destroy",
+    "apus_cuda_ep_window_handle_bytes", "apus_cuda_ep_window_handle",
+    "apus_cuda_ep_window_attach", "apus_cuda_ep_window_attach_local",
+    "apus_cuda_ep_push_dev", "apus_cuda_ep_wait_dev",
+    "apus_cuda_ep_window_experts_dev", "apus_cuda_ep_return_dev",
+    "apus_cuda_ep_shared_dev", "apus_cuda_ep_combine_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
     "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
@@ -130,6 +136,21 @@ class Backend:
         L.apus_cuda_experts_dev.argtypes = [vp, vp, vp, sz, vp, vp]
         L.apus_cuda_ep_finish_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp,
                                               C.POINTER(MoeTrace), vp]
+        L.apus_cuda_ep_window_create.argtypes = [sz, sz, sz, sz, sz, sz,
+                                                 C.POINTER(vp)]
+        L.apus_cuda_ep_window_destroy.argtypes = [vp]
+        L.apus_cuda_ep_window_destroy.restype = None
+        L.apus_cuda_ep_window_handle_bytes.argtypes = []
+        L.apus_cuda_ep_window_handle_bytes.restype = sz
+        L.apus_cuda_ep_window_handle.argtypes = [vp, vp]
+        L.apus_cuda_ep_window_attach.argtypes = [vp, sz, vp]
+        L.apus_cuda_ep_window_attach_local.argtypes = [vp, sz, vp]
+        L.apus_cuda_ep_push_dev.argtypes = [vp, vp, vp, sz, C.c_uint32, vp, vp]
+        L.apus_cuda_ep_wait_dev.argtypes = [vp, C.c_int, C.c_uint32, vp]
+        L.apus_cuda_ep_window_experts_dev.argtypes = [vp, vp, vp]
+        L.apus_cuda_ep_return_dev.argtypes = [vp, C.c_uint32, vp]
+        L.apus_cuda_ep_shared_dev.argtypes = [vp, vp, sz, vp, vp]
+        L.apus_cuda_ep_combine_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
         L.apus_synth_fill_host.argtypes = [u16p, sz, C.c_uint64, C.c_uint32,
@@ -387,6 +408,59 @@ class Backend:
         self._check(self.lib.apus_cuda_ep_finish_dev(
             layer, d_x, T, d_y_sorted, d_pos, d_w, d_sgl, d_out,
             C.byref(tr) if tr else None, stream), "apus_cuda_ep_finish_dev")
+
+    # ---- expert parallelism through peer memory ---------------------------
+    def ep_window_create(self, max_tokens, topk, H, E, n_ranks, rank):
+        w = vp()
+        self._check(self.lib.apus_cuda_ep_window_create(
+            max_tokens, topk, H, E, n_ranks, rank, C.byref(w)),
+            "apus_cuda_ep_window_create")
+        return w
+
+    def ep_window_destroy(self, w):
+        self.lib.apus_cuda_ep_window_destroy(w)
+
+    def ep_window_handle(self, w):
+        buf = C.create_string_buffer(self.lib.apus_cuda_ep_window_handle_bytes())
+        self._check(self.lib.apus_cuda_ep_window_handle(w, buf),
+                    "apus_cuda_ep_window_handle")
+        return buf.raw
+
+    def ep_window_attach(self, w, peer, handle):
+        self._check(self.lib.apus_cuda_ep_window_attach(
+            w, peer, C.c_char_p(handle)), "apus_cuda_ep_window_attach")
+
+    def ep_window_attach_local(self, w, peer, other):
+        self._check(self.lib.apus_cuda_ep_window_attach_local(w, peer, other),
+                    "apus_cuda_ep_window_attach_local")
+
+    def ep_push_dev(self, w, d_x, d_idx, T, epoch, d_pos, stream=None):
+        self._check(self.lib.apus_cuda_ep_push_dev(w, d_x, d_idx, T, epoch,
+                                                   d_pos, stream),
+                    "apus_cuda_ep_push_dev")
+
+    def ep_wait_dev(self, w, which, epoch, stream=None):
+        self._check(self.lib.apus_cuda_ep_wait_dev(w, which, epoch, stream),
+                    "apus_cuda_ep_wait_dev")
+
+    def ep_window_experts_dev(self, w, layer, stream=None):
+        self._check(self.lib.apus_cuda_ep_window_experts_dev(w, layer, stream),
+                    "apus_cuda_ep_window_experts_dev")
+
+    def ep_return_dev(self, w, epoch, stream=None):
+        self._check(self.lib.apus_cuda_ep_return_dev(w, epoch, stream),
+                    "apus_cuda_ep_return_dev")
+
+    def ep_shared_dev(self, layer, d_x, T, d_sy, stream=None):
+        self._check(self.lib.apus_cuda_ep_shared_dev(layer, d_x, T, d_sy,
+                                                     stream),
+                    "apus_cuda_ep_shared_dev")
+
+    def ep_combine_dev(self, w, layer, T, d_pos, d_w, d_sy, d_sgl, d_out,
+                       stream=None):
+        self._check(self.lib.apus_cuda_ep_combine_dev(
+            w, layer, T, d_pos, d_w, d_sy, d_sgl, d_out, stream),
+            "apus_cuda_ep_combine_dev")
 
     def rmsnorm_dev(self, d_x, d_w, d_y, T, N, stream=None):
         self._check(self.lib.apus_cuda_rmsnorm_dev(d_x, d_w, d_y, T, N,

@@ -26,6 +26,7 @@
 #include "router_certify.cuh"
 #include "decode_gemv.cuh"
 #include "dispatch.cuh"
+#include "ep_window.cuh"
 #include "misc_kernels.cuh"
 #include "prefill_gemm.cuh"
 #include "router.cuh"
@@ -1386,7 +1387,7 @@ extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
     int blocks = (int)((total + 255) / 256);
     if (blocks > c->sm_count * 16) blocks = c->sm_count * 16;
     launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, d_x, o.perm,
-             (int)A, (int)H, (int)topk, d_send_x);
+             (int)A, (int)H, (int)topk, d_send_x, (const int32_t *)nullptr);
     LAUNCHED();
     launch_k(ep_gather_ids_kernel, dim3((unsigned)((A + 255) / 256)), dim3(256),
              0, st, d_idx, o.perm, (int)A, d_send_e);
@@ -1479,6 +1480,232 @@ extern "C" int apus_cuda_ep_finish_dev(ApusCudaLayer *L, const uint16_t *d_x,
     }
     return run_finalize(c, cfg, (int)T, d_y_sorted, d_pos, d_w, b.sy, d_sgl,
                         d_out, d_tr, st);
+}
+
+/* ---- expert parallelism through peer memory (ep_window.cuh) ------------- */
+struct ApusCudaEpWindow {
+    EpwLayout l;
+    EpwPeers peers;
+    bool opened[EPW_MAX_RANKS];      /* mapped with cudaIpcOpenMemHandle */
+    int me;
+    int topk, E;
+    unsigned char *base;
+    uint16_t *y;                     /* [n*cap][H] expert outputs by slot */
+    int32_t *offsets, *perm, *counts;
+    int32_t *uh;                     /* dispatch scratch */
+    unsigned int *counter;           /* [2] finished-CTA counters */
+};
+
+extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t H,
+                                          size_t E, size_t n_ranks, size_t rank,
+                                          ApusCudaEpWindow **out) {
+    if (!out || !max_tokens || !topk || !H || H % 8 || !n_ranks ||
+        n_ranks > EPW_MAX_RANKS || rank >= n_ranks || !E || E % n_ranks)
+        return fail("ep_window_create: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    ApusCudaEpWindow *w = new ApusCudaEpWindow();
+    memset(w, 0, sizeof *w);
+    const size_t cap = max_tokens * topk;
+    w->l = epw_layout((int)n_ranks, (int)cap, (int)H);
+    w->me = (int)rank;
+    w->topk = (int)topk;
+    w->E = (int)E;
+    const size_t A = cap;
+    const size_t local = n_ranks * cap * H * 2 + (n_ranks + 1) * 4 + A * 4 +
+                         n_ranks * 4 + dispatch_scratch_bytes(A, n_ranks) + 4096;
+    unsigned char *loc = nullptr;
+    if (cudaMalloc(&w->base, w->l.total) != cudaSuccess ||
+        cudaMalloc(&loc, local) != cudaSuccess) {
+        if (w->base) cudaFree(w->base);
+        delete w;
+        return fail("ep_window_create: out of device memory (%zu + %zu bytes)",
+                    w->l.total, local);
+    }
+    cudaMemset(w->base, 0, w->l.total);
+    cudaMemset(loc, 0, local);
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    size_t o = 0;
+    w->y = (uint16_t *)(loc + o);        o = up(o + n_ranks * cap * H * 2);
+    w->offsets = (int32_t *)(loc + o);   o = up(o + (n_ranks + 1) * 4);
+    w->perm = (int32_t *)(loc + o);      o = up(o + A * 4);
+    w->counts = (int32_t *)(loc + o);    o = up(o + n_ranks * 4);
+    w->counter = (unsigned int *)(loc + o); o = up(o + 8);
+    w->uh = (int32_t *)(loc + o);
+    w->peers.base[rank] = w->base;
+    CU_OK(cudaDeviceSynchronize());
+    *out = w;
+    return 0;
+}
+
+extern "C" void apus_cuda_ep_window_destroy(ApusCudaEpWindow *w) {
+    if (!w) return;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < w->l.n; r++)
+        if (w->opened[r]) cudaIpcCloseMemHandle(w->peers.base[r]);
+    if (w->y) cudaFree(w->y);           /* first address of the local allocation */
+    if (w->base) cudaFree(w->base);
+    delete w;
+}
+
+extern "C" size_t apus_cuda_ep_window_handle_bytes(void) {
+    return sizeof(cudaIpcMemHandle_t);
+}
+
+extern "C" int apus_cuda_ep_window_handle(ApusCudaEpWindow *w, void *out) {
+    if (!w || !out) return fail("ep_window_handle: bad args");
+    cudaIpcMemHandle_t h;
+    CU_OK(cudaIpcGetMemHandle(&h, w->base));
+    memcpy(out, &h, sizeof h);
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_window_attach(ApusCudaEpWindow *w, size_t peer,
+                                          const void *handle) {
+    if (!w || !handle || peer >= (size_t)w->l.n || (int)peer == w->me)
+        return fail("ep_window_attach: bad args");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *p = nullptr;
+    CU_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    w->peers.base[peer] = (unsigned char *)p;
+    w->opened[peer] = true;
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_window_attach_local(ApusCudaEpWindow *w, size_t peer,
+                                                ApusCudaEpWindow *other) {
+    if (!w || !other || peer >= (size_t)w->l.n || other->l.total != w->l.total)
+        return fail("ep_window_attach_local: bad args");
+    w->peers.base[peer] = other->base;
+    return 0;
+}
+
+static int epw_ready(ApusCudaEpWindow *w, const char *what) {
+    if (!w) return fail("%s: no window", what);
+    for (int r = 0; r < w->l.n; r++)
+        if (!w->peers.base[r]) return fail("%s: peer %d not attached", what, r);
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_push_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
+                                     const int32_t *d_idx, size_t T, uint32_t epoch,
+                                     int32_t *d_pos, void *stream) {
+    if (epw_ready(w, "ep_push_dev")) return 1;
+    const size_t A = T * w->topk;
+    if (!d_x || !d_idx || !d_pos || !T || A > (size_t)w->l.cap)
+        return fail("ep_push_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DispatchOut o;
+    memset(&o, 0, sizeof o);
+    o.counts = w->counts;
+    o.offsets = w->offsets;
+    o.perm = w->perm;
+    o.pos = d_pos;
+    if (launch_dispatch(c, d_idx, (int)A, w->l.n, o, w->uh, st,
+                        DispatchKey{0, w->E / w->l.n}))
+        return 1;
+    long total = (long)A * (w->l.H / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > c->sm_count * 8) blocks = c->sm_count * 8;
+    launch_k(epw_push_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx,
+             (const int32_t *)w->perm, (const int32_t *)w->offsets, (int)A, w->topk,
+             w->l, w->peers, w->me, epoch, w->counter);
+    LAUNCHED();
+    return 0;
+}
+
+/* which: 0 = pushes of all sources have landed here; 1 = all returns have */
+extern "C" int apus_cuda_ep_wait_dev(ApusCudaEpWindow *w, int which, uint32_t epoch,
+                                     void *stream) {
+    if (epw_ready(w, "ep_wait_dev")) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    const uint32_t *flags =
+        reinterpret_cast<const uint32_t *>(w->base + (which ? w->l.fbk : w->l.fin));
+    launch_k(epw_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, flags, w->l.n,
+             epoch, c->d_status);
+    LAUNCHED();
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_window_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *L,
+                                               void *stream) {
+    if (epw_ready(w, "ep_window_experts_dev")) return 1;
+    return apus_cuda_experts_dev(L, (const uint16_t *)(w->base + w->l.rx),
+                                 (const int32_t *)(w->base + w->l.re),
+                                 (size_t)w->l.n * w->l.cap, w->y, stream);
+}
+
+extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
+                                       void *stream) {
+    if (epw_ready(w, "ep_return_dev")) return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    launch_k(epw_return_kernel, dim3(c->sm_count * 4), dim3(256), 0, (cudaStream_t)stream,
+             (const uint16_t *)w->y, w->l, w->peers, w->me, epoch, w->counter + 1);
+    LAUNCHED();
+    return 0;
+}
+
+/* The shared expert of the rank's own tokens: d_sy [T,H] BF16 (c/layer.h:350-353). */
+extern "C" int apus_cuda_ep_shared_dev(ApusCudaLayer *L, const uint16_t *d_x, size_t T,
+                                       uint16_t *d_sy, void *stream) {
+    if (!L || !d_x || !d_sy || !T) return fail("ep_shared_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const ApusCudaMoeCfg &cfg = L->cfg;
+    ApusCudaMoeCfg cx = cfg;
+    cx.top_k = 1;
+    const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
+    if (prefill && ensure_maps(L)) return 1;
+    BlockBufs b;
+    block_layout(cx, T, nullptr, &b, prefill);
+    if (arena_reserve(c->ws, b.total)) return 1;
+    if (block_layout(cx, T, &c->ws, &b, prefill)) return 1;
+    CU_OK(cudaMemsetAsync(b.d.counts, 0, cfg.experts * 4, st));
+    CU_OK(cudaMemsetAsync(b.d.offsets, 0, (cfg.experts + 1) * 4, st));
+    CU_OK(cudaMemsetAsync(b.d.n_groups, 0, 4, st));
+    if (prefill) {
+        const int before = c->last_block_launches;
+        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
+                                (int)L->e_begin, d_x, (int)T, 0, 1, true, b.d, b.xg,
+                                b.act, b.sa, b.eo, d_sy, b.tiles, c->d_status, st,
+                                &c->last_block_launches, nullptr))
+            return fail("%s", prefill_last_error());
+        c->launches += (uint64_t)(c->last_block_launches - before);
+        return 0;
+    }
+    if (run_decode_experts(c, L, d_x, (int)T, 1, 0, b, true, b.eo, st)) return 1;
+    CU_OK(cudaMemcpyAsync(d_sy, b.sy, T * cfg.hidden * 2, cudaMemcpyDeviceToDevice, st));
+    return 0;
+}
+
+/* out = rnd(rnd(sum_j w_j * y_j) + rnd(sy * rnd(sigmoid(sgl)))) with the returned
+ * rows of the window as y (c/layer.h:349,356-360). */
+extern "C" int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *L, size_t T,
+                                        const int32_t *d_pos, const uint16_t *d_w,
+                                        const uint16_t *d_sy, const uint16_t *d_sgl,
+                                        uint16_t *d_out, void *stream) {
+    if (epw_ready(w, "ep_combine_dev")) return 1;
+    if (!L || !T || !d_pos || !d_w || !d_sy || !d_sgl || !d_out ||
+        T * L->cfg.top_k > (size_t)w->l.cap)
+        return fail("ep_combine_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    return run_finalize(c, L->cfg, (int)T, (const uint16_t *)(w->base + w->l.by), d_pos,
+                        d_w, d_sy, d_sgl, d_out, nullptr, (cudaStream_t)stream);
 }
 
 /* ------------------------------------------------------------------------ */

@@ -39,7 +39,10 @@ struct DispatchKey {
     int base;
     int div;
 };
+/* An id of -1 is an empty slot: skipped without complaint (key -2).  Any other
+ * id outside the key range is an error (key -1 or >= E). */
 __device__ __forceinline__ int dispatch_key(int raw, DispatchKey kx) {
+    if (raw == -1) return -2;
     const int v = raw - kx.base;
     return v < 0 ? -1 : v / kx.div;
 }
@@ -80,7 +83,7 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     for (int s = 0; s < DISPATCH_UNIT / 32; s++) {
         const int a = a_lo + s * 32 + lane;
         int k = (a < A) ? dispatch_key(idx[a], kx) : -1;
-        if (a < A && (k < 0 || k >= E)) {
+        if (a < A && (k == -1 || k >= E)) {
             set_status(status, ST_BAD_INDEX);
             k = -1;
         }
@@ -168,7 +171,10 @@ dispatch_hist_kernel(const int32_t *__restrict__ idx, int A, int E,
         const int a_hi = min(A, a_lo + DISPATCH_UNIT);
         for (int a = a_lo + lane; a < a_hi; a += 32) {
             int k = dispatch_key(idx[a], kx);
-            if (k < 0 || k >= E) { set_status(status, ST_BAD_INDEX); continue; }
+            if (k < 0 || k >= E) {
+                if (k != -2) set_status(status, ST_BAD_INDEX);
+                continue;
+            }
             atomicAdd(&h[k], 1);
         }
         __syncwarp();

@@ -268,13 +268,16 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
     }
 }
 
-/* xg[p, :] = x[perm[p] / TK, :] — the rows of c/layer.h:603-605's memcpy */
+/* xg[p, :] = x[perm[p] / TK, :] — the rows of c/layer.h:603-605's memcpy.
+ * n_valid (optional): how many of the A slots hold an assignment (empty slots
+ * have no entry in perm). */
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint16_t *__restrict__ x,
                    const int32_t *__restrict__ perm, int A, int H, int TK,
-                   uint16_t *__restrict__ xg) {
+                   uint16_t *__restrict__ xg, const int32_t *__restrict__ n_valid) {
     pdl_enter();
     const int c8 = H / 8;
+    if (n_valid) A = min(A, max(*n_valid, 0));
     const long total = (long)A * c8;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long)gridDim.x * blockDim.x) {
@@ -785,7 +788,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
         launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H,
-                 TK, xg);
+                 TK, xg, (const int32_t *)(d.offsets + E));
         (*launches)++;
     }
     if (mark) mark(APUS_CUDA_STAGE_GATHER);

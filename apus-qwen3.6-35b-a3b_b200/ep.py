@@ -109,3 +109,80 @@ class CudaOps:
                               pos.data_ptr(), w.data_ptr(), sgl.data_ptr(),
                               out.data_ptr(), stream=self._s())
         return out
+
+
+class PeerWindowBlock:
+    """The same block step with the two exchanges done by kernels that store
+    straight into the peers' memory (apus_cuda_ep_push_dev / _return_dev): no
+    collective on the data path and no host synchronisation inside a step.
+    torch.distributed is used once, to hand round the windows' IPC handles."""
+
+    def __init__(self, be, layer, cfg, rank, world, max_tokens, group=None,
+                 window=None):
+        import torch.distributed as dist
+        assert cfg["experts"] % world == 0
+        self.be, self.layer, self.cfg = be, layer, cfg
+        self.rank, self.world, self.max_tokens = rank, world, max_tokens
+        self.epoch = 0
+        self.win = window or be.ep_window_create(
+            max_tokens, cfg["top_k"], cfg["hidden"], cfg["experts"], world, rank)
+        self.owns = window is None
+        if window is None and world > 1:
+            mine = be.ep_window_handle(self.win)
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            for r in range(world):
+                if r != rank:
+                    be.ep_window_attach(self.win, r, handles[r])
+            dist.barrier(group=group)
+
+    def close(self):
+        if self.owns and self.win:
+            self.be.ep_window_destroy(self.win)
+        self.win = None
+
+    def _s(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    # the step in three parts, so that a test can run several ranks in one
+    # process: all `begin`s before any `middle`, all `middle`s before any `end`
+    def begin(self, x):
+        T, H = x.shape
+        TK = self.cfg["top_k"]
+        assert T <= self.max_tokens
+        self.epoch += 1
+        st = dict(x=x)
+        st["idx"] = torch.empty((T, TK), dtype=torch.int32, device=x.device)
+        st["w"] = torch.empty((T, TK), dtype=torch.int16, device=x.device)
+        st["sgl"] = torch.empty((T,), dtype=torch.int16, device=x.device)
+        st["pos"] = torch.empty((T * TK,), dtype=torch.int32, device=x.device)
+        st["sy"] = torch.empty((T, H), dtype=torch.int16, device=x.device)
+        be, s = self.be, self._s()
+        be.ep_route_dev(self.layer, x.data_ptr(), T, st["idx"].data_ptr(),
+                        st["w"].data_ptr(), st["sgl"].data_ptr(), stream=s)
+        be.ep_push_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
+                       self.epoch, st["pos"].data_ptr(), stream=s)
+        be.ep_shared_dev(self.layer, x.data_ptr(), T, st["sy"].data_ptr(),
+                         stream=s)
+        return st
+
+    def middle(self):
+        be, s = self.be, self._s()
+        be.ep_wait_dev(self.win, 0, self.epoch, stream=s)
+        be.ep_window_experts_dev(self.win, self.layer, stream=s)
+        be.ep_return_dev(self.win, self.epoch, stream=s)
+
+    def end(self, st):
+        be, s = self.be, self._s()
+        x = st["x"]
+        out = torch.empty_like(x)
+        be.ep_wait_dev(self.win, 1, self.epoch, stream=s)
+        be.ep_combine_dev(self.win, self.layer, x.shape[0], st["pos"].data_ptr(),
+                          st["w"].data_ptr(), st["sy"].data_ptr(),
+                          st["sgl"].data_ptr(), out.data_ptr(), stream=s)
+        return out
+
+    def forward(self, x):
+        st = self.begin(x)
+        self.middle()
+        return self.end(st)

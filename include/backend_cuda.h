@@ -284,6 +284,55 @@ int apus_cuda_ep_finish_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
                             uint16_t *d_out, const ApusCudaMoeTrace *d_tr,
                             void *stream);
 
+/* ---- expert parallelism without a collective library on the data path ------
+ * Net-new (no reference counterpart).  Steps 2, 3 and 5 above as kernels that
+ * store straight into the peers' memory over NVLink, with no host
+ * synchronisation inside a step.  Every rank creates one window (a device
+ * allocation holding, per source rank, a region of max_tokens*topk rows and
+ * their expert ids, plus the rows returned to it), publishes its CUDA IPC
+ * handle, and attaches every peer's.  One block step with epoch e (a counter
+ * the caller increments per step, the same on all ranks, starting at 1):
+ *
+ *   apus_cuda_ep_route_dev          idx, w, sgl of the rank's tokens
+ *   apus_cuda_ep_push_dev           rows and ids into the owners' windows;
+ *                                   d_pos as in apus_cuda_ep_pack_dev
+ *   apus_cuda_ep_shared_dev         shared expert (overlaps the peers' pushes)
+ *   apus_cuda_ep_wait_dev(0, e)     every source's push has landed here
+ *   apus_cuda_ep_window_experts_dev resident experts on the received rows
+ *   apus_cuda_ep_return_dev         outputs into the senders' windows
+ *   apus_cuda_ep_wait_dev(1, e)     every peer's return has landed here
+ *   apus_cuda_ep_combine_dev        weighted sum in slot order, gate, add
+ *
+ * All ranks must run the same sequence of steps.  Waits are bounded (about two
+ * seconds); one that runs out sets apus_cuda_last_block_status() to 6 and the
+ * step's output is not valid, but the context stays usable.  The result equals
+ * apus_cuda_moe_block_dev bit for bit, as for the collective-based steps. */
+typedef struct ApusCudaEpWindow ApusCudaEpWindow;
+int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t H, size_t E,
+                               size_t n_ranks, size_t rank, ApusCudaEpWindow **out);
+void apus_cuda_ep_window_destroy(ApusCudaEpWindow *w);
+/* size of the opaque handle a rank publishes (a CUDA IPC memory handle) */
+size_t apus_cuda_ep_window_handle_bytes(void);
+int apus_cuda_ep_window_handle(ApusCudaEpWindow *w, void *out_handle);
+/* map the window of rank `peer` (another process on this node) */
+int apus_cuda_ep_window_attach(ApusCudaEpWindow *w, size_t peer, const void *handle);
+/* the same for a window created in this process (several ranks per process) */
+int apus_cuda_ep_window_attach_local(ApusCudaEpWindow *w, size_t peer,
+                                     ApusCudaEpWindow *other);
+int apus_cuda_ep_push_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
+                          const int32_t *d_idx, size_t T, uint32_t epoch,
+                          int32_t *d_pos, void *stream);
+int apus_cuda_ep_wait_dev(ApusCudaEpWindow *w, int which, uint32_t epoch, void *stream);
+int apus_cuda_ep_window_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer,
+                                    void *stream);
+int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch, void *stream);
+int apus_cuda_ep_shared_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
+                            uint16_t *d_sy, void *stream);
+int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer, size_t T,
+                             const int32_t *d_pos, const uint16_t *d_w,
+                             const uint16_t *d_sy, const uint16_t *d_sgl,
+                             uint16_t *d_out, void *stream);
+
 /* ---- stages of the block, device pointers (kernel-level tests) ---------- */
 int apus_cuda_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
                         int32_t *d_idx, uint16_t *d_w, void *stream);

@@ -103,3 +103,85 @@ def test_ep_world_size_one_process_group(gpu, be, synth):
         assert np.array_equal(out.cpu().numpy().view(np.uint16), whole)
     finally:
         dist.destroy_process_group()
+
+
+def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1):
+    """N ranks in this process, one peer window each, attached to one another
+    by pointer.  All pushes are launched before the first wait, all returns
+    before the first wait for them, so no kernel ever waits on a later one."""
+    T, H = x.shape
+    per, E = T // N, cfg["experts"]
+    layers = [be.layer_create(cfg, W, r * E // N, (r + 1) * E // N)
+              for r in range(N)]
+    wins = [be.ep_window_create(per, cfg["top_k"], H, E, N, r) for r in range(N)]
+    for r in range(N):
+        for q in range(N):
+            if q != r:
+                be.ep_window_attach_local(wins[r], q, wins[q])
+    blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, per, window=wins[r])
+            for r in range(N)]
+    xs = [torch.from_numpy(x[r * per:(r + 1) * per].view(np.int16).copy()).cuda()
+          for r in range(N)]
+    for _ in range(steps):
+        sts = [blks[r].begin(xs[r]) for r in range(N)]
+        for r in range(N):
+            blks[r].middle()
+        outs = [blks[r].end(sts[r]) for r in range(N)]
+    torch.cuda.synchronize()
+    assert be.last_block_status() == 0
+    out = np.concatenate([o.cpu().numpy().view(np.uint16) for o in outs])
+    for w in wins:
+        be.ep_window_destroy(w)
+    for l in layers:
+        be.layer_destroy(l)
+    return out
+
+
+@pytest.mark.parametrize("path", ["gemm", "gemv"])
+@pytest.mark.parametrize("N,T", [(2, 20), (2, 200), (4, 400), (8, 1024)])
+def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, monkeypatch):
+    """The exchange through peer windows (rows stored straight into the
+    owner's memory, outputs stored straight back) gives the single-GPU block
+    bit for bit; three steps in a row reuse the windows."""
+    import torch
+    from apus_b200 import ep
+    monkeypatch.setenv("APUS_CUDA_DECODE_MAX_T",
+                       "0" if path == "gemm" else "1000000")
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
+        x = synth.host_x(be, T, cfg["hidden"], seed=13)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        got = emulate_windows(be, ep, torch, cfg, W, x, N, steps=3)
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
+
+
+def test_peer_window_skewed_router_one_owner(be, synth):
+    """Every assignment of every token goes to experts of rank 0: the other
+    ranks receive nothing and return nothing."""
+    import torch
+    from apus_b200 import ep
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=17, sigma=0.05)
+        # router rows of experts 0..15 get a large positive last column
+        rw = synth.bf16_to_f32(W["rtr_w"]).copy()
+        rw[:16, -1] = 4.0
+        rw[16:, -1] = -4.0
+        W = dict(W)
+        W["rtr_w"] = synth.f32_to_bf16(rw)
+        x = synth.bf16_to_f32(synth.host_x(be, 64, 512, seed=17)).copy()
+        x[:, -1] = 8.0
+        x = synth.f32_to_bf16(x)
+        whole = be.moe_block(cfg, W, x, trace=True)
+        assert int(whole["idx"].max()) < 16
+        got = emulate_windows(be, ep, torch, cfg, W, x, 4)
+        assert np.array_equal(got, whole["out"])
+    finally:
+        be.disable()
