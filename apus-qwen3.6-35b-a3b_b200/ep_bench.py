@@ -33,7 +33,11 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     x_all = synth.host_x(be, T * world, H, seed=args.seed)
     x_host = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
     d_x = torch.from_numpy(x_host).cuda()
-    blk = ep.EPBlock(ep.CudaOps(be, layer, cfg), cfg, rank, world)
+    exchange = getattr(args, "exchange", "peer")
+    if exchange == "peer":
+        blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T)
+    else:
+        blk = ep.EPBlock(ep.CudaOps(be, layer, cfg), cfg, rank, world)
 
     def step():
         return blk.forward(d_x)
@@ -77,8 +81,19 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
                        device="cuda")
     dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e.item())
-    rows = torch.tensor([blk.last_sent_rows, blk.last_recv_rows],
-                        dtype=torch.float64, device="cuda")
+    if exchange == "peer":
+        # rows that left this GPU: assignments owned by another rank
+        idx = torch.empty((T, cfg["top_k"]), dtype=torch.int32, device="cuda")
+        w_ = torch.empty((T, cfg["top_k"]), dtype=torch.int16, device="cuda")
+        sgl_ = torch.empty((T,), dtype=torch.int16, device="cuda")
+        be.ep_route_dev(layer, d_x.data_ptr(), T, idx.data_ptr(), w_.data_ptr(),
+                        sgl_.data_ptr(), stream=sp)
+        torch.cuda.synchronize()
+        sent = int(((idx // per) != rank).sum().item())
+        rows = torch.tensor([sent, sent], dtype=torch.float64, device="cuda")
+    else:
+        rows = torch.tensor([blk.last_sent_rows, blk.last_recv_rows],
+                            dtype=torch.float64, device="cuda")
     dist.all_reduce(rows, op=dist.ReduceOp.SUM)
     dist.all_reduce(launches, op=dist.ReduceOp.SUM)
     if sampler is not None:
@@ -105,7 +120,10 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
             "gpu_launches": int(launches.item()),
             "exchange": {"rows_sent_per_step": float(rows[0]),
                          "bytes_each_way_per_step": float(rows[0]) * H * 2,
-                         "collective": "all_to_all_single (NCCL), rows as bytes"},
+                         "collective": ("none: kernels store rows into the owner's "
+                                        "memory over NVLink (CUDA IPC windows)"
+                                        if exchange == "peer" else
+                                        "all_to_all_single (NCCL), rows as bytes")},
             "block": {"device_status": status},
         }
         if sampler is not None:
@@ -117,10 +135,13 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
                    + 2 * T * H * 2 + 2 * float(rows[0]) / world * H * 2)
         ach = per_gpu / (ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": "whole step on one GPU (all "
-                            "kernels + NCCL all-to-all)", "achieved": ach,
+                            "kernels + exchange)", "achieved": ach,
                             "peak": peaks["hbm_gbs"], "peak_source": peaks["_source"],
                             "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                             "traffic": None,
                             "algorithmic_bytes_per_launch": per_gpu}
         print(json.dumps(line))
+    dist.barrier()
+    if exchange == "peer":
+        blk.close()
     dist.destroy_process_group()

@@ -328,6 +328,9 @@ def main():
     ap.add_argument("--chain", action="store_true",
                     help="with a layer stack: chain the layers through rmsnorm "
                          "and the residual add instead of one batch per layer")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="multi-GPU arm: rows exchanged by kernels that store into "
+                         "the peers' memory (default), or by NCCL all-to-all")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from the host instead of "
                          "replaying a captured CUDA graph")

@@ -185,3 +185,36 @@ def test_peer_window_skewed_router_one_owner(be, synth):
         assert np.array_equal(got, whole["out"])
     finally:
         be.disable()
+
+
+@pytest.mark.parametrize("T", [24, 300])
+def test_peer_window_two_processes(be, synth, T, tmp_path):
+    """Two real ranks, one per GPU, windows mapped through CUDA IPC: the rows
+    cross NVLink by the kernels' own stores.  Three steps; the last one must
+    equal the single-GPU block bit for bit."""
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                          "ep_peer_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = 29800 + os.getpid() % 100
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+         "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+         "--master-port", str(port), worker, str(tmp_path), str(T), "3"],
+        env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    got = np.concatenate([np.load(tmp_path / f"out_{k}.npy") for k in range(2)])
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
+        x = synth.host_x(be, 2 * T, cfg["hidden"], seed=102)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
