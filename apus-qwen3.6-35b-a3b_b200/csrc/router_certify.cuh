@@ -45,9 +45,10 @@ constexpr int RC_TT = 8;            /* tokens per CTA */
 constexpr int RC_THREADS = 256;      /* one warp per token in the first phase */
 constexpr int RC_XPAD = 4;          /* floats between token rows: rows on
                                      * different bank groups */
-constexpr int RC_CW = 3;            /* warps that walk chains */
+constexpr int RC_CW = 4;            /* warps that walk chains: 128 pairs in one round (8 tokens
+                                     * give 86 on average; a second round doubles the latency) */
 constexpr int RC_BLK = 32;          /* weights per staged row block */
-constexpr int RC_AHEAD = 3;         /* row blocks requested ahead of the one in use */
+constexpr int RC_AHEAD = 2;         /* row blocks requested ahead of the one in use */
 constexpr int RC_NBUF = RC_AHEAD + 1;
 constexpr int RC_WPITCH = RC_BLK * 2 + 16;   /* bytes per staged row block */
 constexpr int ST_BOUND_VIOLATED = 5;
