@@ -138,7 +138,7 @@ def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1):
 
 
 @pytest.mark.parametrize("path", ["gemm", "gemv"])
-@pytest.mark.parametrize("N,T", [(2, 20), (2, 200), (4, 400), (8, 1024)])
+@pytest.mark.parametrize("N,T", [(2, 20), (2, 200), (4, 400), (8, 1024), (4, 2400)])
 def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, monkeypatch):
     """The exchange through peer windows (rows stored straight into the
     owner's memory, outputs stored straight back) gives the single-GPU block
