@@ -228,29 +228,31 @@ build_tiles_kernel(const int32_t *__restrict__ counts,
         total_b += warp_tot[1][w];
     }
     const int first_a = base_a + inc_a - nt_a, first_b = base_b + inc_b - nt_b;
+    /* The shared expert is dense over the tokens (always full-width tiles) and
+     * its tiles come FIRST.  They are the expensive ones — wide MMAs fed from
+     * L2 and a long epilogue — and at the end of the list they were the
+     * kernel's tail: a few CTAs computing while HBM idles.  At the front they
+     * run beside the routed tiles' weight stream. */
+    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
+    const int sh_a = nts_a * m_gu_sh, sh_b = nts_b * m_dn;
     if (tid < E && cnt > 0) {
         const int off = offsets[tid];
         for (int m = 0; m < m_gu; m++)
             for (int n = 0; n < nt_a; n++)
-                tl.gu[(size_t)first_a * m_gu + (size_t)m * nt_a + n] = make_int4(
-                    tid, m, off + n * bn_gu, min(bn_gu, cnt - n * bn_gu));
+                tl.gu[(size_t)sh_a + (size_t)first_a * m_gu + (size_t)m * nt_a + n] =
+                    make_int4(tid, m, off + n * bn_gu, min(bn_gu, cnt - n * bn_gu));
         for (int m = 0; m < m_dn; m++)
             for (int n = 0; n < nt_b; n++)
-                tl.dn[(size_t)first_b * m_dn + (size_t)m * nt_b + n] = make_int4(
-                    tid, m, off + n * bn_dn, min(bn_dn, cnt - n * bn_dn));
+                tl.dn[(size_t)sh_b + (size_t)first_b * m_dn + (size_t)m * nt_b + n] =
+                    make_int4(tid, m, off + n * bn_dn, min(bn_dn, cnt - n * bn_dn));
     }
-    /* shared expert: dense over all T tokens */
-    /* the shared expert is dense over the tokens: always full-width tiles */
-    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
-    for (int i = tid; i < nts_a * m_gu_sh; i += blockDim.x) {
+    for (int i = tid; i < sh_a; i += blockDim.x) {
         int m = i / nts_a, n = i - m * nts_a;
-        tl.gu[(size_t)total_a * m_gu + i] =
-            make_int4(E, m, n * PG_BN_GU, min(PG_BN_GU, T - n * PG_BN_GU));
+        tl.gu[i] = make_int4(E, m, n * PG_BN_GU, min(PG_BN_GU, T - n * PG_BN_GU));
     }
-    for (int i = tid; i < nts_b * m_dn; i += blockDim.x) {
+    for (int i = tid; i < sh_b; i += blockDim.x) {
         int m = i / nts_b, n = i - m * nts_b;
-        tl.dn[(size_t)total_b * m_dn + i] =
-            make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
+        tl.dn[i] = make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
     }
     if (tid < E) {
         tl.done[tid] = 0;
