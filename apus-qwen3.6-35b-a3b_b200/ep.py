@@ -124,17 +124,36 @@ class PeerWindowBlock:
         self.be, self.layer, self.cfg = be, layer, cfg
         self.rank, self.world, self.max_tokens = rank, world, max_tokens
         self.epoch = 0
-        self.win = window or be.ep_window_create(
-            max_tokens, cfg["top_k"], cfg["hidden"], cfg["experts"], world, rank)
         self.owns = window is None
-        if window is None and world > 1:
+        self.win = window
+        if window is not None:
+            return
+        # every rank goes through the same collective calls whatever fails on
+        # it, so that a rank without peer access cannot leave the others waiting
+        err, mine = None, None
+        try:
+            self.win = be.ep_window_create(max_tokens, cfg["top_k"], cfg["hidden"],
+                                           cfg["experts"], world, rank)
             mine = be.ep_window_handle(self.win)
+        except Exception as e:
+            err = e
+        if world > 1:
             handles = [None] * world
             dist.all_gather_object(handles, mine, group=group)
-            for r in range(world):
-                if r != rank:
-                    be.ep_window_attach(self.win, r, handles[r])
-            dist.barrier(group=group)
+            if err is None and all(h is not None for h in handles):
+                try:
+                    for r in range(world):
+                        if r != rank:
+                            be.ep_window_attach(self.win, r, handles[r])
+                except Exception as e:
+                    err = e
+            oks = [None] * world
+            dist.all_gather_object(oks, err is None, group=group)
+            if err is None and not all(oks):
+                err = RuntimeError("a peer could not map the windows")
+        if err is not None:
+            self.close()
+            raise RuntimeError(f"peer windows: {err}")
 
     def close(self):
         if self.owns and self.win:

@@ -2,6 +2,7 @@
 per GPU (launched by torch.distributed.run)."""
 import json
 import os
+import sys
 import time
 
 import numpy as np
@@ -34,9 +35,22 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     x_host = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
     d_x = torch.from_numpy(x_host).cuda()
     exchange = getattr(args, "exchange", "peer")
+    exchange_note = None
     if exchange == "peer":
-        blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T)
-    else:
+        # every rank must take the same arm: agree on whether the windows came up
+        ok = torch.ones(1, device="cuda")
+        try:
+            blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T)
+        except Exception as e:             # e.g. no peer access between two GPUs
+            exchange_note = f"{type(e).__name__}: {e}"
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            if rank == 0:
+                print(f"peer windows unavailable ({exchange_note}); using the NCCL "
+                      "all-to-all exchange", file=sys.stderr)
+            exchange = "nccl"
+    if exchange != "peer":
         blk = ep.EPBlock(ep.CudaOps(be, layer, cfg), cfg, rank, world)
 
     def step():
@@ -120,6 +134,7 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
             "gpu_launches": int(launches.item()),
             "exchange": {"rows_sent_per_step": float(rows[0]),
                          "bytes_each_way_per_step": float(rows[0]) * H * 2,
+                         "requested": getattr(args, "exchange", "peer"),
                          "collective": ("none: kernels store rows into the owner's "
                                         "memory over NVLink (CUDA IPC windows)"
                                         if exchange == "peer" else
