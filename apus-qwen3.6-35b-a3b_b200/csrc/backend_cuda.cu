@@ -568,9 +568,13 @@ static size_t dispatch_scratch_bytes(size_t A, size_t E) {
     return units * E * sizeof(int32_t);
 }
 
+/* tp (optional, in/out): tile lists wanted with the dispatch.  The one-CTA
+ * kernel builds them in the same launch and leaves tp->on set; the three-pass
+ * form clears it and the caller launches build_tiles_kernel. */
 static int launch_dispatch(Ctx *c, const int32_t *didx, int A, int E,
                            DispatchOut o, int32_t *unit_hist,
-                           cudaStream_t st, DispatchKey kx = DispatchKey{0, 1}) {
+                           cudaStream_t st, DispatchKey kx = DispatchKey{0, 1},
+                           TilePlan *tp = nullptr) {
     if (E < 1 || E > 1024) return fail("dispatch: unsupported E=%d", E);
     if (A <= DISPATCH_SMALL_MAX) {
         const size_t smem = (size_t)32 * E * sizeof(int);
@@ -581,10 +585,14 @@ static int launch_dispatch(Ctx *c, const int32_t *didx, int A, int E,
                                        32 * 1024 * (int)sizeof(int)));
             attr_set = true;
         }
-        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), smem, st, didx, A, E, kx, o, c->d_status);
+        TilePlan none;
+        memset(&none, 0, sizeof none);
+        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), smem, st, didx, A, E, kx, o,
+                 c->d_status, tp ? *tp : none);
         LAUNCHED();
         return 0;
     }
+    if (tp) tp->on = 0;
     int units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
     int blocks = (units + DISPATCH_WARPS - 1) / DISPATCH_WARPS;
     size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);
@@ -1111,7 +1119,12 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
         b.d.grp_n = nullptr;
         b.d.n_groups = nullptr;
     }
-    if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st)) return 1;
+    TilePlan plan;
+    memset(&plan, 0, sizeof plan);
+    if (prefill) plan = prefill_tile_plan(cfg, Ti, true, Ti * TK, b.tiles);
+    if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st, DispatchKey{0, 1},
+                        prefill ? &plan : nullptr))
+        return 1;
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (prefill) {
         const int before = c->last_block_launches;
@@ -1120,7 +1133,7 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
                                 (int)L->e_begin, d_ln2, Ti, Ti * TK, TK, true, b.d,
                                 b.xg, b.act, b.sa, b.eo, b.sy, b.tiles,
                                 c->d_status, st, &c->last_block_launches,
-                                mark_cb))
+                                mark_cb, plan.on ? &plan : nullptr))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
     } else {
@@ -1422,15 +1435,19 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
         b.d.grp_n = nullptr;
         b.d.n_groups = nullptr;
     }
+    TilePlan plan;
+    memset(&plan, 0, sizeof plan);
+    if (prefill) plan = prefill_tile_plan(cx, (int)R, false, (int)R, b.tiles);
     if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
-                        DispatchKey{(int)L->e_begin, 1}))
+                        DispatchKey{(int)L->e_begin, 1}, prefill ? &plan : nullptr))
         return 1;
     if (prefill) {
         const int before = c->last_block_launches;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x,
                                 (int)R, (int)R, 1, false, b.d, b.xg, b.act, b.sa,
                                 d_y, b.sy, b.tiles, c->d_status, st,
-                                &c->last_block_launches, nullptr))
+                                &c->last_block_launches, nullptr,
+                                plan.on ? &plan : nullptr))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
         return 0;
@@ -1876,7 +1893,9 @@ extern "C" int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T,
         CU_OK(cudaFuncSetAttribute(dispatch_small_kernel,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    32 * 1024 * (int)sizeof(int)));
-        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), (size_t)32 * E * sizeof(int), st, d_idx, Ai, Ei, DispatchKey{0, 1}, o, status);
+        TilePlan none;
+        memset(&none, 0, sizeof none);
+        launch_k(dispatch_small_kernel, dim3(1), dim3(1024), (size_t)32 * E * sizeof(int), st, d_idx, Ai, Ei, DispatchKey{0, 1}, o, status, none);
     } else {
         const int blocks = (int)((units + DISPATCH_WARPS - 1) / DISPATCH_WARPS);
         const size_t smem = (size_t)DISPATCH_WARPS * E * sizeof(int);

@@ -58,6 +58,110 @@ struct DispatchOut {
     int32_t *n_groups;   /* [1] */
 };
 
+/* ---- tile list --------------------------------------------------------------
+ * One entry per (expert, weight-row tile, token-row tile): {v, m, row0, nrows}.
+ * v == E is the shared expert (rows are token indices); otherwise row0 is a
+ * position in dispatch order.  Tiles that share weights are adjacent, so when
+ * an expert has several token tiles its weights come from HBM once and from
+ * L2 afterwards. */
+struct TileLists {
+    int4 *gu;        /* gate_up tiles */
+    int4 *dn;        /* down tiles */
+    int *n_gu, *n_dn;
+    /* per expert (index E: the shared expert): gate_up tiles finished so far
+     * (counted once per epilogue warp) and how many there are */
+    int *done, *need;
+    /* next tile to hand out, one counter per expert kernel (gate_up, down) */
+    int *sched;
+};
+
+/* What the tile lists are built from (host side fills it in) */
+struct TilePlan {
+    int on;                 /* 0: no tile lists wanted */
+    int T;                  /* tokens the shared expert runs over (0: none) */
+    int m_gu, m_gu_sh, m_dn;   /* weight-row tiles per expert: gate_up, shared gate_up, down */
+    int bn_gu, bn_dn;       /* token rows per routed tile */
+    int bn_sh_gu, bn_sh_dn; /* token rows per shared-expert tile */
+    TileLists tl;
+};
+
+/* All 1024 threads of a one-CTA kernel call this with thread e < E holding
+ * expert e's row count and first sorted position. */
+__device__ __forceinline__ void build_tiles_body(int cnt, int off, int E, int T, int m_gu,
+                                                 int m_gu_sh, int m_dn, int bn_gu,
+                                                 int bn_dn, int bn_sh_gu, int bn_sh_dn,
+                                                 TileLists tl) {
+    __shared__ int warp_tot[2][32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nt_a = (cnt + bn_gu - 1) / bn_gu;
+    const int nt_b = (cnt + bn_dn - 1) / bn_dn;
+    int inc_a = nt_a, inc_b = nt_b;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int va = __shfl_up_sync(0xffffffffu, inc_a, d);
+        int vb = __shfl_up_sync(0xffffffffu, inc_b, d);
+        if (lane >= d) { inc_a += va; inc_b += vb; }
+    }
+    if (lane == 31) { warp_tot[0][warp] = inc_a; warp_tot[1][warp] = inc_b; }
+    __syncthreads();
+    int base_a = 0, total_a = 0, base_b = 0, total_b = 0;
+    for (int w = 0; w < 32; w++) {
+        if (w < warp) { base_a += warp_tot[0][w]; base_b += warp_tot[1][w]; }
+        total_a += warp_tot[0][w];
+        total_b += warp_tot[1][w];
+    }
+    const int first_a = base_a + inc_a - nt_a, first_b = base_b + inc_b - nt_b;
+    /* The shared expert is dense over the tokens (always full-width tiles) and
+     * its tiles come FIRST.  They are the expensive ones — wide MMAs fed from
+     * L2 and a long epilogue — and at the end of the list they were the
+     * kernel's tail: a few CTAs computing while HBM idles.  At the front they
+     * run beside the routed tiles' weight stream. */
+    const int nts_a = (T + bn_sh_gu - 1) / bn_sh_gu, nts_b = (T + bn_sh_dn - 1) / bn_sh_dn;
+    const int sh_a = nts_a * m_gu_sh, sh_b = nts_b * m_dn;
+    if (tid < E && cnt > 0) {
+        for (int m = 0; m < m_gu; m++)
+            for (int n = 0; n < nt_a; n++)
+                tl.gu[(size_t)sh_a + (size_t)first_a * m_gu + (size_t)m * nt_a + n] =
+                    make_int4(tid, m, off + n * bn_gu, min(bn_gu, cnt - n * bn_gu));
+        for (int m = 0; m < m_dn; m++)
+            for (int n = 0; n < nt_b; n++)
+                tl.dn[(size_t)sh_b + (size_t)first_b * m_dn + (size_t)m * nt_b + n] =
+                    make_int4(tid, m, off + n * bn_dn, min(bn_dn, cnt - n * bn_dn));
+    }
+    for (int i = tid; i < sh_a; i += blockDim.x) {
+        int m = i / nts_a, n = i - m * nts_a;
+        tl.gu[i] = make_int4(E, m, n * bn_sh_gu, min(bn_sh_gu, T - n * bn_sh_gu));
+    }
+    for (int i = tid; i < sh_b; i += blockDim.x) {
+        int m = i / nts_b, n = i - m * nts_b;
+        tl.dn[i] = make_int4(E, m, n * bn_sh_dn, min(bn_sh_dn, T - n * bn_sh_dn));
+    }
+    if (tid < E) {
+        tl.done[tid] = 0;
+        tl.need[tid] = nt_a * m_gu;
+    }
+    if (tid == 0) {
+        tl.done[E] = 0;
+        tl.need[E] = nts_a * m_gu_sh;
+        tl.sched[0] = 0;
+        tl.sched[1] = 0;
+        tl.done[E + 1] = 0;                               /* all of them together */
+        tl.need[E + 1] = total_a * m_gu + nts_a * m_gu_sh;
+        *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
+        *tl.n_dn = total_b * m_dn + nts_b * m_dn;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+build_tiles_kernel(const int32_t *__restrict__ counts,
+                   const int32_t *__restrict__ offsets, int E, TilePlan tp) {
+    pdl_enter();
+    const int tid = threadIdx.x;
+    build_tiles_body(tid < E ? counts[tid] : 0, tid < E ? offsets[tid] : 0, E, tp.T, tp.m_gu,
+                     tp.m_gu_sh, tp.m_dn, tp.bn_gu, tp.bn_dn, tp.bn_sh_gu, tp.bn_sh_dn,
+                     tp.tl);
+}
+
 /* ---- small problems: one block does everything -------------------------- */
 /* A <= 32 * DISPATCH_UNIT, E <= 1024; block = 1024 threads = 32 warps, each
  * warp owning one unit of up to 256 consecutive assignments.  Dynamic shared
@@ -66,7 +170,7 @@ constexpr int DISPATCH_SMALL_MAX = 32 * DISPATCH_UNIT;
 
 __global__ void __launch_bounds__(1024)
 dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
-                      DispatchKey kx, DispatchOut o, int *status) {
+                      DispatchKey kx, DispatchOut o, int *status, TilePlan tp) {
     pdl_enter();
     extern __shared__ int sm[];          /* [32][E] */
     __shared__ int warp_tot[32];
@@ -133,6 +237,10 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     if (tid == 1023) o.offsets[E] = base + inc;   /* == number of valid keys */
     __syncthreads();
     if (tid == 0 && o.n_groups) *o.n_groups = s_ngroups;
+    /* the grouped GEMMs' tile lists come out of the same counts: one launch less */
+    if (tp.on)
+        build_tiles_body(tid < E ? total : 0, tid < E ? off : 0, E, tp.T, tp.m_gu, tp.m_gu_sh,
+                         tp.m_dn, tp.bn_gu, tp.bn_dn, tp.bn_sh_gu, tp.bn_sh_dn, tp.tl);
     /* stable placement inside each warp's unit */
 #pragma unroll
     for (int s = 0; s < DISPATCH_UNIT / 32; s++) {

@@ -174,23 +174,6 @@ __device__ __forceinline__ bool pg_wait(uint64_t *bar, uint32_t parity,
     return false;
 }
 
-/* ---- tile list --------------------------------------------------------------
- * One entry per (expert, weight-row tile, token-row tile): {v, m, row0, nrows}.
- * v == E is the shared expert (rows are token indices); otherwise row0 is a
- * position in dispatch order.  Tiles that share weights are adjacent, so when
- * an expert has several token tiles its weights come from HBM once and from
- * L2 afterwards. */
-struct TileLists {
-    int4 *gu;        /* gate_up tiles */
-    int4 *dn;        /* down tiles */
-    int *n_gu, *n_dn;
-    /* per expert (index E: the shared expert): gate_up tiles finished so far
-     * (counted once per epilogue warp) and how many there are */
-    int *done, *need;
-    /* next tile to hand out, one counter per expert kernel (gate_up, down) */
-    int *sched;
-};
-
 inline size_t prefill_max_ntiles(size_t A, size_t T, size_t E) {
     return A / PG_BN + E + (T + PG_BN_GU - 1) / PG_BN_GU + 1;
 }
@@ -200,74 +183,6 @@ inline size_t prefill_tiles_bytes_for(const ApusCudaMoeCfg &c, size_t A,
     size_t m1 = (c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter) / PG_BM;
     size_t m2 = c.hidden / PG_BM;
     return (nt * m1 + nt * m2) * sizeof(int4) + 256 + (2 * (c.experts + 2) + 2) * sizeof(int);
-}
-
-__global__ void __launch_bounds__(1024)
-build_tiles_kernel(const int32_t *__restrict__ counts,
-                   const int32_t *__restrict__ offsets, int E, int T, int m_gu,
-                   int m_gu_sh, int m_dn, int bn_gu, int bn_dn, TileLists tl) {
-    pdl_enter();
-    __shared__ int warp_tot[2][32];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int cnt = tid < E ? counts[tid] : 0;
-    const int nt_a = (cnt + bn_gu - 1) / bn_gu;
-    const int nt_b = (cnt + bn_dn - 1) / bn_dn;
-    int inc_a = nt_a, inc_b = nt_b;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        int va = __shfl_up_sync(0xffffffffu, inc_a, d);
-        int vb = __shfl_up_sync(0xffffffffu, inc_b, d);
-        if (lane >= d) { inc_a += va; inc_b += vb; }
-    }
-    if (lane == 31) { warp_tot[0][warp] = inc_a; warp_tot[1][warp] = inc_b; }
-    __syncthreads();
-    int base_a = 0, total_a = 0, base_b = 0, total_b = 0;
-    for (int w = 0; w < 32; w++) {
-        if (w < warp) { base_a += warp_tot[0][w]; base_b += warp_tot[1][w]; }
-        total_a += warp_tot[0][w];
-        total_b += warp_tot[1][w];
-    }
-    const int first_a = base_a + inc_a - nt_a, first_b = base_b + inc_b - nt_b;
-    /* The shared expert is dense over the tokens (always full-width tiles) and
-     * its tiles come FIRST.  They are the expensive ones — wide MMAs fed from
-     * L2 and a long epilogue — and at the end of the list they were the
-     * kernel's tail: a few CTAs computing while HBM idles.  At the front they
-     * run beside the routed tiles' weight stream. */
-    const int nts_a = (T + PG_BN_GU - 1) / PG_BN_GU, nts_b = (T + PG_BN_DN - 1) / PG_BN_DN;
-    const int sh_a = nts_a * m_gu_sh, sh_b = nts_b * m_dn;
-    if (tid < E && cnt > 0) {
-        const int off = offsets[tid];
-        for (int m = 0; m < m_gu; m++)
-            for (int n = 0; n < nt_a; n++)
-                tl.gu[(size_t)sh_a + (size_t)first_a * m_gu + (size_t)m * nt_a + n] =
-                    make_int4(tid, m, off + n * bn_gu, min(bn_gu, cnt - n * bn_gu));
-        for (int m = 0; m < m_dn; m++)
-            for (int n = 0; n < nt_b; n++)
-                tl.dn[(size_t)sh_b + (size_t)first_b * m_dn + (size_t)m * nt_b + n] =
-                    make_int4(tid, m, off + n * bn_dn, min(bn_dn, cnt - n * bn_dn));
-    }
-    for (int i = tid; i < sh_a; i += blockDim.x) {
-        int m = i / nts_a, n = i - m * nts_a;
-        tl.gu[i] = make_int4(E, m, n * PG_BN_GU, min(PG_BN_GU, T - n * PG_BN_GU));
-    }
-    for (int i = tid; i < sh_b; i += blockDim.x) {
-        int m = i / nts_b, n = i - m * nts_b;
-        tl.dn[i] = make_int4(E, m, n * PG_BN_DN, min(PG_BN_DN, T - n * PG_BN_DN));
-    }
-    if (tid < E) {
-        tl.done[tid] = 0;
-        tl.need[tid] = nt_a * m_gu;
-    }
-    if (tid == 0) {
-        tl.done[E] = 0;
-        tl.need[E] = nts_a * m_gu_sh;
-        tl.sched[0] = 0;
-        tl.sched[1] = 0;
-        tl.done[E + 1] = 0;                               /* all of them together */
-        tl.need[E + 1] = total_a * m_gu + nts_a * m_gu_sh;
-        *tl.n_gu = total_a * m_gu + nts_a * m_gu_sh;
-        *tl.n_dn = total_b * m_dn + nts_b * m_dn;
-    }
 }
 
 /* xg[p, :] = x[perm[p] / TK, :] — the rows of c/layer.h:603-605's memcpy.
@@ -737,6 +652,41 @@ inline int pg_smem_bytes(bool gate_up) {
            256 /* barriers */;
 }
 
+/* Tile shapes and list storage for A routed rows and T tokens (the shared
+ * expert runs over them when do_shared) */
+inline TilePlan prefill_tile_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, int A,
+                                  void *tiles_ws) {
+    const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
+              E = (int)c.experts;
+    TilePlan p;
+    memset(&p, 0, sizeof p);
+    p.on = 1;
+    p.T = do_shared ? T : 0;
+    p.m_gu = I / PG_BM;
+    p.m_gu_sh = Is / PG_BM;
+    p.m_dn = H / PG_BM;
+    /* token box of the routed tiles: about twice the mean row count of an
+     * expert, so that nearly every expert is one tile and a tile does not pull
+     * rows it will not use through L2 */
+    int want = PG_BN_MIN;
+    while (want < PG_BN_DN && (long)want * E < 2L * A) want *= 2;
+    p.bn_gu = want < PG_BN_GU ? want : PG_BN_GU;
+    p.bn_dn = want < PG_BN_DN ? want : PG_BN_DN;
+    p.bn_sh_gu = PG_BN_GU;
+    p.bn_sh_dn = PG_BN_DN;
+    const size_t nt = prefill_max_ntiles((size_t)A, (size_t)T, (size_t)E);
+    const size_t m1 = (size_t)(p.m_gu > p.m_gu_sh ? p.m_gu : p.m_gu_sh);
+    TileLists &tl = p.tl;
+    tl.gu = reinterpret_cast<int4 *>(tiles_ws);
+    tl.dn = tl.gu + nt * m1;
+    tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * p.m_dn);
+    tl.n_dn = tl.n_gu + 1;
+    tl.done = tl.n_gu + 16;
+    tl.need = tl.done + (E + 2);
+    tl.sched = tl.need + (E + 2);
+    return p;
+}
+
 /* Routed + shared experts through the tensor-core path.  x [T,H] is the block
  * input; d holds the dispatch results; xg/act/sa/eo/sy are workspace. */
 inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
@@ -746,7 +696,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                                const DispatchOut &d, uint16_t *xg, uint16_t *act,
                                uint16_t *sa, uint16_t *eo, uint16_t *sy,
                                void *tiles_ws, int *status, cudaStream_t st,
-                               int *launches, void (*mark)(int stage)) {
+                               int *launches, void (*mark)(int stage),
+                               const TilePlan *built = nullptr) {
     const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
               E = (int)c.experts;
     if (!maps) {
@@ -759,31 +710,21 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                  "grouped GEMM needs %d B shared memory", s1);
         return 1;
     }
-    /* tile lists */
-    const size_t nt = prefill_max_ntiles((size_t)A, (size_t)T, (size_t)E);
-    const int m_gu = I / PG_BM, m_gu_sh = Is / PG_BM, m_dn = H / PG_BM;
-    const size_t m1 = (size_t)(m_gu > m_gu_sh ? m_gu : m_gu_sh);
-    TileLists tl;
-    tl.gu = reinterpret_cast<int4 *>(tiles_ws);
-    tl.dn = tl.gu + nt * m1;
-    tl.n_gu = reinterpret_cast<int *>(tl.dn + nt * m_dn);
-    tl.n_dn = tl.n_gu + 1;
-    tl.done = tl.n_gu + 16;
-    tl.need = tl.done + (E + 2);
-    tl.sched = tl.need + (E + 2);
+    /* tile lists: built by the dispatch kernel already, or here */
+    TilePlan plan = prefill_tile_plan(c, T, do_shared, A, tiles_ws);
+    if (built) {
+        plan = *built;
+    } else {
+        launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, (const int32_t *)d.counts,
+                 (const int32_t *)d.offsets, E, plan);
+        (*launches)++;
+    }
+    const TileLists tl = plan.tl;
+    const int bn_gu = plan.bn_gu, bn_dn = plan.bn_dn;
+    const int m_gu = plan.m_gu, m_gu_sh = plan.m_gu_sh, m_dn = plan.m_dn;
+    (void)m_gu; (void)m_gu_sh; (void)m_dn;
     const bool overlap = g_pg_overlap != 0;
     const int dynamic = g_pg_dynamic;
-    /* token box of the routed tiles: about twice the mean row count of an
-     * expert, so that nearly every expert is one tile and a tile does not pull
-     * rows it will not use through L2 */
-    int want = PG_BN_MIN;
-    while (want < PG_BN_DN && (long)want * E < 2L * A) want *= 2;
-    const int bn_gu = want < PG_BN_GU ? want : PG_BN_GU;
-    const int bn_dn = want < PG_BN_DN ? want : PG_BN_DN;
-    launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, d.counts, d.offsets, E,
-                                           do_shared ? T : 0, m_gu, m_gu_sh, m_dn,
-                                           bn_gu, bn_dn, tl);
-    (*launches)++;
     /* permuted activation rows */
     if (A > 0) {
         long total = (long)A * (H / 8);
