@@ -1627,9 +1627,11 @@ extern "C" int apus_cuda_ep_push_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
     if (launch_dispatch(c, d_idx, (int)A, w->l.n, o, w->uh, st,
                         DispatchKey{0, w->E / w->l.n}))
         return 1;
+    /* two CTAs per SM: every CTA ends with a system-scope fence and a turn at
+     * one counter, so few CTAs with several rows each beat many small ones */
     long total = (long)A * (w->l.H / 8);
     int blocks = (int)((total + 255) / 256);
-    if (blocks > c->sm_count * 8) blocks = c->sm_count * 8;
+    if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
     launch_k(epw_push_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx,
              (const int32_t *)w->perm, (const int32_t *)w->offsets, (int)A, w->topk,
              w->l, w->peers, w->me, epoch, w->counter);
@@ -1666,7 +1668,7 @@ extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
-    launch_k(epw_return_kernel, dim3(c->sm_count * 4), dim3(256), 0, (cudaStream_t)stream,
+    launch_k(epw_return_kernel, dim3(c->sm_count * 2), dim3(256), 0, (cudaStream_t)stream,
              (const uint16_t *)w->y, w->l, w->peers, w->me, epoch, w->counter + 1);
     LAUNCHED();
     return 0;
