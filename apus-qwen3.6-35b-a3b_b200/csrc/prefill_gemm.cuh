@@ -264,10 +264,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     const __grid_constant__ CUtensorMap mapB,     /* xg | act */
                     const __grid_constant__ CUtensorMap mapBs,    /* x  | sa */
                     GemmParams p) {
-    if (MODE == 1 && p.done)
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    else
-        pdl_enter();
+    /* The next kernel may be scheduled now.  This kernel's own wait for the
+     * previous one comes after the prologue below (barriers, TMEM), which
+     * touches nothing the previous kernel writes. */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr bool GATE_UP = MODE == 0;
     constexpr int STAGES = PG_STAGES;
     constexpr int BN = MODE == 1 ? PG_BN_DN : PG_BN_GU;
@@ -312,6 +312,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    /* the down kernel of an overlapped pair does not wait for the whole gate_up
+     * kernel: its producer waits per expert instead */
+    if (!(MODE == 1 && p.done)) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int n_tiles = MODE == 2 ? p.dense_ntiles : *p.n_tiles;
     const int num_kb = p.K / PG_BK;
 

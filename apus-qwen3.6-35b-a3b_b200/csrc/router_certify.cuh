@@ -196,7 +196,10 @@ __device__ __forceinline__ float rc_walk(const uint16_t *const *rows, unsigned c
  */
 __global__ void __launch_bounds__(RC_THREADS)
 router_certify_kernel(CertifyArgs a) {
-    pdl_enter();
+    /* the next kernel may be scheduled; this kernel's own wait for the fast-logit
+     * GEMM comes after the tokens are staged (they are the GEMM's input, complete
+     * before it started) */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char rc_smem[];
     const int T = a.T, E = a.E, K = a.K;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -262,6 +265,7 @@ router_certify_kernel(CertifyArgs a) {
             s_xnorm[tl] = xnorm;
             atomicMin(&s_xmin, xmin);
         }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int e0 = 0; e0 < E; e0 += 256) {
             float av[8];
 #pragma unroll
@@ -320,6 +324,7 @@ router_certify_kernel(CertifyArgs a) {
         }
         if (a.extra_row && lane == 0) pairs[atomicAdd(&s_npairs, 1)] = (tl << 16) | E;
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");   /* warps without a token */
     __syncthreads();
 
     /* ---- exact chains, one lane per pair ---- */
