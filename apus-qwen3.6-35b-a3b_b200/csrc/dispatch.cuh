@@ -171,7 +171,7 @@ constexpr int DISPATCH_SMALL_MAX = 32 * DISPATCH_UNIT;
 __global__ void __launch_bounds__(1024)
 dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
                       DispatchKey kx, DispatchOut o, int *status, TilePlan tp) {
-    pdl_enter();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ int sm[];          /* [32][E] */
     __shared__ int warp_tot[32];
     __shared__ int s_ngroups;
@@ -179,6 +179,7 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     int *h = sm + warp * E;
     for (int e = lane; e < E; e += 32) h[e] = 0;
     if (tid == 0) s_ngroups = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   /* idx is the previous kernel's */
     __syncwarp();
     /* this warp's keys stay in registers for both passes */
     const int a_lo = warp * DISPATCH_UNIT;

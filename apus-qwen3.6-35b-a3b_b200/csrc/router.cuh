@@ -397,7 +397,9 @@ router_small_kernel(const uint16_t *__restrict__ x,
                     float *__restrict__ logits_ws,     /* [T][E] fp32 */
                     unsigned int *__restrict__ counters, /* [T], zero between calls */
                     int *status) {
-    pdl_enter();
+    /* the next kernel may be scheduled; the wait for the previous one comes
+     * after the router rows (constants) have been requested */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int pitch = K * 2 + 16;                 /* bytes; de-conflicts banks */
     const int xpitch = K + 4;                     /* floats; likewise for the tokens */
@@ -427,6 +429,7 @@ router_small_kernel(const uint16_t *__restrict__ x,
         }
     }
     if (tid < ROUTER_SMALL_TOK) s_last[tid] = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   /* the tokens may be its output */
     __syncthreads();
     unsigned int xmin = 0x7f800000u;
     const int c8 = K / 8;
