@@ -195,6 +195,7 @@ static int ctx_init() {
     g_apus_use_pdl = env_long("APUS_CUDA_PDL", 1) != 0;
     g_pg_overlap = (int)env_long("APUS_CUDA_GEMM_OVERLAP", 1);
     g_pg_dynamic = (int)env_long("APUS_CUDA_GEMM_DYNAMIC", 3);
+    g_pg_direct = (int)env_long("APUS_CUDA_GEMM_DIRECT", 1);
     g_ctx = c;
     return 0;
 }

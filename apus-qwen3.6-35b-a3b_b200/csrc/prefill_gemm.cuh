@@ -134,6 +134,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+/* one accumulator column: 32 lanes x 32 bits */
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];"
+                 : "=r"(r)
+                 : "r"(taddr)
+                 : "memory");
+    return r;
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -234,6 +243,12 @@ struct GemmParams {
      * was still busy with the tail of the kernel before, simply takes fewer
      * tiles.  Null: tile i + k * gridDim.x belongs to CTA i. */
     int *sched;
+    /* gate_up with a handful of tokens (direct_tk = top_k, else 0): no gathered
+     * copy of the rows.  Every routed tile multiplies its weights with ALL
+     * direct_T tokens of the block input (one box; the MMA is as cheap for 32
+     * columns as for 2), and the epilogue picks, for each of the expert's rows,
+     * the column of that row's token. */
+    int direct_tk, direct_T;
     int bn_rows;           /* token rows a routed tile's TMA box fetches (<= BN):
                             * experts with a handful of rows should not pull a
                             * full-width box of their neighbours' rows through L2 */
@@ -351,6 +366,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) + t.y * PG_BM;
                 const int arow2 = shared ? arow : arow + p.up_off;
                 const int brows = (MODE == 2 || shared) ? BN : p.bn_rows;   /* box of mb */
+                const int brow = (MODE == 0 && p.direct_tk && !shared) ? 0 : t.z;
                 if (MODE == 1 && p.done && !all_ready) {
                     /* This expert's activations must be complete and visible.
                      * Once the whole gate_up kernel is through, no tile asks
@@ -395,7 +411,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     if (GATE_UP)
                         tma_load_2d(st + PG_TILE_BYTES, ma2, kb * PG_BK, arow2,
                                     &full[s]);
-                    tma_load_2d(st + B_OFF, mb, (kb0 + kb) * PG_BK, t.z, &full[s]);
+                    tma_load_2d(st + B_OFF, mb, (kb0 + kb) * PG_BK, brow, &full[s]);
                     kiter++;
                     return true;
                 };
@@ -422,7 +438,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                 const int4 t = pg_tile<MODE>(p, tile);
                 const int acc = it & 1;
                 const uint32_t aph = (uint32_t)(it >> 1) & 1u;
-                const int n = ((t.w + 15) >> 4) << 4;
+                const int ncols = (MODE == 0 && p.direct_tk && t.x != p.E) ? p.direct_T : t.w;
+                const int n = ((ncols + 15) >> 4) << 4;
                 const uint32_t idesc = umma_idesc(n);
                 if (!pg_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status,
                              ST_TMEM_TIMEOUT)) {
@@ -491,6 +508,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
             uint16_t *out = shared ? p.out_shared : p.out_routed;
             const int ld = shared ? p.ld_shared : p.ld_routed;
             const int col = t.y * PG_BM + row;
+            if (MODE == 0 && p.direct_tk && !shared) {
+                /* row n of this expert belongs to token perm[.] / top_k: its
+                 * accumulator column is the token's index */
+                if (half == 0) {
+                    for (int n = 0; n < t.w; n++) {
+                        const int tok = __ldg(&p.perm[t.z + n]) / p.direct_tk;
+                        const uint32_t g1 = tmem_ld1(taddr + (uint32_t)tok);
+                        const uint32_t u1 = tmem_ld1(taddr + 128u + (uint32_t)tok);
+                        tmem_ld_wait();
+                        const float gv = bf16_round(__uint_as_float(g1));
+                        const float uv = bf16_round(__uint_as_float(u1));
+                        out[(size_t)(t.z + n) * ld + col] = silu_act_bits(gv, uv);
+                    }
+                }
+            } else
             for (int c0 = half * 32; c0 < t.w; c0 += 64) {
                 uint32_t g[32];
                 tmem_ld32(taddr + (uint32_t)c0, g);
@@ -648,6 +680,7 @@ inline void prefill_maps_free(PrefillMaps *m) { delete m; }
  * counter (bit 0: gate_up kernel, bit 1: down kernel). */
 inline int g_pg_overlap = 1;
 inline int g_pg_dynamic = 3;
+inline int g_pg_direct = 1;      /* up to 32 tokens: no gathered copy of the rows */
 
 inline int pg_smem_bytes(bool gate_up) {
     (void)gate_up;
@@ -728,8 +761,10 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     (void)m_gu; (void)m_gu_sh; (void)m_dn;
     const bool overlap = g_pg_overlap != 0;
     const int dynamic = g_pg_dynamic;
+    /* a handful of tokens: the gate_up kernel reads the block input itself */
+    const bool direct = A > 0 && T <= PG_BN_MIN && bn_gu == PG_BN_MIN && g_pg_direct != 0;
     /* permuted activation rows */
-    if (A > 0) {
+    if (A > 0 && !direct) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
@@ -741,8 +776,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     /* activation-side tensor maps (buffers move with the workspace) */
     CUtensorMap m_xg, m_x, m_act, m_sa;
     int bad = 0;
-    bad |= encode_2d(maps->encode, &m_xg, A > 0 ? (const void *)xg : (const void *)x,
-                     (size_t)(A > 0 ? A : 1), H, bn_gu);
+    bad |= encode_2d(maps->encode, &m_xg, (A > 0 && !direct) ? (const void *)xg : (const void *)x,
+                     (size_t)(direct ? T : (A > 0 ? A : 1)), H, bn_gu);
     bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H);
     bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
                      (size_t)(A > 0 ? A : 1), I, bn_dn);
@@ -771,6 +806,9 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.bn_rows = bn_gu;
     p1.done = overlap ? tl.done : nullptr;
     p1.need = tl.need;
+    p1.perm = d.perm;
+    p1.direct_tk = direct ? TK : 0;
+    p1.direct_T = T;
     p1.sched = (dynamic & 1) ? tl.sched : nullptr;
     launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS), s1, st, maps->w_gu, maps->sh_g, maps->sh_u, m_xg, m_x, p1);
     (*launches)++;
@@ -786,6 +824,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_routed = H;
     p2.ld_shared = H;
     p2.perm = d.perm;
+    p2.direct_tk = 0;
     p2.bn_rows = bn_dn;
     p2.sched = (dynamic & 2) ? tl.sched + 1 : nullptr;
     if (Is != I) {

@@ -219,3 +219,26 @@ def test_block_with_overlap_knobs_off(be, orc, synth, qwen_weights, knob, monkey
         assert be.last_block_status() == 0
     finally:
         be.disable()
+
+
+@pytest.mark.parametrize("T", [5, 16, 31, 32])
+def test_block_few_tokens_without_gathered_rows(be, orc, synth, qwen_weights, T,
+                                                monkeypatch):
+    """Up to 32 tokens the gate_up kernel multiplies every expert's weights
+    with all tokens of the block input and picks each row's column in its
+    epilogue, instead of reading a gathered copy of the rows.  Same block as
+    with the gathered copy, bit for bit, and within tolerance of the checker."""
+    cfg = synth.QWEN_CFG
+    x = synth.host_x(be, T, cfg["hidden"], seed=300 + T)
+    outs = {}
+    for knob in ("1", "0"):
+        monkeypatch.setenv("APUS_CUDA_GEMM_DIRECT", knob)
+        be.enable()
+        try:
+            outs[knob] = be.moe_block(cfg, qwen_weights, x)
+            assert be.last_block_status() == 0
+        finally:
+            be.disable()
+    for k in ("idx", "w", "routed", "shared", "out"):
+        assert np.array_equal(outs["1"][k], outs["0"][k]), k
+    check_block(outs["1"], orc.moe_block(cfg, qwen_weights, x), f"direct T={T}")
