@@ -243,7 +243,7 @@ struct GemmParams {
      * was still busy with the tail of the kernel before, simply takes fewer
      * tiles.  Null: tile i + k * gridDim.x belongs to CTA i. */
     int *sched;
-    /* gate_up with a handful of tokens (direct_tk = top_k, else 0): no gathered
+    /* gate_up with up to 64 tokens (direct_tk = top_k, else 0): no gathered
      * copy of the rows.  Every routed tile multiplies its weights with ALL
      * direct_T tokens of the block input (one box; the MMA is as cheap for 32
      * columns as for 2), and the epilogue picks, for each of the expert's rows,
@@ -762,7 +762,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     const bool overlap = g_pg_overlap != 0;
     const int dynamic = g_pg_dynamic;
     /* a handful of tokens: the gate_up kernel reads the block input itself */
-    const bool direct = A > 0 && T <= PG_BN_MIN && bn_gu == PG_BN_MIN && g_pg_direct != 0;
+    const bool direct = A > 0 && T <= 2 * PG_BN_MIN && g_pg_direct != 0;
+    const int box_gu = direct ? (T <= PG_BN_MIN ? PG_BN_MIN : 2 * PG_BN_MIN) : bn_gu;
     /* permuted activation rows */
     if (A > 0 && !direct) {
         long total = (long)A * (H / 8);
@@ -777,7 +778,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     CUtensorMap m_xg, m_x, m_act, m_sa;
     int bad = 0;
     bad |= encode_2d(maps->encode, &m_xg, (A > 0 && !direct) ? (const void *)xg : (const void *)x,
-                     (size_t)(direct ? T : (A > 0 ? A : 1)), H, bn_gu);
+                     (size_t)(direct ? T : (A > 0 ? A : 1)), H, box_gu);
     bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H);
     bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
                      (size_t)(A > 0 ? A : 1), I, bn_dn);
@@ -803,7 +804,7 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_routed = I;
     p1.ld_shared = Is;
     p1.status = status;
-    p1.bn_rows = bn_gu;
+    p1.bn_rows = box_gu;
     p1.done = overlap ? tl.done : nullptr;
     p1.need = tl.need;
     p1.perm = d.perm;

@@ -221,10 +221,10 @@ def test_block_with_overlap_knobs_off(be, orc, synth, qwen_weights, knob, monkey
         be.disable()
 
 
-@pytest.mark.parametrize("T", [5, 16, 31, 32])
+@pytest.mark.parametrize("T", [5, 16, 31, 32, 33, 64])
 def test_block_few_tokens_without_gathered_rows(be, orc, synth, qwen_weights, T,
                                                 monkeypatch):
-    """Up to 32 tokens the gate_up kernel multiplies every expert's weights
+    """Up to 64 tokens the gate_up kernel multiplies every expert's weights
     with all tokens of the block input and picks each row's column in its
     epilogue, instead of reading a gathered copy of the rows.  Same block as
     with the gathered copy, bit for bit, and within tolerance of the checker."""
