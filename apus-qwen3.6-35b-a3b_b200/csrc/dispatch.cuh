@@ -177,7 +177,11 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     __shared__ int s_ngroups;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int *h = sm + warp * E;
-    for (int e = lane; e < E; e += 32) h[e] = 0;
+    /* warps beyond the last unit hold no assignment: their histograms are
+     * neither cleared nor summed (a handful of tokens is one unit) */
+    const int units = (A + DISPATCH_UNIT - 1) / DISPATCH_UNIT;
+    if (warp < units)
+        for (int e = lane; e < E; e += 32) h[e] = 0;
     if (tid == 0) s_ngroups = 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");   /* idx is the previous kernel's */
     __syncwarp();
@@ -201,7 +205,7 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     for (int e = tid; e < E; e += 1024) {   /* E <= 1024: at most one e */
         int run = 0;
 #pragma unroll 8
-        for (int w = 0; w < 32; w++) {
+        for (int w = 0; w < units; w++) {
             int v = sm[w * E + e];
             sm[w * E + e] = run;
             run += v;
@@ -222,7 +226,7 @@ dispatch_small_kernel(const int32_t *__restrict__ idx, int A, int E,
     if (tid < E) {
         o.counts[tid] = total;
         o.offsets[tid] = off;
-        for (int w = 0; w < 32; w++) sm[w * E + tid] += off;   /* cursors */
+        for (int w = 0; w < units; w++) sm[w * E + tid] += off;   /* cursors */
         if (o.grp_expert && total > 0) {
             int ng = (total + GROUP_TOKENS - 1) / GROUP_TOKENS;
             int g0 = atomicAdd(&s_ngroups, ng);
