@@ -1512,6 +1512,7 @@ struct ApusCudaEpWindow {
     int32_t *offsets, *perm, *counts;
     int32_t *uh;                     /* dispatch scratch */
     unsigned int *counter;           /* [2] finished-CTA counters */
+    uint32_t *d_epoch;               /* step number for calls made with epoch 0 */
 };
 
 extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t H,
@@ -1531,7 +1532,7 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     w->E = (int)E;
     const size_t A = cap;
     const size_t local = n_ranks * cap * H * 2 + (n_ranks + 1) * 4 + A * 4 +
-                         n_ranks * 4 + dispatch_scratch_bytes(A, n_ranks) + 4096;
+                         n_ranks * 4 + dispatch_scratch_bytes(A, n_ranks) + 8192;
     unsigned char *loc = nullptr;
     if (cudaMalloc(&w->base, w->l.total) != cudaSuccess ||
         cudaMalloc(&loc, local) != cudaSuccess) {
@@ -1549,6 +1550,7 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     w->perm = (int32_t *)(loc + o);      o = up(o + A * 4);
     w->counts = (int32_t *)(loc + o);    o = up(o + n_ranks * 4);
     w->counter = (unsigned int *)(loc + o); o = up(o + 8);
+    w->d_epoch = (uint32_t *)(loc + o);  o = up(o + 4);
     w->uh = (int32_t *)(loc + o);
     w->peers.base[rank] = w->base;
     CU_OK(cudaDeviceSynchronize());
@@ -1635,7 +1637,7 @@ extern "C" int apus_cuda_ep_push_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
     if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
     launch_k(epw_push_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx,
              (const int32_t *)w->perm, (const int32_t *)w->offsets, (int)A, w->topk,
-             w->l, w->peers, w->me, epoch, w->counter);
+             w->l, w->peers, w->me, epoch, w->counter, w->d_epoch);
     LAUNCHED();
     return 0;
 }
@@ -1650,7 +1652,7 @@ extern "C" int apus_cuda_ep_wait_dev(ApusCudaEpWindow *w, int which, uint32_t ep
     const uint32_t *flags =
         reinterpret_cast<const uint32_t *>(w->base + (which ? w->l.fbk : w->l.fin));
     launch_k(epw_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, flags, w->l.n,
-             epoch, c->d_status);
+             epoch, c->d_status, (const uint32_t *)w->d_epoch);
     LAUNCHED();
     return 0;
 }
@@ -1670,7 +1672,8 @@ extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     launch_k(epw_return_kernel, dim3(c->sm_count * 2), dim3(256), 0, (cudaStream_t)stream,
-             (const uint16_t *)w->y, w->l, w->peers, w->me, epoch, w->counter + 1);
+             (const uint16_t *)w->y, w->l, w->peers, w->me, epoch, w->counter + 1,
+             (const uint32_t *)w->d_epoch);
     LAUNCHED();
     return 0;
 }

@@ -110,8 +110,11 @@ __global__ void __launch_bounds__(256)
 epw_push_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ idx,
                 const int32_t *__restrict__ perm, const int32_t *__restrict__ offsets,
                 int A, int TK, EpwLayout l, EpwPeers peers, int me, uint32_t epoch,
-                unsigned int *counter) {
+                unsigned int *counter, uint32_t *d_epoch) {
     pdl_enter();
+    /* epoch 0: the step number lives on the device (this push opens step
+     * *d_epoch + 1), so that a captured CUDA graph can be replayed */
+    if (epoch == 0) epoch = *d_epoch + 1;
     __shared__ int s_off[EPW_MAX_RANKS + 1];
     __shared__ unsigned char *s_base[EPW_MAX_RANKS];
     if (threadIdx.x <= l.n) s_off[threadIdx.x] = offsets[threadIdx.x];
@@ -143,6 +146,7 @@ epw_push_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ idx,
         int32_t *h = reinterpret_cast<int32_t *>(s_base[d] + l.hdr) + me * 4;
         h[0] = s_off[d + 1] - s_off[d];
         h[1] = s_off[d];
+        if (d == 0) *d_epoch = epoch;      /* every CTA has read it: this one is the last */
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(s_base[d] + l.fin) + me, epoch);
     }
@@ -150,8 +154,10 @@ epw_push_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ idx,
 
 /* flags[n] in this rank's own window.  One warp. */
 __global__ void __launch_bounds__(32)
-epw_wait_kernel(const uint32_t *flags, int n, uint32_t epoch, int *status) {
+epw_wait_kernel(const uint32_t *flags, int n, uint32_t epoch, int *status,
+                const uint32_t *d_epoch) {
     pdl_enter();
+    if (epoch == 0) epoch = *d_epoch;
     if ((int)threadIdx.x >= n) return;
     for (uint32_t i = 0; i < EPW_WAIT_POLLS; i++) {
         const uint32_t v = ld_acquire_sys(flags + threadIdx.x);
@@ -165,8 +171,9 @@ epw_wait_kernel(const uint32_t *flags, int n, uint32_t epoch, int *status) {
  * + i] of rank s. */
 __global__ void __launch_bounds__(256)
 epw_return_kernel(const uint16_t *__restrict__ y, EpwLayout l, EpwPeers peers, int me,
-                  uint32_t epoch, unsigned int *counter) {
+                  uint32_t epoch, unsigned int *counter, const uint32_t *d_epoch) {
     pdl_enter();
+    if (epoch == 0) epoch = *d_epoch;
     __shared__ int s_cnt[EPW_MAX_RANKS + 1], s_dst[EPW_MAX_RANKS];
     __shared__ unsigned char *s_base[EPW_MAX_RANKS];
     if (threadIdx.x < EPW_MAX_RANKS) s_base[threadIdx.x] = peers.base[threadIdx.x];

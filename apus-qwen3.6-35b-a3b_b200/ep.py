@@ -118,12 +118,14 @@ class PeerWindowBlock:
     torch.distributed is used once, to hand round the windows' IPC handles."""
 
     def __init__(self, be, layer, cfg, rank, world, max_tokens, group=None,
-                 window=None):
+                 window=None, device_epoch=False):
         import torch.distributed as dist
         assert cfg["experts"] % world == 0
         self.be, self.layer, self.cfg = be, layer, cfg
         self.rank, self.world, self.max_tokens = rank, world, max_tokens
         self.epoch = 0
+        # step number kept on the device: the step can be captured in a CUDA graph
+        self.device_epoch = device_epoch
         self.owns = window is None
         self.win = window
         if window is not None:
@@ -169,7 +171,8 @@ class PeerWindowBlock:
         T, H = x.shape
         TK = self.cfg["top_k"]
         assert T <= self.max_tokens
-        self.epoch += 1
+        if not self.device_epoch:
+            self.epoch += 1
         st = dict(x=x)
         st["idx"] = torch.empty((T, TK), dtype=torch.int32, device=x.device)
         st["w"] = torch.empty((T, TK), dtype=torch.int16, device=x.device)

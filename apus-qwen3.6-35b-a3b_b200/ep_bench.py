@@ -40,7 +40,7 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
         # every rank must take the same arm: agree on whether the windows came up
         ok = torch.ones(1, device="cuda")
         try:
-            blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T)
+            blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=True)
         except Exception as e:             # e.g. no peer access between two GPUs
             exchange_note = f"{type(e).__name__}: {e}"
             ok.zero_()
@@ -60,6 +60,21 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+    # The window step has no host synchronisation and no collective call, and
+    # its step number lives on the device: capture it once, replay it.
+    use_graph = exchange == "peer" and not getattr(args, "no_graph", False)
+    if use_graph:
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out_g = blk.forward(d_x)
+
+        def step():
+            graph.replay()
+            return out_g
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
     sampler = None
     if rank == 0 and clock_sampler is not None:
         sampler = clock_sampler(local)       # SM clock and throttle reasons of GPU 0
@@ -121,7 +136,7 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
                                f"GPU, uniform router, seed {args.seed}")
         cfgline["tokens_per_step"] = Tg
         cfgline["parallelism"] = f"ep{world}"
-        cfgline["launch"] = "host launches"
+        cfgline["launch"] = "cuda graph replay" if use_graph else "host launches"
         line = {
             "metric": metric, "value": Tg / (ms * 1e-3), "unit": unit,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

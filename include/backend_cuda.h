@@ -303,6 +303,9 @@ int apus_cuda_ep_finish_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
  *   apus_cuda_ep_wait_dev(1, e)     every peer's return has landed here
  *   apus_cuda_ep_combine_dev        weighted sum in slot order, gate, add
  *
+ * With epoch 0 in every call the step number is kept on the device (a push opens
+ * the next step), so the eight calls can be captured once in a CUDA graph and
+ * replayed.
  * All ranks must run the same sequence of steps.  Waits are bounded (about two
  * seconds); one that runs out sets apus_cuda_last_block_status() to 6 and the
  * step's output is not valid, but the context stays usable.  The result equals

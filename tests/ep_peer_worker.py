@@ -14,6 +14,7 @@ from tests.conftest import load_package  # noqa: E402
 
 def main():
     outdir, T, steps = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    use_graph = len(sys.argv) > 4 and sys.argv[4] == "1"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -28,12 +29,26 @@ def main():
     W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
     per = cfg["experts"] // world
     layer = be.layer_create(cfg, W, rank * per, (rank + 1) * per)
-    blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T)
+    blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=use_graph)
     out = None
+    d_x = torch.empty((T, cfg["hidden"]), dtype=torch.int16, device="cuda")
+    graph = None
     for s in range(steps):
         x = synth.host_x(be, T * world, cfg["hidden"], seed=100 + s)
         mine = np.ascontiguousarray(x[rank * T:(rank + 1) * T]).view(np.int16)
-        out = blk.forward(torch.from_numpy(mine).cuda())
+        d_x.copy_(torch.from_numpy(mine))
+        if not use_graph:
+            out = blk.forward(d_x)
+        elif s == 0:
+            out = blk.forward(d_x)             # workspaces grow outside the capture
+            torch.cuda.synchronize()
+            dist.barrier()
+            stream = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out = blk.forward(d_x)
+        else:
+            graph.replay()
     torch.cuda.synchronize()
     status = be.last_block_status()
     np.save(os.path.join(outdir, f"out_{rank}.npy"),

@@ -105,7 +105,7 @@ def test_ep_world_size_one_process_group(gpu, be, synth):
         dist.destroy_process_group()
 
 
-def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1):
+def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1, device_epoch=False):
     """N ranks in this process, one peer window each, attached to one another
     by pointer.  All pushes are launched before the first wait, all returns
     before the first wait for them, so no kernel ever waits on a later one."""
@@ -118,7 +118,8 @@ def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1):
         for q in range(N):
             if q != r:
                 be.ep_window_attach_local(wins[r], q, wins[q])
-    blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, per, window=wins[r])
+    blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, per, window=wins[r],
+                               device_epoch=device_epoch)
             for r in range(N)]
     xs = [torch.from_numpy(x[r * per:(r + 1) * per].view(np.int16).copy()).cuda()
           for r in range(N)]
@@ -187,11 +188,12 @@ def test_peer_window_skewed_router_one_owner(be, synth):
         be.disable()
 
 
-@pytest.mark.parametrize("T", [24, 300])
-def test_peer_window_two_processes(be, synth, T, tmp_path):
+@pytest.mark.parametrize("T,graph", [(24, 0), (300, 0), (300, 1)])
+def test_peer_window_two_processes(be, synth, T, graph, tmp_path):
     """Two real ranks, one per GPU, windows mapped through CUDA IPC: the rows
-    cross NVLink by the kernels' own stores.  Three steps; the last one must
-    equal the single-GPU block bit for bit."""
+    cross NVLink by the kernels' own stores.  Three steps (graph = 1: the step
+    captured once in a CUDA graph and replayed, its number kept on the device);
+    the last one must equal the single-GPU block bit for bit."""
     import subprocess
     import sys
     import torch
@@ -204,7 +206,8 @@ def test_peer_window_two_processes(be, synth, T, tmp_path):
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
          "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-         "--master-port", str(port), worker, str(tmp_path), str(T), "3"],
+         "--master-port", str(port), worker, str(tmp_path), str(T), "3",
+         str(graph)],
         env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     got = np.concatenate([np.load(tmp_path / f"out_{k}.npy") for k in range(2)])
@@ -215,6 +218,25 @@ def test_peer_window_two_processes(be, synth, T, tmp_path):
         W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
         x = synth.host_x(be, 2 * T, cfg["hidden"], seed=102)
         whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
+
+
+def test_peer_window_step_number_on_the_device(be, synth):
+    """Epoch 0 in every call: the windows count the steps themselves (what a
+    captured CUDA graph of the step needs).  Four steps, four ranks."""
+    import torch
+    from apus_b200 import ep
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=21, sigma=0.05)
+        x = synth.host_x(be, 160, cfg["hidden"], seed=21)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        got = emulate_windows(be, ep, torch, cfg, W, x, 4, steps=4,
+                              device_epoch=True)
         assert np.array_equal(got, whole)
     finally:
         be.disable()
