@@ -65,10 +65,19 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     use_graph = exchange == "peer" and not getattr(args, "no_graph", False)
     if use_graph:
         dist.barrier()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            out_g = blk.forward(d_x)
-
+        ok = torch.ones(1, device="cuda")
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out_g = blk.forward(d_x)
+        except Exception as e:
+            print(f"rank {rank}: graph capture failed ({type(e).__name__}: {e}); "
+                  "host launches", file=sys.stderr)
+            ok.zero_()
+        torch.cuda.synchronize()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)      # all ranks take the same arm
+        use_graph = float(ok.item()) != 0.0
+    if use_graph:
         def step():
             graph.replay()
             return out_g
