@@ -240,3 +240,33 @@ def test_peer_window_step_number_on_the_device(be, synth):
         assert np.array_equal(got, whole)
     finally:
         be.disable()
+
+
+def test_peer_window_wait_gives_up(be, synth):
+    """A peer that never pushes: the wait runs out after about two seconds,
+    the status word says so (6), and the context and the windows stay usable."""
+    import time
+    import torch
+    from apus_b200 import ep
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        wins = [be.ep_window_create(16, 8, 512, 64, 2, r) for r in range(2)]
+        be.ep_window_attach_local(wins[0], 1, wins[1])
+        be.ep_window_attach_local(wins[1], 0, wins[0])
+        t0 = time.time()
+        be.ep_wait_dev(wins[0], 0, 7)            # nobody ever announces step 7
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 30
+        assert be.last_block_status() == 6
+        assert be.last_block_status() == 0       # read once, then clear
+        for w in wins:
+            be.ep_window_destroy(w)
+        W = synth.host_weights(be, cfg, seed=23, sigma=0.05)
+        x = synth.host_x(be, 32, cfg["hidden"], seed=23)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        got = emulate_windows(be, ep, torch, cfg, W, x, 2)
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
