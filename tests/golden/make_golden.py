@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Regenerates the committed golden fixtures under tests/golden/.
 
-Run here, where the reference checkout exists (REF, default /root/reference);
-the fixtures it writes are what travels.  Three families:
+Run where a checkout of the reference exists (environment variable REF names
+it); the fixtures it writes are what travels.  Three families:
 
   m4a/      the reference's own per-op MoE goldens: its generator
             tests/m4a/gen_golden.py is imported unmodified and run with its
