@@ -57,6 +57,9 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
         return blk.forward(d_x)
 
     out = step()
+    l_one = be.launches()
+    out = step()
+    per_step = be.launches() - l_one        # kernels of one step (host launches)
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -97,7 +100,9 @@ def run(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler=None):
     for _ in range(args.steps):
         out = step()
     e1.record(stream)
-    launches = torch.tensor([float(be.launches() - l0)], device="cuda")
+    # a replayed graph launches the kernels that one captured step launched
+    n_launched = per_step * args.steps if use_graph else be.launches() - l0
+    launches = torch.tensor([float(n_launched)], device="cuda")
     torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
