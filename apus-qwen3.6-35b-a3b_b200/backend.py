@@ -60,7 +60,8 @@ SYMBOLS = [
     "apus_cuda_moe_route_topn", "apus_cuda_moe_dispatch",
     "apus_cuda_moe_block", "apus_cuda_block_hooks", "apus_cuda_layer_create",
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
-    "apus_cuda_layer_refresh", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
+    "apus_cuda_layer_refresh", "apus_cuda_layer_upload",
+    "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
     "apus_cuda_fused_timeline", "apus_cuda_router_exact_chains",
@@ -122,6 +123,9 @@ class Backend:
         L.apus_cuda_layer_tensor.argtypes = [vp, C.c_int, C.POINTER(sz)]
         L.apus_cuda_layer_tensor.restype = vp
         L.apus_cuda_layer_refresh.argtypes = [vp]
+        L.apus_cuda_layer_upload.argtypes = [vp, C.c_int, u16p, sz, sz]
+        L.apus_cuda_debug_fast_logits.argtypes = [u16p, u16p, sz, sz, sz, f32p,
+                                                  f32p, f32p, f32p]
         L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
                                               C.POINTER(MoeTrace), vp]
         L.apus_cuda_reserve.argtypes = [C.POINTER(MoeCfg), sz]
@@ -316,6 +320,30 @@ class Backend:
     def layer_refresh(self, layer):
         self._check(self.lib.apus_cuda_layer_refresh(layer),
                     "apus_cuda_layer_refresh")
+
+    def layer_upload(self, layer, name, src, first=0):
+        """Host uint16 array -> elements [first, first + src.size) of a
+        resident tensor of the layer."""
+        src = _u16(src)
+        self._check(self.lib.apus_cuda_layer_upload(
+            layer, TENSOR_IDS[name], _ptr(src, u16p), first, src.size),
+            "apus_cuda_layer_upload")
+
+    def debug_fast_logits(self, x, wg):
+        """(fast [T,E] f32, xnorm [T], wnorm [E+1], cbound) of the many-token
+        router's tensor-core scoring."""
+        x, wg = _u16(x), _u16(wg)
+        T, K = x.shape
+        E = wg.shape[0]
+        fast = np.zeros((T, E), np.float32)
+        xn = np.zeros(T, np.float32)
+        wn = np.zeros(E + 1, np.float32)
+        cb = np.zeros(1, np.float32)
+        self._check(self.lib.apus_cuda_debug_fast_logits(
+            _ptr(x, u16p), _ptr(wg, u16p), T, E, K, _ptr(fast, f32p),
+            _ptr(xn, f32p), _ptr(wn, f32p), _ptr(cb, f32p)),
+            "apus_cuda_debug_fast_logits")
+        return fast, xn, wn, float(cb[0])
 
     def reserve(self, cfg, T):
         c = MoeCfg.from_dict(cfg)

@@ -48,6 +48,11 @@ struct Arena {
     char *base = nullptr;
     size_t cap = 0;
     size_t off = 0;
+    /* Chunks this arena has outgrown.  A captured CUDA graph keeps the
+     * addresses it was captured with (kernel arguments, tensor maps by value),
+     * so an outgrown chunk is never freed while the backend is enabled: a
+     * replay of an older capture still finds its memory. */
+    std::vector<void *> retired;
     void reset() { off = 0; }
     void *take(size_t bytes) {
         size_t o = (off + 255) & ~(size_t)255;
@@ -98,6 +103,10 @@ struct Ctx {
     size_t df_act_elems = 0, df_sa_elems = 0;
     int last_block_launches = 0;
     bool hooks_filled = false;
+    /* ordering of calls that arrive on different streams */
+    cudaStream_t cur_stream = nullptr, last_stream = nullptr;
+    cudaEvent_t last_ev = nullptr;
+    bool have_last = false, cur_capturing = false;
     /* optional per-stage CUDA events inside the block (benchmarks) */
     bool stage_timing = false;
     cudaEvent_t ev[16] = {};
@@ -202,16 +211,72 @@ static int ctx_init() {
 
 static int arena_reserve(Arena &a, size_t bytes) {
     if (a.cap >= bytes) return 0;
+    /* growing inside a capture would need a device-wide synchronisation,
+     * which a capturing stream does not allow */
+    if (g_ctx && g_ctx->cur_capturing)
+        return fail("workspace too small for this call inside a stream capture: "
+                    "call apus_cuda_reserve for the largest shape before capturing");
     CU_OK(cudaDeviceSynchronize());
-    if (a.base) CU_OK(cudaFree(a.base));
+    if (a.base) a.retired.push_back(a.base);
     a.base = nullptr;
     a.cap = 0;
-    size_t want = bytes + (bytes >> 3) + (1u << 20);
+    size_t want = bytes + (bytes >> 2) + (1u << 20);
     CU_OK(cudaMalloc((void **)&a.base, want));
     a.cap = want;
     a.off = 0;
     return 0;
 }
+static void arena_free(Arena &a) {
+    if (a.base) cudaFree(a.base);
+    for (void *p : a.retired) cudaFree(p);
+    a.retired.clear();
+    a.base = nullptr;
+    a.cap = a.off = 0;
+}
+
+/* All device-pointer entry points share one workspace, one status word and
+ * the counters of the one-kernel decode path, whatever stream they are given.
+ * A call that arrives on another stream than the call before it is ordered
+ * behind that call with an event, so two callers on two streams get serial,
+ * correct results instead of a silent race.  Inside a stream capture nothing
+ * is recorded or waited for (a capture must not depend on work outside it):
+ * replays of captured graphs are ordered by their caller. */
+static int order_begin(Ctx *c, cudaStream_t st) {
+    c->cur_stream = st;
+    c->cur_capturing = false;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    c->cur_capturing = cs != cudaStreamCaptureStatusNone;
+    if (c->cur_capturing) return 0;
+    if (c->have_last && c->last_stream != st)
+        CU_OK(cudaStreamWaitEvent(st, c->last_ev, 0));
+    return 0;
+}
+static void order_end(Ctx *c, cudaStream_t st) {
+    if (c->cur_capturing) return;
+    if (!c->last_ev &&
+        cudaEventCreateWithFlags(&c->last_ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    if (cudaEventRecord(c->last_ev, st) == cudaSuccess) {
+        c->last_stream = st;
+        c->have_last = true;
+    } else {
+        cudaGetLastError();
+    }
+}
+/* brackets one device-pointer entry point */
+struct Ordered {
+    Ctx *c;
+    cudaStream_t st;
+    int rc;
+    Ordered(Ctx *c_, cudaStream_t st_) : c(c_), st(st_), rc(order_begin(c_, st_)) {}
+    ~Ordered() { order_end(c, st); }
+};
 
 #define LAUNCHED()                                                         \
     do {                                                                   \
@@ -297,8 +362,9 @@ extern "C" void apus_cuda_disable(void) {
     cudaDeviceSynchronize();
     for (auto &kv : c->wcache) cudaFree(kv.second.ptr);
     for (auto &kv : c->layers) layer_free(kv.second);
-    if (c->ws.base) cudaFree(c->ws.base);
-    if (c->io.base) cudaFree(c->io.base);
+    arena_free(c->ws);
+    arena_free(c->io);
+    if (c->last_ev) cudaEventDestroy(c->last_ev);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_router_counters) cudaFree(c->d_router_counters);
     if (c->d_rc_stats) cudaFree(c->d_rc_stats);
@@ -369,6 +435,8 @@ static int dense_op(const uint16_t *w, const uint16_t *x, void *y, size_t M,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
+    Ordered ord(c, c->stream);
+    if (ord.rc) return 1;
     const uint16_t *dw = (const uint16_t *)weight_buf(c, w, O * K * 2);
     if (!dw) return 1;
     size_t xb = M * K * 2, yb = M * O * (f32_out ? 4 : 2);
@@ -468,7 +536,7 @@ static int launch_router(Ctx *c, const uint16_t *dx, const uint16_t *dwr, int T,
         ca.wmin_extra = aux->wmin_extra;
         /* the sequential chain errs by at most (K-1)u times the sum of the
          * term magnitudes; the tensor cores are granted eight times that */
-        ca.cbound = 9.1f * (float)K * 5.9604645e-8f;
+        ca.cbound = 9.1f * (float)K * 5.9604645e-8f;   /* = debug_fast_logits' *cbound */
         ca.logits = nullptr;        /* nobody reads the merged logits */
         ca.idx_out = didx;
         ca.w_out = dw;
@@ -651,6 +719,8 @@ static int route_host(const uint16_t *x, const uint16_t *wg, int32_t *idx,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
+    Ordered ord(c, c->stream);
+    if (ord.rc) return 1;
     size_t need = T * K * 2 + E * K * 2 + T * topk * 6 + T * E * 2 + 4096;
     if (arena_reserve(c->io, need)) return 1;
     c->io.reset();
@@ -698,6 +768,8 @@ extern "C" int apus_cuda_moe_dispatch(const int32_t *idx, size_t T, size_t topk,
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
+    Ordered ord(c, c->stream);
+    if (ord.rc) return 1;
     size_t need = A * 8 + (2 * E + 1) * 4 + dispatch_scratch_bytes(A, E) + 4096;
     if (arena_reserve(c->io, need)) return 1;
     c->io.reset();
@@ -838,6 +910,95 @@ extern "C" int apus_cuda_layer_refresh(ApusCudaLayer *L) {
     return layer_router_stats(g_ctx, L);
 }
 
+extern "C" int apus_cuda_layer_upload(ApusCudaLayer *L, int which,
+                                      const uint16_t *src, size_t first,
+                                      size_t n) {
+    size_t elems = 0;
+    uint16_t *dst = (uint16_t *)apus_cuda_layer_tensor(L, which, &elems);
+    if (!dst || !src || !n || first > elems || n > elems - first)
+        return fail("layer_upload: bad tensor id or range");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    /* set-up call: synchronous, whatever stream used the tensor before */
+    CU_OK(cudaDeviceSynchronize());
+    CU_OK(cudaMemcpy(dst + first, src, n * 2, cudaMemcpyHostToDevice));
+    g_ctx->bytes_uploaded += n * 2;
+    if (which == 1 || which == 7) return layer_router_stats(g_ctx, L);
+    return 0;
+}
+
+/* ||x_t||_2 with the margin router_certify_kernel applies (one warp per row) */
+__global__ void __launch_bounds__(256)
+dbg_xnorm_kernel(const uint16_t *__restrict__ x, int T, int K, float *__restrict__ out) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    float ss = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float v = bf16_f32(x[(size_t)warp * K + k]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) out[warp] = sqrtf(ss) * 1.001f;
+}
+__global__ void __launch_bounds__(256)
+dbg_sum_slabs_kernel(const float *__restrict__ slabs, int nslab, size_t n,
+                     float *__restrict__ out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float p[RC_MAX_SLABS];
+        for (int sl = 0; sl < RC_MAX_SLABS; sl++) p[sl] = sl < nslab ? slabs[sl * n + i] : 0.0f;
+        out[i] = (p[0] + p[1]) + (p[2] + p[3]);     /* the certify kernel's order */
+    }
+}
+
+extern "C" int apus_cuda_debug_fast_logits(const uint16_t *x, const uint16_t *wg,
+                                           size_t T, size_t E, size_t K,
+                                           float *fast, float *xnorm,
+                                           float *wnorm, float *cbound) {
+    if (!x || !wg || !fast || !xnorm || !wnorm || !cbound || !T || !E || !K)
+        return fail("debug_fast_logits: bad args");
+    if (E % PG_BM || K % 256) return fail("debug_fast_logits: E %% 128 or K %% 256");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    Ordered ord(c, c->stream);
+    if (ord.rc) return 1;
+    cudaStream_t st = c->stream;
+    const size_t need = T * K * 2 + E * K * 2 + (RC_MAX_SLABS + 1) * T * E * 4 +
+                        (T + E + 1) * 4 + 8192;
+    if (arena_reserve(c->io, need)) return 1;
+    c->io.reset();
+    uint16_t *dx = (uint16_t *)c->io.take(T * K * 2);
+    uint16_t *dw = (uint16_t *)c->io.take(E * K * 2);
+    float *slabs = (float *)c->io.take(RC_MAX_SLABS * T * E * 4);
+    float *dfast = (float *)c->io.take(T * E * 4);
+    float *dxn = (float *)c->io.take(T * 4);
+    float *dwn = (float *)c->io.take((E + 1) * 4);
+    CU_OK(cudaMemcpyAsync(dx, x, T * K * 2, cudaMemcpyHostToDevice, st));
+    CU_OK(cudaMemcpyAsync(dw, wg, E * K * 2, cudaMemcpyHostToDevice, st));
+    CU_OK(cudaMemsetAsync(dwn, 0, (E + 1) * 4, st));
+    CU_OK(cudaMemsetAsync(c->d_status, 0, 4, st));
+    /* the same K split the block's router would choose for this shape */
+    const int ksplit = dense_logits_ksplit(c->sm_count, (int)T, (int)E, (int)K);
+    int launches = 0;
+    if (run_dense_logits(c->sm_count, c->smem_optin, dw, dx, (int)T, (int)E, (int)K,
+                         ksplit, slabs, c->d_status, st, &launches))
+        return fail("%s", prefill_last_error());
+    dbg_sum_slabs_kernel<<<c->sm_count * 4, 256, 0, st>>>(slabs, ksplit, T * E, dfast);
+    dbg_xnorm_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(dx, (int)T, (int)K, dxn);
+    row_norm_kernel<<<(unsigned)((E * 32 + 255) / 256), 256, 0, st>>>(dw, (int)E, (int)K, dwn);
+    LAUNCHED();
+    CU_OK(cudaMemcpyAsync(fast, dfast, T * E * 4, cudaMemcpyDeviceToHost, st));
+    CU_OK(cudaMemcpyAsync(xnorm, dxn, T * 4, cudaMemcpyDeviceToHost, st));
+    CU_OK(cudaMemcpyAsync(wnorm, dwn, (E + 1) * 4, cudaMemcpyDeviceToHost, st));
+    int stw = 0;
+    CU_OK(cudaMemcpyAsync(&stw, c->d_status, 4, cudaMemcpyDeviceToHost, st));
+    CU_OK(cudaStreamSynchronize(st));
+    if (stw) return fail("debug_fast_logits: device status %d", stw);
+    *cbound = 9.1f * (float)K * 5.9604645e-8f;
+    return 0;
+}
+
 /* ------------------------------------------------------------------------ */
 /* the block                                                                 */
 /* ------------------------------------------------------------------------ */
@@ -853,6 +1014,7 @@ struct BlockBufs {
 };
 
 static size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
+static int fused_scratch(Ctx *c, const ApusCudaMoeCfg &cfg);
 
 /* carve (or just size, when a.base == NULL) the block's workspace */
 static int block_layout(const ApusCudaMoeCfg &c, size_t T, Arena *a,
@@ -909,6 +1071,8 @@ extern "C" int apus_cuda_reserve(const ApusCudaMoeCfg *cfg, size_t T) {
     if (ctx_init()) return 1;
     BlockBufs b;
     block_layout(*cfg, T, nullptr, &b, true);
+    g_ctx->cur_capturing = false;
+    if (fused_scratch(g_ctx, *cfg)) return 1;
     return arena_reserve(g_ctx->ws, b.total);
 }
 
@@ -1007,6 +1171,26 @@ static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T,
 }
 
 
+/* scratch of the one-kernel path, sized by the layer shape */
+static int fused_scratch(Ctx *c, const ApusCudaMoeCfg &cfg) {
+    const size_t need_act = (size_t)DF_MAX_A * cfg.moe_inter,
+                 need_sa = (size_t)DF_MAX_T * cfg.shared_inter;
+    if (c->df_act_elems >= need_act && c->df_sa_elems >= need_sa) return 0;
+    if (c->cur_capturing)
+        return fail("decode scratch missing inside a stream capture: call "
+                    "apus_cuda_reserve before capturing");
+    CU_OK(cudaDeviceSynchronize());
+    /* outgrown buffers stay allocated until disable (older captures) */
+    if (c->d_df_act) c->ws.retired.push_back(c->d_df_act);
+    if (c->d_df_sa) c->ws.retired.push_back(c->d_df_sa);
+    c->d_df_act = c->d_df_sa = nullptr;
+    CU_OK(cudaMalloc(&c->d_df_act, need_act * 2));
+    CU_OK(cudaMalloc(&c->d_df_sa, need_sa * 2));
+    c->df_act_elems = need_act;
+    c->df_sa_elems = need_sa;
+    return 0;
+}
+
 /* The one-kernel path for a handful of tokens (cooperative launch). */
 static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
                             uint16_t *d_out, int T, const ApusCudaMoeTrace *tr,
@@ -1015,16 +1199,7 @@ static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
     const int H = (int)cfg.hidden, I = (int)cfg.moe_inter,
               Is = (int)cfg.shared_inter, E = (int)cfg.experts,
               TK = (int)cfg.top_k;
-    const size_t need_act = (size_t)DF_MAX_A * I, need_sa = (size_t)DF_MAX_T * Is;
-    if (c->df_act_elems < need_act || c->df_sa_elems < need_sa) {
-        CU_OK(cudaDeviceSynchronize());
-        if (c->d_df_act) cudaFree(c->d_df_act);
-        if (c->d_df_sa) cudaFree(c->d_df_sa);
-        CU_OK(cudaMalloc(&c->d_df_act, need_act * 2));
-        CU_OK(cudaMalloc(&c->d_df_sa, need_sa * 2));
-        c->df_act_elems = need_act;
-        c->df_sa_elems = need_sa;
-    }
+    if (fused_scratch(c, cfg)) return 1;
     FusedArgs a;
     memset(&a, 0, sizeof a);
     a.T = T; a.H = H; a.I = I; a.Is = Is; a.E = E; a.TK = TK;
@@ -1160,6 +1335,8 @@ extern "C" int apus_cuda_moe_block_dev(ApusCudaLayer *layer,
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(g_ctx, st);
+    if (ord.rc) return 1;
     if (layer->maps == nullptr && prefill_supported(layer->cfg) &&
         (int)T > g_ctx->decode_max_t) {
         layer->maps = prefill_maps_create(layer->cfg, layer->exp_gu,
@@ -1281,6 +1458,8 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
         c->layers.emplace(w->rtr_w, L);
     }
     const size_t H = cfg->hidden, TK = cfg->top_k;
+    Ordered ord(c, c->stream);
+    if (ord.rc) return 1;
     size_t need = 2 * T * H * 2 + T * TK * 6 + 3 * T * H * 2 + 8192;
     if (arena_reserve(c->io, need)) return 1;
     c->io.reset();
@@ -1348,6 +1527,8 @@ extern "C" int apus_cuda_ep_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const size_t E = L->cfg.experts;
     if (arena_reserve(c->ws, T * E * 18 + 8192)) return 1;
     c->ws.reset();
@@ -1383,6 +1564,8 @@ extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const size_t need = dispatch_scratch_bytes(A, n_ranks) + A * 4 +
                         (n_ranks + 1) * 4 + 4096;
     if (arena_reserve(c->ws, need)) return 1;
@@ -1419,6 +1602,8 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const size_t ne = L->e_end - L->e_begin;
     if (!ne) return fail("experts_dev: no routed experts resident");
     ApusCudaMoeCfg cx = L->cfg;       /* the shape dispatch and tiling see */
@@ -1470,6 +1655,8 @@ extern "C" int apus_cuda_ep_finish_dev(ApusCudaLayer *L, const uint16_t *d_x,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const ApusCudaMoeCfg &cfg = L->cfg;
     /* shared expert only: a dispatch result with no routed rows */
     ApusCudaMoeCfg cx = cfg;
@@ -1621,6 +1808,8 @@ extern "C" int apus_cuda_ep_push_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     DispatchOut o;
     memset(&o, 0, sizeof o);
     o.counts = w->counts;
@@ -1649,6 +1838,8 @@ extern "C" int apus_cuda_ep_wait_dev(ApusCudaEpWindow *w, int which, uint32_t ep
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
+    Ordered ord(c, (cudaStream_t)stream);
+    if (ord.rc) return 1;
     const uint32_t *flags =
         reinterpret_cast<const uint32_t *>(w->base + (which ? w->l.fbk : w->l.fin));
     launch_k(epw_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, flags, w->l.n,
@@ -1671,6 +1862,8 @@ extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
+    Ordered ord(c, (cudaStream_t)stream);
+    if (ord.rc) return 1;
     launch_k(epw_return_kernel, dim3(c->sm_count * 2), dim3(256), 0, (cudaStream_t)stream,
              (const uint16_t *)w->y, w->l, w->peers, w->me, epoch, w->counter + 1,
              (const uint32_t *)w->d_epoch);
@@ -1687,6 +1880,8 @@ extern "C" int apus_cuda_ep_shared_dev(ApusCudaLayer *L, const uint16_t *d_x, si
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const ApusCudaMoeCfg &cfg = L->cfg;
     ApusCudaMoeCfg cx = cfg;
     cx.top_k = 1;
@@ -1727,6 +1922,8 @@ extern "C" int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *L, s
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
+    Ordered ord(c, (cudaStream_t)stream);
+    if (ord.rc) return 1;
     return run_finalize(c, L->cfg, (int)T, (const uint16_t *)(w->base + w->l.by), d_pos,
                         d_w, d_sy, d_sgl, d_out, nullptr, (cudaStream_t)stream);
 }
@@ -1744,6 +1941,8 @@ extern "C" int apus_cuda_route_dev(ApusCudaLayer *L, const uint16_t *d_x,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     const size_t E = L->cfg.experts;
     if (arena_reserve(c->ws, T * E * 18 + 8192)) return 1;
     c->ws.reset();
@@ -1765,6 +1964,8 @@ extern "C" int apus_cuda_dispatch_dev(const int32_t *d_idx, size_t T,
     Ctx *c = g_ctx;
     c->last_block_launches = 0;
     cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
     size_t need = dispatch_scratch_bytes(A, E) + 1024;
     if (arena_reserve(c->io, need)) return 1;
     c->io.reset();
@@ -1863,6 +2064,9 @@ extern "C" int apus_cuda_dispatch_dev_static(const int32_t *d_idx, size_t T,
                                              int32_t *d_offsets,
                                              int32_t *d_perm, void *stream) {
     const size_t A = T * topk;
+    /* g_mu guards the error text (and nothing else here: this entry point
+     * touches none of the context's state) */
+    std::lock_guard<std::recursive_mutex> lk_err(g_mu);
     if (!d_idx || !d_counts || !d_offsets || !d_perm || !A || !E)
         return fail("dispatch_dev_static: bad args");
     if (E > 1024) return fail("dispatch_dev_static: unsupported E=%zu", E);

@@ -167,7 +167,10 @@ class PeerWindowBlock:
 
     # the step in three parts, so that a test can run several ranks in one
     # process: all `begin`s before any `middle`, all `middle`s before any `end`
-    def begin(self, x):
+    def begin(self, x, mark=None):
+        """mark (optional): called with a stage name after each stage's launch,
+        so that a benchmark can bracket the stages with events."""
+        mark = mark or (lambda name: None)
         T, H = x.shape
         TK = self.cfg["top_k"]
         assert T <= self.max_tokens
@@ -182,29 +185,39 @@ class PeerWindowBlock:
         be, s = self.be, self._s()
         be.ep_route_dev(self.layer, x.data_ptr(), T, st["idx"].data_ptr(),
                         st["w"].data_ptr(), st["sgl"].data_ptr(), stream=s)
+        mark("route")
         be.ep_push_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
                        self.epoch, st["pos"].data_ptr(), stream=s)
+        mark("push")
         be.ep_shared_dev(self.layer, x.data_ptr(), T, st["sy"].data_ptr(),
                          stream=s)
+        mark("shared")
         return st
 
-    def middle(self):
+    def middle(self, mark=None):
+        mark = mark or (lambda name: None)
         be, s = self.be, self._s()
         be.ep_wait_dev(self.win, 0, self.epoch, stream=s)
+        mark("wait_rows")
         be.ep_window_experts_dev(self.win, self.layer, stream=s)
+        mark("experts")
         be.ep_return_dev(self.win, self.epoch, stream=s)
+        mark("return")
 
-    def end(self, st):
+    def end(self, st, mark=None):
+        mark = mark or (lambda name: None)
         be, s = self.be, self._s()
         x = st["x"]
         out = torch.empty_like(x)
         be.ep_wait_dev(self.win, 1, self.epoch, stream=s)
+        mark("wait_returns")
         be.ep_combine_dev(self.win, self.layer, x.shape[0], st["pos"].data_ptr(),
                           st["w"].data_ptr(), st["sy"].data_ptr(),
                           st["sgl"].data_ptr(), out.data_ptr(), stream=s)
+        mark("combine")
         return out
 
-    def forward(self, x):
-        st = self.begin(x)
-        self.middle()
-        return self.end(st)
+    def forward(self, x, mark=None):
+        st = self.begin(x, mark)
+        self.middle(mark)
+        return self.end(st, mark)

@@ -1,22 +1,32 @@
 #!/usr/bin/env python3
 """Benchmark of the MoE-block hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T]
-                  [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one pass of the MoE block (router -> top-8 -> dispatch -> routed
-SwiGLU experts + shared expert -> weighted combine) over one batch of T
-synthetic tokens at the Qwen3.6-35B-A3B dimensions (H 2048, 256 experts, top-8,
-I 512).  Default workload: T=512 prefill, one layer, seed 0, weights resident
-in HBM.  Prints ONE JSON line.
+SwiGLU experts + shared expert -> weighted combine) over one batch of synthetic
+tokens at the Qwen3.6-35B-A3B dimensions (H 2048, 256 experts, top-8, I 512),
+weights resident in HBM.  Prints ONE JSON line.
+
+Default workload, the same at every GPU count (strong scaling): one layer,
+T = 8192 tokens, Zipf(1.1)-skewed router (hottest expert about ten times the
+mean load), seed 0.  With N GPUs the experts are sharded 256/N per GPU and the
+tokens 8192/N per GPU; rows travel between GPUs inside the step.
 
   value      tokens/s with inputs already in HBM (CUDA events, max over ranks)
-  e2e        tokens/s through the host-pointer C-ABI call the engine would
-             make (pinned host input, host output, copies inside the timing)
-  roofline   the dominant kernel's algorithmic bytes / its own measured time,
-             against the measured HBM copy bandwidth
+  e2e        tokens/s through the call a user makes with HOST buffers (pinned
+             host input, host output, copies inside the timing)
+  roofline   the dominant kernel's algorithmic flops (or bytes) over its own
+             measured time, against the measured peak
+  sustained  the same step repeated for at least a second, with the SM clock
+             sampled meanwhile
+  parity     rows of the timed output checked against the CPU checker
   cpu_baseline  the reference's own C code (oracle/_ref) on this box's cores
+  configs    (N=1) the other single-GPU workloads: one token per layer over a
+             stack of layers, one layer at 512 tokens, and the 40-layer stack
+             chained through rmsnorm and the residual add at 1, 8, 64 tokens
 
+--tokens T [--uniform] [--layers L] [--chain] times one other shape alone.
 --impl reference times only the reference CPU arm and prints the same line
 shape with "impl": "reference".
 """
@@ -37,6 +47,14 @@ METRIC = "moe_layer_prefill_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0,
                       bf16_tflops_sustained=1400.0)
+HEADLINE_T = 8192
+ZIPF_S = 1.1
+# tuned once on seed 0 so that the hottest expert takes about ten times the
+# mean load at 8192 tokens (2579 rows against 256), then frozen
+ZIPF_BETA = 0.27
+MAX_T = 8448          # largest token count any workload of this file runs
+L2_BYTES = 126 << 20
+DTYPE = "bf16 storage, fp32 accumulate"
 
 
 def load_package():
@@ -58,6 +76,23 @@ def peaks():
     d = dict(FALLBACK_PEAKS)
     d["_source"] = "fallback"
     return d
+
+
+def workload_config(T, skew, seed, layers=1, chain=False):
+    """The `config` object: the same in both arms and at every GPU count."""
+    router = (f"Zipf({ZIPF_S}) router bias through a constant-1 input channel, "
+              f"beta {ZIPF_BETA}" if skew else "uniform router")
+    if layers == 1:
+        w = f"one MoE layer, T={T} tokens per step, {router}"
+    else:
+        w = (f"stack of {layers} MoE layers (independent weights"
+             + (", chained x <- x + moe(rmsnorm(x))" if chain
+                else ", one token batch per layer")
+             + f"), {T} tokens per layer per step, {router}")
+    return {"workload": w + f", seed {seed}, H2048 E256 top8 I512",
+            "tokens_per_step": T, "layers": layers, "skew": bool(skew),
+            "l2_policy": "inputs larger than L2 (126 MB): every step reads "
+                         "more than 1.3 GB of weights"}
 
 
 def algorithmic_bytes(cfg, T, unique_experts):
@@ -111,6 +146,11 @@ class ClockSampler(threading.Thread):
                 pass
             time.sleep(0.05)
 
+    def finish(self):
+        self.stop_flag = True
+        self.join()
+        return self.summary()
+
     def summary(self):
         s = sorted(self.samples)
         return dict(sm_mhz=s[len(s) // 2] if s else None,
@@ -118,23 +158,46 @@ class ClockSampler(threading.Thread):
                     samples=len(s))
 
 
-def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth, min_seconds=0.0):
+# --------------------------------------------------------------------------
+# inputs
+# --------------------------------------------------------------------------
+
+def host_inputs(src, synth, cfg, T, seed, skew, weights=True, layer=0):
+    """(W or None, x) on the host.  `src` provides synth_fill_host: the CUDA
+    binding in our arm, the CPU checker's host-only build in the reference
+    arm."""
+    x = synth.host_x(src, T, cfg["hidden"], seed=seed, layer=layer)
+    W = synth.host_weights(src, cfg, seed=seed, layer=layer) if weights else None
+    if skew:
+        bias = synth.zipf_bias(cfg, seed=seed, s=ZIPF_S, beta=ZIPF_BETA)
+        if W is None:
+            rtr = src.synth_fill_host(cfg["experts"] * cfg["hidden"], seed, layer,
+                                      synth.T_RTR, synth.W_SIGMA)
+            W = {"rtr_w": rtr.reshape(cfg["experts"], cfg["hidden"])}
+            W, x = synth.apply_router_bias(W, x, bias)
+            return W, x          # router matrix only
+        W, x = synth.apply_router_bias(W, x, bias)
+    return W, x
+
+
+def cpu_reference_arm(cfg, W, x, steps, warmup, budget_s=150.0, min_seconds=0.0):
     """Times the reference's own MoE block (apus_layer_moe_batch, AVX2 rows
-    over its pthread pool) on this host.  Returns (tokens/s, threads,
-    sample-description, ms_per_step).  With min_seconds the timed loop keeps
-    going (up to 64 steps) until that much CPU time has been sampled."""
+    over its pthread pool) on this host, on a bounded sample of the batch: the
+    first Ts tokens, Ts the largest power-of-two fraction of T for which
+    warmup + steps passes fit the time budget.  Returns (tokens/s, threads,
+    sample description, ms per step) or None."""
     from oracle import oracle
     if not oracle.Reference.available():
         return None
     ref = oracle.Reference()
-    W = synth.host_weights(be, cfg, seed=seed)
-    x = synth.host_x(be, T, cfg["hidden"], seed=seed)
-    # bound the sample: the full batch when it is cheap, else a slice of it
-    Ts = T
+    T = x.shape[0]
+    probe = min(T, 16)
+    ref.moe_block(cfg, W, x[:probe])
     t0 = time.perf_counter()
-    ref.moe_block(cfg, W, x[:min(T, 16)])
-    est = (time.perf_counter() - t0) * T / min(T, 16)
-    while Ts > 16 and est * Ts / T * (steps + warmup) > 60.0:
+    ref.moe_block(cfg, W, x[:probe])
+    per_tok = (time.perf_counter() - t0) / probe
+    Ts = T
+    while Ts > 16 and per_tok * Ts * (steps + warmup) > budget_s:
         Ts //= 2
     xs = x[:Ts]
     for _ in range(warmup):
@@ -147,39 +210,201 @@ def cpu_reference_arm(cfg, T, seed, steps, warmup, be, synth, min_seconds=0.0):
         best = dt if best is None else min(best, dt)
         spent += dt
         done += 1
-    sample = (f"{Ts} of {T} tokens, one layer, apus_layer_moe_batch, "
-              f"best of {done} ({spent:.1f} s sampled)")
+    sample = (f"first {Ts} of {T} tokens of the same batch, one layer, "
+              f"apus_layer_moe_batch, best of {done} ({spent:.1f} s sampled)")
     return Ts / best, ref.threads(), sample, best * 1e3
 
-L2_BYTES = 126 << 20
+
+# --------------------------------------------------------------------------
+# timing helpers (one GPU)
+# --------------------------------------------------------------------------
+
+def timed(torch, stream, step, steps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
 
 
-def run_stack(args, cfg, config, pkg, synth, L):
-    """A stack of L MoE layers with independent seeded weights, generated in
-    place in HBM.  Every step runs every layer's block once, so nothing a step
-    needs is left in L2 by the previous one.  Layer l reads its own seeded
-    token batch; with --chain the layers are chained as the engine chains them
-    (c/layer.h:386-388): ln2 = rmsnorm(h); h = rnd(h + moe_l(ln2)), and the
-    two elementwise kernels are inside the timed region."""
+def sustained(torch, stream, step, ms_hint, seconds, device_index=0):
+    """The step repeated for at least `seconds`, one timed region, the SM clock
+    sampled meanwhile.  time x clock lets two runs at different clocks be
+    compared."""
+    n = max(8, int(seconds * 1e3 / max(ms_hint, 1e-3)) + 1)
+    sampler = ClockSampler(device_index)
+    sampler.start()
+    time.sleep(0.12)
+    ms = timed(torch, stream, step, n)
+    clk = sampler.finish()
+    return {"steps": n, "ms_per_step": ms, "region_s": ms * n * 1e-3,
+            "clocks": clk,
+            "ms_x_sm_mhz": ms * clk["sm_mhz"] if clk.get("sm_mhz") else None}
+
+
+def capture(torch, stream, fn, no_graph):
+    """fn captured once into a CUDA graph; returns (step callable, mode)."""
+    if no_graph:
+        return fn, "host launches"
+    try:
+        g = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        return g.replay, "cuda graph replay"
+    except Exception as e:          # capture unsupported: say so, go on
+        torch.cuda.synchronize()
+        return fn, f"host launches (graph capture failed: {e})"
+
+
+def measure_layer(env, layer, x_host, T, skew, steps, warmup, sustain_s,
+                  W_host=None, want_e2e=False):
+    """One layer, T tokens.  Returns the measurement object; env carries the
+    backend, torch, stream and peaks."""
     import numpy as np
-    import torch
-    torch.cuda.set_device(0)
-    be = pkg.Backend()
-    be.enable()
-    T, H, TK = args.tokens, cfg["hidden"], cfg["top_k"]
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
+    be, torch, stream, cfg, pk = env["be"], env["torch"], env["stream"], env["cfg"], env["pk"]
     sp = stream.cuda_stream
-    layers = []
-    for l in range(L):
-        h = be.layer_create(cfg, None)
-        synth.device_weights(be, h, cfg, seed=args.seed, layer=l, stream=sp)
-        layers.append(h)
-    be.reserve(cfg, T)
-    chain = args.chain
+    H, TK, I = cfg["hidden"], cfg["top_k"], cfg["moe_inter"]
+    d_x = torch.from_numpy(x_host.view(np.int16)).cuda()
+    d_out = torch.empty_like(d_x)
+    d_idx = torch.empty((T, TK), dtype=torch.int32, device="cuda")
+
+    def direct():
+        be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp)
+
+    be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp,
+                     d_trace={"idx": d_idx.data_ptr()})
+    torch.cuda.synchronize()
+    idx = d_idx.cpu().numpy()
+    load = np.bincount(idx.ravel(), minlength=cfg["experts"])
+    uniq = int((load > 0).sum())
+    launches_per_step = be.last_block_launches()
+    step, mode = capture(torch, stream, direct, env["no_graph"])
+    for _ in range(max(3, warmup)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(torch, stream, step, steps)
+    status = be.last_block_status()
+    # per-stage times, measured live with CUDA events on the launching stream
+    be.stage_timing(True)
+    acc = {}
+    for _ in range(max(3, min(steps, 10))):
+        direct()
+        for k, v in be.last_stage_ms().items():
+            acc[k] = acc.get(k, 0.0) + v
+    be.stage_timing(False)
+    nst = max(3, min(steps, 10))
+    stage_ms = {k: v / nst for k, v in acc.items()}
+    clocks = sampler.finish()
+    res = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "launch": mode,
+           "us_per_token": ms * 1e3 / T, "clocks": clocks,
+           "unique_experts": uniq, "max_over_mean_load": float(load.max() / load.mean()),
+           "stage_ms": stage_ms, "launches_per_step": launches_per_step,
+           "device_status": status}
+    if sustain_s > 0:
+        res["sustained"] = sustained(torch, stream, step, ms, sustain_s)
+    # roofline of the dominant kernel
+    slab_gu, slab_d = 2 * I * H * 2, H * I * 2
+    A = T * TK
+    block_bytes = algorithmic_bytes(cfg, T, uniq)
+    hbm_ideal = block_bytes / (pk["hbm_gbs"] * 1e9)
+    tc_ideal = flops(cfg, T) / (pk["bf16_tflops"] * 1e12)
+    if launches_per_step == 1:
+        kms = sum(stage_ms.values())
+        roof = {"bound": "hbm", "kernel": "decode_fused_kernel",
+                "achieved": block_bytes / (kms * 1e-3) / 1e9 if kms else None,
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
+                "algorithmic_bytes_per_launch": block_bytes}
+    else:
+        dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
+        kname = f"grouped_gemm_kernel<{dom}>"
+        if dom == "gate_up":
+            kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * I * 2
+            kflops = 2 * (A + T) * 2 * I * H
+        else:
+            kbytes = (uniq + 1) * slab_d + (A + T) * I * 2 + (A + T) * H * 2
+            kflops = 2 * (A + T) * H * I
+        kms = stage_ms.get(dom, 0.0)
+        if tc_ideal > hbm_ideal:
+            roof = {"bound": "tensor", "kernel": kname,
+                    "achieved": kflops / (kms * 1e-3) / 1e12 if kms else None,
+                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "traffic": None,
+                    "algorithmic_flops_per_launch": kflops,
+                    "peak_kind": "burst (kernel timed alone between events)"}
+        else:
+            roof = {"bound": "hbm", "kernel": kname,
+                    "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
+                    "algorithmic_bytes_per_launch": kbytes}
+    roof["peak_source"] = pk["_source"]
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
+    res["roofline"] = roof
+    res["block"] = {
+        "algorithmic_bytes": block_bytes, "algorithmic_flops": flops(cfg, T),
+        "hbm_frac_of_measured": block_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+        "tensor_frac_of_measured_burst": flops(cfg, T) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
+        "binding": "tensor" if tc_ideal > hbm_ideal else "hbm"}
+    if "sustained" in res:
+        sms = res["sustained"]["ms_per_step"]
+        res["block"]["tensor_frac_of_measured_sustained"] = (
+            flops(cfg, T) / (sms * 1e-3) / 1e12 / pk.get("bf16_tflops_sustained",
+                                                         pk["bf16_tflops"]))
+        res["block"]["hbm_frac_of_measured_sustained"] = (
+            block_bytes / (sms * 1e-3) / 1e9 / pk["hbm_gbs"])
+    res["_out"] = d_out.cpu().numpy().view(np.uint16)
+    res["_idx"] = idx
+    if want_e2e and W_host is not None:
+        import ctypes as C
+        pkg = env["pkg"]
+        xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
+        xout = torch.empty_like(xin).pin_memory()
+        xin_np, xout_np = xin.numpy().view(np.uint16), xout.numpy().view(np.uint16)
+        c_cfg = pkg.backend.MoeCfg.from_dict(cfg)
+        c_w = pkg.backend.MoeW(*[W_host[k].ctypes.data for k in
+                                 ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u",
+                                  "sh_d", "sh_gate")])
+
+        def e2e_step():
+            rc = be.lib.apus_cuda_moe_block(
+                C.byref(c_cfg), C.byref(c_w),
+                xin_np.ctypes.data_as(C.POINTER(C.c_uint16)),
+                xout_np.ctypes.data_as(C.POINTER(C.c_uint16)), T, None)
+            if rc:
+                raise RuntimeError(be.last_error())
+        for _ in range(3):
+            e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+        assert np.array_equal(xout_np, res["_out"]), \
+            "host-pointer and device-pointer entry points disagree"
+        res["e2e"] = {"value": T / (e2e_ms * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
+                      "ms_per_step": e2e_ms,
+                      "call": "apus_cuda_moe_block (host pointers, pinned buffers)"}
+    return res
+
+
+def measure_stack(env, layers, T, chain, steps, warmup, sustain_s, seed,
+                  want_e2e=True):
+    """A stack of MoE layers with independent seeded weights.  Every step runs
+    every layer's block once, so nothing a step needs is left in L2 by the
+    previous one.  Layer l reads its own seeded token batch; with `chain` the
+    layers are chained as the engine chains them (c/layer.h:386-388): ln2 =
+    rmsnorm(h); h = rnd(h + moe_l(ln2)), the two elementwise steps inside the
+    timed region."""
+    import numpy as np
+    be, torch, stream, cfg, pk = env["be"], env["torch"], env["stream"], env["cfg"], env["pk"]
+    synth = env["synth"]
+    sp = stream.cuda_stream
+    L, H, TK = len(layers), cfg["hidden"], cfg["top_k"]
     n_in = 1 if chain else L
-    x_host = np.stack([synth.host_x(be, T, H, seed=args.seed, layer=l)
-                       for l in range(n_in)])
+    x_host = np.stack([synth.host_x(be, T, H, seed=seed, layer=l) for l in range(n_in)])
     d_x = torch.from_numpy(x_host.view(np.int16)).cuda()      # [n_in, T, H]
     d_h = torch.empty_like(d_x)                               # chain state / outputs
     d_ln = torch.empty((T, H), dtype=torch.int16, device="cuda")
@@ -213,101 +438,245 @@ def run_stack(args, cfg, config, pkg, synth, L):
     one_pass(trace_uniq=uniq)
     torch.cuda.synchronize()
     launches_per_layer = be.last_block_launches() + (2 if chain else 0)
-    step = one_pass
-    launch_mode = "host launches"
-    if not args.no_graph:
-        try:
-            g = torch.cuda.CUDAGraph()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                one_pass()
-            step = g.replay
-            launch_mode = "cuda graph replay"
-        except Exception as e:
-            launch_mode = f"host launches (graph capture failed: {e})"
-            torch.cuda.synchronize()
-    for _ in range(args.warmup):
+    fused = be.last_block_launches() == 1
+    step, mode = capture(torch, stream, one_pass, env["no_graph"])
+    for _ in range(max(3, warmup)):
         step()
-    torch.cuda.synchronize()
     sampler = ClockSampler(0)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = timed(torch, stream, step, steps)
     status = be.last_block_status()
-    # stage times (host launches, events / device timeline per layer)
     be.stage_timing(True)
     acc = {}
     one_pass(timing=acc)
     be.stage_timing(False)
     stage_ms = {k: v / L for k, v in acc.items()}
-    # end to end: pinned host tokens in, result back to host, every step
-    xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
-    hout = torch.empty_like(xin).pin_memory()
-    for _ in range(3):
-        d_x.copy_(xin, non_blocking=True); step(); hout.copy_(d_h, non_blocking=True)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        d_x.copy_(xin, non_blocking=True)
-        step()
-        hout.copy_(d_h, non_blocking=True)
-        torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    sampler.stop_flag = True
-    sampler.join()
-
-    pk = peaks()
+    clocks = sampler.finish()
     bytes_pass = sum(algorithmic_bytes(cfg, T, u) for u in uniq)
     tok_layers = T * L
-    cfgline = dict(config)
-    cfgline.update({
-        "workload": f"stack of {L} MoE layers (independent weights"
-                    + (", chained x <- x + moe(rmsnorm(x))" if chain else
-                       ", one token batch per layer")
-                    + f"), {T} tokens per layer per step, uniform router, "
-                    f"seed {args.seed}, H2048 E256 top8 I512",
-        "layers": L, "launch": launch_mode,
-        "l2_policy": f"inputs larger than L2: one pass reads "
-                     f"{bytes_pass / 1e6:.0f} MB of weights across {L} layers"})
     kms = sum(stage_ms.values())
-    fused = be.last_block_launches() == 1
-    line = {
-        "metric": METRIC, "value": tok_layers / (ms * 1e-3), "unit": UNIT,
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16 storage, fp32 accumulate",
-        "data": "synthetic", "config": cfgline, "clocks": sampler.summary(),
-        "e2e": {"value": tok_layers / (e2e_ms * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": n_in * T * H * 2,
-                "d2h_bytes_per_step": n_in * T * H * 2,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": launches_per_layer * L * args.steps,
-        "roofline": {"bound": "hbm",
-                     "kernel": "decode_fused_kernel" if fused else "whole layer (all kernels)",
-                     "achieved": bytes_pass / L / (kms * 1e-3) / 1e9 if kms else None,
-                     "peak": pk["hbm_gbs"], "peak_source": pk["_source"],
-                     "unit": "GB/s",
-                     "frac": (bytes_pass / L / (kms * 1e-3) / 1e9 / pk["hbm_gbs"]) if kms else None,
-                     "traffic": None,
-                     "algorithmic_bytes_per_launch": bytes_pass / L},
-        "block": {"algorithmic_bytes_per_layer": bytes_pass / L,
-                  "hbm_frac_of_measured": bytes_pass / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
-                  "unique_experts_mean": sum(uniq) / L, "stage_ms_per_layer": stage_ms,
-                  "us_per_token_layer": ms * 1e3 / tok_layers,
-                  "device_status": status},
-    }
+    res = {"ms_per_step": ms, "token_layers_per_s": tok_layers / (ms * 1e-3),
+           "us_per_token_layer": ms * 1e3 / tok_layers, "layers": L,
+           "tokens_per_layer": T, "chained": bool(chain), "launch": mode,
+           "clocks": clocks, "launches_per_step": launches_per_layer * L,
+           "unique_experts_mean": sum(uniq) / L, "stage_ms_per_layer": stage_ms,
+           "device_status": status,
+           "l2_policy": f"inputs larger than L2: one pass reads "
+                        f"{bytes_pass / 1e6:.0f} MB of weights across {L} layers",
+           "roofline": {"bound": "hbm",
+                        "kernel": "decode_fused_kernel" if fused else
+                                  "whole layer (all kernels of the block)",
+                        "achieved": bytes_pass / L / (kms * 1e-3) / 1e9 if kms else None,
+                        "peak": pk["hbm_gbs"], "peak_source": pk["_source"],
+                        "unit": "GB/s",
+                        "frac": (bytes_pass / L / (kms * 1e-3) / 1e9 / pk["hbm_gbs"])
+                                if kms else None,
+                        "traffic": None,
+                        "algorithmic_bytes_per_launch": bytes_pass / L},
+           "block": {"algorithmic_bytes_per_layer": bytes_pass / L,
+                     "hbm_frac_of_measured": bytes_pass / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                     "ideal_ms_per_step_at_measured_hbm":
+                         bytes_pass / (pk["hbm_gbs"] * 1e9) * 1e3}}
+    if sustain_s > 0:
+        res["sustained"] = sustained(torch, stream, step, ms, sustain_s)
+    if want_e2e:
+        # end to end: pinned host tokens in, result back to host, every step
+        xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
+        hout = torch.empty_like(xin).pin_memory()
+        for _ in range(3):
+            d_x.copy_(xin, non_blocking=True); step(); hout.copy_(d_h, non_blocking=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            d_x.copy_(xin, non_blocking=True)
+            step()
+            hout.copy_(d_h, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+        res["e2e"] = {"value": tok_layers / (e2e_ms * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": n_in * T * H * 2,
+                      "d2h_bytes_per_step": n_in * T * H * 2, "ms_per_step": e2e_ms}
+    return res
+
+
+def strip(res):
+    return {k: v for k, v in res.items() if not k.startswith("_")}
+
+
+def device_layers(env, n, seed):
+    """n layers with independent seeded weights, generated in place in HBM."""
+    be, synth, cfg = env["be"], env["synth"], env["cfg"]
+    sp = env["stream"].cuda_stream
+    out = []
+    for l in range(n):
+        h = be.layer_create(cfg, None)
+        synth.device_weights(be, h, cfg, seed=seed, layer=l, stream=sp)
+        out.append(h)
+    return out
+
+
+def make_env(pkg, synth, cfg, no_graph):
+    import torch
+    torch.cuda.set_device(0)
+    be = pkg.Backend()
+    be.enable()
+    stream = torch.cuda.Stream()       # every launch and event goes here
+    torch.cuda.set_stream(stream)
+    be.reserve(cfg, MAX_T)             # before any capture: growth would stall
+    return dict(be=be, torch=torch, stream=stream, cfg=cfg, pk=peaks(), pkg=pkg,
+                synth=synth, no_graph=no_graph)
+
+
+def line_from_layer(res, config, args, T):
+    line = {"metric": METRIC, "value": res["tokens_per_s"], "unit": UNIT,
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
+            "data": "synthetic", "config": config, "launch": res["launch"],
+            "clocks": res["clocks"],
+            "gpu_launches": res["launches_per_step"] * args.steps,
+            "roofline": res["roofline"]}
+    for k in ("e2e", "sustained"):
+        if k in res:
+            line[k] = res[k]
+    blk = dict(res["block"])
+    blk.update(unique_experts=res["unique_experts"],
+               max_over_mean_load=res["max_over_mean_load"],
+               stage_ms=res["stage_ms"], us_per_token=res["us_per_token"],
+               device_status=res["device_status"])
+    line["block"] = blk
+    return line
+
+
+def run_headline(args, cfg, pkg, synth):
+    """N = 1: configuration 3's workload on one GPU, then the other single-GPU
+    configurations as sub-measurements."""
+    import numpy as np
+    env = make_env(pkg, synth, cfg, args.no_graph)
+    be = env["be"]
+    T, skew = HEADLINE_T, True
+    W, x_host = host_inputs(be, synth, cfg, T, args.seed, skew)
+    layer = be.layer_create(cfg, W)
+    res = measure_layer(env, layer, x_host, T, skew, args.steps, args.warmup,
+                        args.sustain, W_host=W, want_e2e=True)
+    line = line_from_layer(res, workload_config(T, skew, args.seed), args, T)
+    # parity of the timed output: ids of every token, full rows on a sample
+    from oracle import oracle
+    orc = oracle.Restatement()
+    ridx, _ = orc.route_batch(x_host, W["rtr_w"], cfg["top_k"])
+    rows = np.sort(np.random.default_rng(args.seed).choice(T, 32, replace=False))
+    exp = orc.moe_block(cfg, W, np.ascontiguousarray(x_host[rows]))
+    a = synth.bf16_to_f32(res["_out"][rows]).astype(np.float64)
+    b = synth.bf16_to_f32(exp["out"]).astype(np.float64)
+    par = {"rows": int(len(rows)), "idx_exact": bool(np.array_equal(res["_idx"][rows], exp["idx"])),
+           "idx_exact_all_tokens": bool(np.array_equal(res["_idx"], ridx)),
+           "tokens_with_ids_checked": int(T),
+           "max_abs": float(np.abs(a - b).max()),
+           "rel_l2": float(np.linalg.norm(a - b) / (np.linalg.norm(b) + 1e-30)),
+           "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2},
+           "checker": "oracle.Restatement(): route_batch on every token, "
+                      "moe_block on the sampled rows"}
+    par["ok"] = bool(par["idx_exact"] and par["idx_exact_all_tokens"]
+                     and par["max_abs"] <= 2e-2 and par["rel_l2"] <= 1e-2)
+    line["parity"] = par
     if not args.no_cpu_baseline:
-        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth, min_seconds=10.0)
+        r = cpu_reference_arm(cfg, W, x_host, 3, 1, budget_s=20.0, min_seconds=10.0)
         if r is not None:
             v, threads, sample, _ = r
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
-                                    "kind": "reference",
-                                    "sample": sample + " (one layer of the stack)"}
+                                    "kind": "reference", "sample": sample}
+    be.layer_destroy(layer)
+    del W
+    if not args.no_sub:
+        subs = {}
+        st, wu = args.steps, args.warmup
+        stack = device_layers(env, 40, args.seed)
+        x512 = synth.host_x(be, 512, cfg["hidden"], seed=args.seed)
+        r = measure_layer(env, stack[0], x512, 512, False, st, wu, args.sustain / 2)
+        subs["config1_one_layer_T512_uniform"] = dict(
+            strip(r), config=workload_config(512, False, args.seed))
+        r = measure_stack(env, stack[:10], 1, False, st, wu, args.sustain / 2, args.seed)
+        subs["config0_decode_T1"] = dict(
+            r, config=workload_config(1, False, args.seed, 10, False),
+            note="the T=1 block of configuration 0, run over ten independent "
+                 "layers per step so that no weight byte is L2-resident from "
+                 "the step before")
+        for B in (1, 8, 64):
+            r = measure_stack(env, stack, B, True, st, wu, args.sustain / 2, args.seed)
+            subs[f"config2_40_layers_chained_B{B}"] = dict(
+                r, config=workload_config(B, False, args.seed, 40, True))
+        line["configs"] = subs
+    print(json.dumps(line))
+
+
+def run_manual(args, cfg, pkg, synth):
+    """--tokens T: one other shape alone (profiling runs, sweeps)."""
+    env = make_env(pkg, synth, cfg, args.no_graph)
+    be = env["be"]
+    T, skew = args.tokens, not args.uniform
+    L = args.layers
+    if L <= 0:
+        est_uniq = min(cfg["experts"], T * cfg["top_k"])
+        per_layer = algorithmic_bytes(cfg, T, est_uniq)
+        L = 1 if per_layer >= 4 * L2_BYTES else -(-4 * L2_BYTES // per_layer)
+    if L > 1:
+        layers = device_layers(env, L, args.seed)
+        r = measure_stack(env, layers, T, args.chain, args.steps, args.warmup,
+                          args.sustain, args.seed)
+        line = {"metric": METRIC, "value": r["token_layers_per_s"], "unit": UNIT,
+                "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
+                "data": "synthetic",
+                "config": workload_config(T, False, args.seed, L, args.chain),
+                "launch": r["launch"], "clocks": r["clocks"], "e2e": r.get("e2e"),
+                "gpu_launches": r["launches_per_step"] * args.steps,
+                "roofline": r["roofline"], "block": r["block"],
+                "stage_ms_per_layer": r["stage_ms_per_layer"],
+                "us_per_token_layer": r["us_per_token_layer"]}
+        if "sustained" in r:
+            line["sustained"] = r["sustained"]
+        print(json.dumps(line))
+        return
+    W, x_host = host_inputs(be, synth, cfg, T, args.seed, skew)
+    layer = be.layer_create(cfg, W)
+    res = measure_layer(env, layer, x_host, T, skew, args.steps, args.warmup,
+                        args.sustain, W_host=W, want_e2e=True)
+    line = line_from_layer(res, workload_config(T, skew, args.seed), args, T)
+    if not args.no_cpu_baseline:
+        r = cpu_reference_arm(cfg, W, x_host, 3, 1, budget_s=20.0, min_seconds=10.0)
+        if r is not None:
+            v, threads, sample, _ = r
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
+                                    "kind": "reference", "sample": sample}
+    print(json.dumps(line))
+
+
+def run_reference(args, cfg, synth):
+    """The reference's own CPU implementation of the path on this box's host
+    cores, on the configuration of our arm.  Inputs come from the checker's
+    host-only build of the generator: the CUDA library is not loaded."""
+    from oracle import oracle
+    T = args.tokens or HEADLINE_T
+    skew = not args.uniform
+    config = workload_config(T, skew, args.seed)
+    if not oracle.Reference.available():
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "oracle/_ref was not built"}))
+        return
+    orc = oracle.Restatement()
+    W, x = host_inputs(orc, synth, cfg, T, args.seed, skew)
+    v, threads, sample, ms = cpu_reference_arm(cfg, W, x, args.steps, args.warmup,
+                                               budget_s=150.0)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 storage, fp32 arithmetic",
+            "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads,
+                             "kind": "reference", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
@@ -316,15 +685,22 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--tokens", type=int, default=512)
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="time this many tokens (global) instead of the default "
+                         "workload; one GPU: that shape alone, no sub-measurements")
+    ap.add_argument("--uniform", action="store_true",
+                    help="uniform router instead of the Zipf-skewed one")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub", action="store_true",
+                    help="skip the sub-measurements of the one-GPU line")
+    ap.add_argument("--sustain", type=float, default=1.0,
+                    help="seconds of the sustained region (0: skip)")
     ap.add_argument("--layers", type=int, default=0,
-                    help="run a stack of this many MoE layers with independent "
-                         "weights, chained as x <- x + moe(rmsnorm(x)); default: "
-                         "1, or as many as it takes for one pass to read more "
-                         "than four times the L2 capacity (small token counts)")
+                    help="with --tokens: a stack of this many MoE layers with "
+                         "independent weights; default 1, or as many as it takes "
+                         "for one pass to read four times the L2 capacity")
     ap.add_argument("--chain", action="store_true",
                     help="with a layer stack: chain the layers through rmsnorm "
                          "and the residual add instead of one batch per layer")
@@ -334,6 +710,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from the host instead of "
                          "replaying a captured CUDA graph")
+    ap.add_argument("--no-check", action="store_true",
+                    help="multi-GPU arm: skip the output check after the timing")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -341,225 +719,24 @@ def main():
     pkg = load_package()
     import apus_b200.synth as synth
     cfg = dict(synth.QWEN_CFG)
-    T = args.tokens
-    config = {"workload": f"one MoE layer, prefill T={T}, uniform router, seed "
-                          f"{args.seed}, H2048 E256 top8 I512",
-              "tokens_per_step": T, "layers": 1,
-              "l2_policy": "inputs larger than L2 (1.6 GB of weights per step)"}
 
     if args.impl == "reference":
-        if rank != 0:
-            return
-        be = pkg.Backend()
-        steps = max(1, min(args.steps, 5))
-        warm = max(1, min(args.warmup, 2))
-        r = cpu_reference_arm(cfg, T, args.seed, steps, warm, be, synth)
-        if r is None:
-            print(json.dumps({"impl": "reference",
-                              "unavailable": "oracle/_ref was not built"}))
-            return
-        v, threads, sample, ms = r
-        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT,
-                "n_gpus": args.gpus, "steps": steps, "warmup": warm,
-                "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "bf16 storage, fp32 arithmetic",
-                "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads,
-                                 "kind": "reference", "sample": sample},
-                "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        if rank == 0:
+            run_reference(args, cfg, synth)
         return
-
-    import numpy as np
-    import torch
     if world > 1:
         from apus_b200 import ep_bench
-        ep_bench.run(args, cfg, config, pkg, synth, METRIC, UNIT, peaks(), ClockSampler)
+        T = args.tokens or HEADLINE_T
+        skew = not args.uniform
+        ep_bench.run(args, cfg, workload_config(T, skew, args.seed), pkg, synth,
+                     METRIC, UNIT, peaks(), ClockSampler,
+                     dict(T=T, skew=skew, zipf_s=ZIPF_S, zipf_beta=ZIPF_BETA,
+                          flops=flops(cfg, T), dtype=DTYPE))
         return
-
-    # small token counts touch few experts: one layer's working set would sit
-    # in L2 from step to step, so they run as a stack of independent layers
-    L = args.layers
-    if L <= 0:
-        est_uniq = min(cfg["experts"], T * cfg["top_k"])
-        per_layer = algorithmic_bytes(cfg, T, est_uniq)
-        L = 1 if per_layer >= 4 * L2_BYTES else -(-4 * L2_BYTES // per_layer)
-    if L > 1:
-        run_stack(args, cfg, config, pkg, synth, L)
-        return
-
-    torch.cuda.set_device(0)
-    be = pkg.Backend()
-    be.enable()
-    H = cfg["hidden"]
-    W = synth.host_weights(be, cfg, seed=args.seed)
-    x_host = synth.host_x(be, T, H, seed=args.seed)
-    layer = be.layer_create(cfg, W)
-    be.reserve(cfg, T)
-    stream = torch.cuda.Stream()       # every launch and event goes here
-    torch.cuda.set_stream(stream)
-    d_x = torch.from_numpy(x_host.view(np.int16)).cuda()
-    d_out = torch.empty_like(d_x)
-    d_idx = torch.empty((T, cfg["top_k"]), dtype=torch.int32, device="cuda")
-    sp = stream.cuda_stream
-
-    def step():
-        be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp)
-
-    # unique experts touched (for the algorithmic byte count)
-    be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T, stream=sp,
-                     d_trace={"idx": d_idx.data_ptr()})
-    torch.cuda.synchronize()
-    uniq = int(torch.unique(d_idx).numel())
-    launches_per_step = be.last_block_launches()
-
-    # one block call captured into a CUDA graph: the replay is what a serving
-    # loop would issue per layer (no per-launch host work)
-    launch_mode = "host launches"
-    if not args.no_graph:
-        try:
-            g = torch.cuda.CUDAGraph()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=stream):
-                be.moe_block_dev(layer, d_x.data_ptr(), d_out.data_ptr(), T,
-                                 stream=torch.cuda.current_stream().cuda_stream)
-            direct = step
-            step = g.replay
-            launch_mode = "cuda graph replay"
-        except Exception as e:          # capture unsupported: say so, go on
-            launch_mode = f"host launches (graph capture failed: {e})"
-            torch.cuda.synchronize()
-    config["launch"] = launch_mode
-
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    status = be.last_block_status()
-
-    # per-stage times, measured live with CUDA events on the launching stream
-    if launch_mode.startswith("cuda graph"):
-        step = direct
-    be.stage_timing(True)
-    acc = {}
-    for _ in range(args.steps):
-        step()
-        for k, v in be.last_stage_ms().items():
-            acc[k] = acc.get(k, 0.0) + v
-    be.stage_timing(False)
-    stage_ms = {k: v / args.steps for k, v in acc.items()}
-
-    # end to end through the host-pointer entry point (pinned host buffers)
-    xin = torch.from_numpy(x_host.view(np.int16)).pin_memory()
-    xout = torch.empty_like(xin).pin_memory()
-    xin_np, xout_np = xin.numpy().view(np.uint16), xout.numpy().view(np.uint16)
-    c_cfg = pkg.backend.MoeCfg.from_dict(cfg)
-    c_w = pkg.backend.MoeW(*[W[k].ctypes.data for k in
-                             ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u",
-                              "sh_d", "sh_gate")])
-    import ctypes as C
-
-    def e2e_step():
-        rc = be.lib.apus_cuda_moe_block(
-            C.byref(c_cfg), C.byref(c_w),
-            xin_np.ctypes.data_as(C.POINTER(C.c_uint16)),
-            xout_np.ctypes.data_as(C.POINTER(C.c_uint16)), T, None)
-        if rc:
-            raise RuntimeError(be.last_error())
-    for _ in range(max(3, args.warmup)):
-        e2e_step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    sampler.stop_flag = True
-    sampler.join()
-    assert np.array_equal(xout_np, d_out.cpu().numpy().view(np.uint16)), \
-        "host-pointer and device-pointer entry points disagree"
-
-    pk = peaks()
-    slab_gu = 2 * cfg["moe_inter"] * H * 2
-    slab_d = H * cfg["moe_inter"] * 2
-    A = T * cfg["top_k"]
-    I = cfg["moe_inter"]
-    hbm_ideal = algorithmic_bytes(cfg, T, uniq) / (pk["hbm_gbs"] * 1e9)
-    tc_ideal = flops(cfg, T) / (pk["bf16_tflops"] * 1e12)
-    if launches_per_step == 1:
-        # the one-kernel decode path: the kernel IS the block; its duration is
-        # the device-timeline sum of its phases
-        dom = "decode_fused_kernel"
-        kbytes = algorithmic_bytes(cfg, T, uniq)
-        kms = sum(stage_ms.values())
-        roof = {"bound": "hbm", "kernel": dom,
-                "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
-                "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
-                "algorithmic_bytes_per_launch": kbytes}
+    if args.tokens:
+        run_manual(args, cfg, pkg, synth)
     else:
-        dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
-        kname = ("grouped_gemm_kernel<gate_up>" if dom == "gate_up"
-                 else "grouped_gemm_kernel<down>")
-        if T <= 4:
-            kname = "decode_" + dom + "_kernel"
-        if dom == "gate_up":
-            kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * I * 2
-            kflops = 2 * (A + T) * 2 * I * H
-        else:
-            kbytes = (uniq + 1) * slab_d + (A + T) * I * 2 + (A + T) * H * 2
-            kflops = 2 * (A + T) * H * I
-        kms = stage_ms.get(dom, 0.0)
-        if tc_ideal > hbm_ideal:
-            roof = {"bound": "tensor", "kernel": kname,
-                    "achieved": kflops / (kms * 1e-3) / 1e12 if kms else None,
-                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "traffic": None,
-                    "algorithmic_flops_per_launch": kflops}
-        else:
-            # ncu dram__bytes_read+write of this launch at the default workload
-            # (profiles/grouped_gemm_t512_prefill.md); other sizes not captured
-            traffic = None
-            if T == 512 and uniq == 256:
-                traffic = 1.1005e9 + 7.5e6 if dom == "gate_up" else 0.5439e9 + 17.2e6
-            roof = {"bound": "hbm", "kernel": kname,
-                    "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": traffic,
-                    "algorithmic_bytes_per_launch": kbytes}
-    roof["peak_source"] = pk["_source"]
-    roof["frac"] = roof["achieved"] / roof["peak"] if roof["achieved"] else None
-    block_bytes = algorithmic_bytes(cfg, T, uniq)
-    line = {
-        "metric": METRIC, "value": T / (ms * 1e-3), "unit": UNIT,
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16 storage, fp32 accumulate",
-        "data": "synthetic", "config": config,
-        "clocks": sampler.summary(),
-        "e2e": {"value": T / (e2e_ms * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": roof,
-        "block": {"algorithmic_bytes": block_bytes,
-                  "hbm_frac_of_measured": block_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
-                  "tensor_frac_of_measured": flops(cfg, T) / (ms * 1e-3) / 1e12 / pk["bf16_tflops"],
-                  "unique_experts": uniq, "stage_ms": stage_ms,
-                  "us_per_token": ms * 1e3 / T, "device_status": status},
-    }
-    if not args.no_cpu_baseline:
-        r = cpu_reference_arm(cfg, T, args.seed, 3, 1, be, synth, min_seconds=10.0)
-        if r is not None:
-            v, threads, sample, _ = r
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads,
-                                    "kind": "reference", "sample": sample}
-    print(json.dumps(line))
+        run_headline(args, cfg, pkg, synth)
 
 
 if __name__ == "__main__":

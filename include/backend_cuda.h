@@ -185,19 +185,44 @@ void *apus_cuda_layer_tensor(ApusCudaLayer *layer, int which, size_t *elems);
  * router weights for the magnitude bound the router kernel's fast path
  * depends on. */
 int apus_cuda_layer_refresh(ApusCudaLayer *layer);
+/* Copy n BF16 elements from host memory into tensor `which` of the layer,
+ * starting at element `first` of the resident part (ids as for
+ * apus_cuda_layer_tensor).  Synchronous set-up call; the engine's eager load
+ * fills exp_gu / exp_d expert by expert like this (c/model.h:505-537).
+ * Writing rtr_w or sh_gate refreshes the router statistics. */
+int apus_cuda_layer_upload(ApusCudaLayer *layer, int which, const uint16_t *src,
+                           size_t first, size_t n);
 
 /* The block on device pointers: d_ln2 [T,H] -> d_out [T,H]; d_tr members are
  * device pointers (or NULL).  Enqueued on `stream` (a cudaStream_t; NULL is the
- * CUDA default stream, as everywhere in this header); does not synchronise.  Workspace comes from a
- * per-process arena that grows on demand (growth synchronises; call
- * apus_cuda_reserve first to avoid that inside a timed region or a stream
- * capture).  Path selection: T <= APUS_CUDA_DECODE_MAX_T (default 64) takes
- * the bandwidth-bound grouped-GEMV kernels, larger T the tcgen05 grouped
- * GEMM. */
+ * CUDA default stream, as everywhere in this header); does not synchronise.
+ *
+ * Path selection: T <= APUS_CUDA_FUSED_MAX_T (default and maximum 4) runs the
+ * whole block as one cooperative kernel; larger T runs router -> dispatch ->
+ * tcgen05 grouped GEMMs (gate/up, down) -> combine when the shape fits the MMA
+ * tiles (H, I, Is multiples of 128, Is == I), else the grouped-GEMV kernels.
+ * APUS_CUDA_DECODE_MAX_T (default 4) is the largest T that still takes the
+ * grouped-GEMV kernels on a shape the GEMM supports.
+ *
+ * Shared state.  Every device-pointer entry point of this header (the block,
+ * the expert-parallel steps, route_dev, dispatch_dev) works in ONE per-process
+ * workspace with one status word, whatever stream it is given.  The library
+ * therefore orders a call behind the previous call when it arrives on a
+ * different stream (an event wait on the device; no host synchronisation), so
+ * calls from two streams or two threads are serialised on the GPU, not raced.
+ * Inside a stream capture no such event is recorded or waited for: graphs
+ * captured from these calls must be replayed in one stream order by the caller.
+ *
+ * Workspace growth.  The arena grows on demand; growth synchronises the device
+ * and is refused (nonzero return) while `stream` is capturing.  Call
+ * apus_cuda_reserve for the largest T first to keep both out of a timed region
+ * or a capture.  An outgrown arena is kept allocated until apus_cuda_disable,
+ * so a graph captured earlier stays valid after later, larger calls. */
 int apus_cuda_moe_block_dev(ApusCudaLayer *layer, const uint16_t *d_ln2,
                             uint16_t *d_out, size_t T,
                             const ApusCudaMoeTrace *d_tr, void *stream);
-/* Grow the workspace arena for blocks of up to T tokens of this shape. */
+/* Grow the workspace arena for blocks of up to T tokens of this shape (and
+ * allocate the one-kernel path's scratch for it). */
 int apus_cuda_reserve(const ApusCudaMoeCfg *c, size_t T);
 /* Kernels one apus_cuda_moe_block_dev call launched last time (for the
  * benchmark's launch count). */
@@ -230,6 +255,16 @@ int apus_cuda_fused_timeline(unsigned long long *out, int cap);
  * run since enable (256 per token would be the plain exact router), -1 when
  * not enabled.  APUS_CUDA_ROUTER_CERTIFY=0 selects the plain exact router. */
 long apus_cuda_router_exact_chains(void);
+/* Diagnostic for the same router (host pointers, synchronous): the fast
+ * tensor-core logits of every (token, expert) pair, fast [T,E] fp32, summed
+ * over the K slices as the router does, together with the three factors of
+ * the error bound it relies on: |fast - exact chain| <= cbound * xnorm[t] *
+ * wnorm[e] (wnorm [E+1], the last entry the largest).  Tests compare this
+ * with the engine's exact fp32 chain on every pair.  E % 128 == 0,
+ * K % 256 == 0. */
+int apus_cuda_debug_fast_logits(const uint16_t *x, const uint16_t *wg, size_t T,
+                                size_t E, size_t K, float *fast, float *xnorm,
+                                float *wnorm, float *cbound);
 
 /* Device-side status word of the last block call: 0 = ok; nonzero = a
  * bounded wait inside a kernel gave up (the context stays usable). */

@@ -145,6 +145,16 @@ class Restatement(_Base):
     def threads(self):
         return self._fn("threads", [], C.c_int)()
 
+    def synth_fill_host(self, n, seed, layer, tensor_id, sigma, first=0):
+        """The seeded tensor stream of the package (csrc/synth.h), host-only
+        build: same signature as Backend.synth_fill_host, so synth.host_x /
+        host_weights take this object in place of the CUDA binding."""
+        out = np.empty(n, np.uint16)
+        self._fn("synth_fill", [u16p, sz, C.c_uint64, C.c_uint32, C.c_uint32,
+                                C.c_uint64, C.c_double])(
+            _p(out, u16p), n, seed, layer, tensor_id, first, sigma)
+        return out
+
     def gemv(self, w, x):
         w, x = _u16(w), _u16(x)
         O, K = w.shape

@@ -125,9 +125,9 @@ def test_block_skewed_router(gpu, orc, be, synth):
     assert load.max() > 4 * load.mean()
 
 
-@pytest.mark.parametrize("skew", [False, True])
+@pytest.mark.parametrize("T,skew", [(8192, False), (8192, True), (8448, False)])
 def test_block_full_size_rows_match_the_checker(gpu, orc, be, synth,
-                                                qwen_weights, skew):
+                                                qwen_weights, T, skew):
     """Benchmark configuration 3's shape on one GPU: 8192 tokens at the real
     dimensions, uniform and Zipf(1.1)-skewed routing.  Every token's result
     depends on that token alone, so the CPU checker runs on a seeded sample of
@@ -135,13 +135,17 @@ def test_block_full_size_rows_match_the_checker(gpu, orc, be, synth,
     the full-size GPU call; the dispatch of the full batch is checked through
     its defining property."""
     cfg = synth.QWEN_CFG
-    T = 8192
     W = qwen_weights
     x = synth.host_x(be, T, cfg["hidden"], seed=31)
     if skew:
-        W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=31))
+        W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=31, beta=0.27))
     got = gpu.moe_block(cfg, W, x)
     assert gpu.last_block_status() == 0
+    # the router's result for EVERY token (the CPU checker routes the whole
+    # batch in under a second); full rows on a seeded sample
+    ridx, rw = orc.route_batch(x, W["rtr_w"], cfg["top_k"])
+    assert np.array_equal(got["idx"], ridx)
+    assert (got["w"] != rw).mean() <= 0.002
     rows = np.sort(np.random.default_rng(31).choice(T, 96, replace=False))
     exp = orc.moe_block(cfg, W, x[rows])
     check_block({k: got[k][rows] for k in ("idx", "w", "routed", "shared", "out")},

@@ -39,6 +39,30 @@ def test_static_scratch_dispatch_matches_twice_in_a_row(gpu):
     _case(gpu, torch, 3, 8, 256, 3)          # single-block path
 
 
+def test_static_scratch_dispatch_allocates_nothing(gpu):
+    """After one call (which looks up the array's address), further calls leave
+    the device's free memory exactly where it was: the caller whose pool owns
+    the rest of HBM never sees the library take a byte."""
+    import torch
+    T, TK, E = 2000, 8, 256
+    rng = np.random.default_rng(4)
+    idx = torch.from_numpy(rng.integers(0, E, (T, TK)).astype(np.int32)).cuda()
+    counts = torch.empty((E,), dtype=torch.int32, device="cuda")
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device="cuda")
+    perm = torch.empty((T * TK,), dtype=torch.int32, device="cuda")
+    sp = torch.cuda.current_stream().cuda_stream
+    args = (idx.data_ptr(), T, TK, E, counts.data_ptr(), offsets.data_ptr(),
+            perm.data_ptr())
+    gpu.dispatch_dev_static(*args, stream=sp)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        gpu.dispatch_dev_static(*args, stream=sp)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+
+
 def test_static_scratch_dispatch_refuses_oversize(gpu):
     import torch
     T, TK, E = 40000, 8, 1000                # 1250 units * 1000 > 262144
