@@ -62,7 +62,8 @@ SYMBOLS = [
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
     "apus_cuda_layer_refresh", "apus_cuda_layer_upload",
     "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
-    "apus_cuda_last_block_launches", "apus_cuda_last_block_status",
+    "apus_cuda_last_block_launches", "apus_cuda_last_block_path",
+    "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
     "apus_cuda_fused_timeline", "apus_cuda_router_exact_chains",
     "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
@@ -386,6 +387,10 @@ class Backend:
 
     def last_block_launches(self):
         return int(self.lib.apus_cuda_last_block_launches())
+
+    def last_block_path(self):
+        """0 one-kernel, 1 grouped GEMV, 2 one-SM GEMM, 3 two-SM GEMM."""
+        return int(self.lib.apus_cuda_last_block_path())
 
     def last_block_status(self):
         return int(self.lib.apus_cuda_last_block_status())

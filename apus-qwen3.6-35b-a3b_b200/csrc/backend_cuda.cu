@@ -29,6 +29,7 @@
 #include "ep_window.cuh"
 #include "misc_kernels.cuh"
 #include "prefill_gemm.cuh"
+#include "pair_gemm.cuh"
 #include "router.cuh"
 
 using namespace apus;
@@ -102,7 +103,9 @@ struct Ctx {
     bool df_timeline_valid = false;
     size_t df_act_elems = 0, df_sa_elems = 0;
     int last_block_launches = 0;
+    int last_block_path = 0;
     bool hooks_filled = false;
+    size_t ep_rows_hint = 0;     /* rows the next experts_dev call expects (0: its R) */
     /* ordering of calls that arrive on different streams */
     cudaStream_t cur_stream = nullptr, last_stream = nullptr;
     cudaEvent_t last_ev = nullptr;
@@ -205,6 +208,8 @@ static int ctx_init() {
     g_pg_overlap = (int)env_long("APUS_CUDA_GEMM_OVERLAP", 1);
     g_pg_dynamic = (int)env_long("APUS_CUDA_GEMM_DYNAMIC", 3);
     g_pg_direct = (int)env_long("APUS_CUDA_GEMM_DIRECT", 1);
+    g_pp_enable = (int)env_long("APUS_CUDA_PAIR", 1);
+    g_pp_min_rows = (int)env_long("APUS_CUDA_PAIR_MIN_ROWS", 96);
     g_ctx = c;
     return 0;
 }
@@ -1269,8 +1274,10 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
                     "expert-parallel entry points for a partial layer");
     c->last_block_launches = 0;
     c->df_timeline_valid = false;
-    if (fused_supported(c, cfg, T))
+    if (fused_supported(c, cfg, T)) {
+        c->last_block_path = APUS_CUDA_PATH_FUSED;
         return run_fused_decode(c, L, d_ln2, d_out, (int)T, d_tr, st);
+    }
     const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
     BlockBufs b;
     block_layout(cfg, T, nullptr, &b, prefill);
@@ -1295,14 +1302,28 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
         b.d.grp_n = nullptr;
         b.d.n_groups = nullptr;
     }
+    /* many rows per expert: the kernels in which two SMs share a tile */
+    const bool pair = prefill && pair_supported(cfg, c->sm_count, c->smem_optin) &&
+                      (size_t)Ti * TK >= (size_t)g_pp_min_rows * E;
+    c->last_block_path = pair ? APUS_CUDA_PATH_GEMM_2SM
+                              : (prefill ? APUS_CUDA_PATH_GEMM : APUS_CUDA_PATH_GEMV);
     TilePlan plan;
     memset(&plan, 0, sizeof plan);
-    if (prefill) plan = prefill_tile_plan(cfg, Ti, true, Ti * TK, b.tiles);
+    if (prefill && !pair) plan = prefill_tile_plan(cfg, Ti, true, Ti * TK, b.tiles);
     if (launch_dispatch(c, b.idx, Ti * TK, E, b.d, b.unit_hist, st, DispatchKey{0, 1},
-                        prefill ? &plan : nullptr))
+                        prefill && !pair ? &plan : nullptr))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
-    if (prefill) {
+    if (pair) {
+        const int before = c->last_block_launches;
+        g_mark_stream = st;
+        if (run_pair_experts(c->sm_count, c->smem_optin, L->maps, cfg, (int)L->e_begin,
+                             d_ln2, Ti, Ti * TK, TK, true, b.d, b.xg, b.act, b.sa, b.eo,
+                             b.sy, b.tiles, c->d_status, st, &c->last_block_launches,
+                             mark_cb))
+            return fail("%s", prefill_last_error());
+        c->launches += (uint64_t)(c->last_block_launches - before);
+    } else if (prefill) {
         const int before = c->last_block_launches;
         g_mark_stream = st;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cfg,
@@ -1424,6 +1445,9 @@ extern "C" long apus_cuda_router_exact_chains(void) {
 
 extern "C" int apus_cuda_last_block_launches(void) {
     return g_ctx ? g_ctx->last_block_launches : 0;
+}
+extern "C" int apus_cuda_last_block_path(void) {
+    return g_ctx ? g_ctx->last_block_path : -1;
 }
 extern "C" int apus_cuda_last_block_status(void) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
@@ -1621,12 +1645,25 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
         b.d.grp_n = nullptr;
         b.d.n_groups = nullptr;
     }
+    const size_t rows_expected = c->ep_rows_hint ? c->ep_rows_hint : R;
+    c->ep_rows_hint = 0;
+    const bool pair = prefill && pair_supported(L->cfg, c->sm_count, c->smem_optin) &&
+                      rows_expected >= (size_t)g_pp_min_rows * ne;
     TilePlan plan;
     memset(&plan, 0, sizeof plan);
-    if (prefill) plan = prefill_tile_plan(cx, (int)R, false, (int)R, b.tiles);
+    if (prefill && !pair) plan = prefill_tile_plan(cx, (int)R, false, (int)R, b.tiles);
     if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
-                        DispatchKey{(int)L->e_begin, 1}, prefill ? &plan : nullptr))
+                        DispatchKey{(int)L->e_begin, 1}, prefill && !pair ? &plan : nullptr))
         return 1;
+    if (pair) {
+        const int before = c->last_block_launches;
+        if (run_pair_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x, (int)R, (int)R,
+                             1, false, b.d, b.xg, b.act, b.sa, d_y, b.sy, b.tiles,
+                             c->d_status, st, &c->last_block_launches, nullptr))
+            return fail("%s", prefill_last_error());
+        c->launches += (uint64_t)(c->last_block_launches - before);
+        return 0;
+    }
     if (prefill) {
         const int before = c->last_block_launches;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x,
@@ -1851,6 +1888,11 @@ extern "C" int apus_cuda_ep_wait_dev(ApusCudaEpWindow *w, int which, uint32_t ep
 extern "C" int apus_cuda_ep_window_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *L,
                                                void *stream) {
     if (epw_ready(w, "ep_window_experts_dev")) return 1;
+    {
+        /* of the n * cap slots about cap hold a row (what one rank sends in all) */
+        std::lock_guard<std::recursive_mutex> lk(g_mu);
+        if (g_ctx) g_ctx->ep_rows_hint = (size_t)w->l.cap;
+    }
     return apus_cuda_experts_dev(L, (const uint16_t *)(w->base + w->l.rx),
                                  (const int32_t *)(w->base + w->l.re),
                                  (size_t)w->l.n * w->l.cap, w->y, stream);

@@ -1,0 +1,487 @@
+/*
+ * pair_gemm.cuh — the expert products for thousands of tokens: a grouped BF16
+ * GEMM in which TWO SMs work on one tile (tcgen05.mma.cta_group::2).
+ *
+ * Replaces, like prefill_gemm.cuh, the per-expert loop of the CPU engine's
+ * batched body (c/layer.h:599-621) and its shared-expert GEMMs
+ * (c/layer.h:593-596); this is the form for many rows per expert, where the
+ * one-SM kernel is held back by the operand bytes every SM has to pull through
+ * L2 (48 KB per 64-deep k-block for a 128 x 128(x2) tile).
+ *
+ * Orientation: the expert's TOKEN rows are the MMA's M dimension, 256 per pair
+ * of CTAs (128 per CTA, one TMEM lane each), the WEIGHT rows are N = 256, of
+ * which each CTA of the pair loads one half into its own shared memory; the
+ * pair's MMA reads both halves.  Per k-block a CTA pulls 16 KB of tokens and
+ * 16 KB of weights for 128 x 256 outputs: two thirds of the bytes per flop of
+ * the one-SM kernel, and an expert with up to 256 rows reads its weights once.
+ *
+ *   gate_up:  N = 128 gate rows (CTA 0's half) | the 128 matching up rows
+ *             (CTA 1's half), so every thread finds g and u of the same
+ *             (token, i) in its own TMEM lane:
+ *             act = rnd(rnd(silu(rnd g)) * rnd u)   routed  (c/moe.h:387-395)
+ *             sa  = rnd(silu(rnd g) * rnd u)        shared  (c/moe.h:438-445)
+ *   down:     N = 256 output columns h0..h0+255 (128 per CTA);
+ *             y = rnd(D) stored at row perm[r] of the flat assignment-ordered
+ *             buffer (the engine's eo, c/layer.h:618) or row t of sy.
+ *
+ * A thread owns one token row, so its outputs are contiguous: 16-byte stores.
+ *
+ * One persistent cluster of two CTAs per SM pair, 10 warps per CTA: warp 0
+ * issues TMA loads (no multicast: each CTA loads its own operands; the
+ * completion bytes of both CTAs are counted on the leader's barrier), warp 1 of
+ * the leader CTA issues the MMAs and both warps 1 own their CTA's 512 TMEM
+ * columns (two accumulator stages), warps 2-9 drain the accumulators.  Stage
+ * and accumulator hand-backs from the MMA to both CTAs are tcgen05.commit with
+ * a cluster mask.  Every wait is bounded; a wait that runs out raises the
+ * CTA's abort flag and records a status code, and every role falls through to
+ * the common exit (cluster barrier, TMEM release).
+ */
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "dispatch.cuh"
+#include "prefill_gemm.cuh"
+
+namespace apus {
+
+constexpr int PP_BM = 128;          /* token rows per CTA (256 per pair) */
+constexpr int PP_BN = 256;          /* weight rows per tile (128 per CTA) */
+constexpr int PP_BK = 64;
+constexpr int PP_HALF_BYTES = 128 * PP_BK * 2;       /* 16 KB */
+constexpr int PP_STAGE_BYTES = 2 * PP_HALF_BYTES;    /* tokens | weights */
+constexpr int PP_STAGES = 6;
+constexpr int PP_EPI_WARPS = 8;
+constexpr int PP_THREADS = 64 + PP_EPI_WARPS * 32;
+constexpr int PP_TMEM_COLS = 512;
+constexpr uint32_t PP_PEER_MASK = 0xFEFFFFFFu;      /* cluster address of CTA 0's copy */
+
+inline int pp_smem_bytes() { return PP_STAGES * PP_STAGE_BYTES + 1024 + 256; }
+
+struct PairParams {
+    const int4 *tiles;       /* {expert or E, n-tile, first row, rows <= 256} */
+    const int *n_tiles;
+    int K;
+    int E, e_begin;
+    int rows_per_expert;     /* weight rows per expert in the routed tensor */
+    int up_off;              /* gate_up: offset of the up rows (I) */
+    uint16_t *out_routed, *out_shared;
+    int ld_routed, ld_shared;
+    const int32_t *perm;     /* down: sorted position -> flat assignment */
+    int *status;
+};
+
+__device__ __forceinline__ uint32_t pp_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void pp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+/* TMA tile load into this CTA's shared memory; completion bytes counted on the
+ * LEADER CTA's barrier at the same offset (no multicast) */
+__device__ __forceinline__ void pp_tma_load(void *dst, const CUtensorMap *map, int x, int y,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::"
+        "complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PP_PEER_MASK), "r"(x),
+        "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void pp_tmem_alloc(uint32_t *holder, uint32_t cols) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+            smem_u32(holder)),
+        "r"(cols)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void pp_tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void pp_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+/* arrive, once every MMA issued so far is done, on the barrier at this offset
+ * in BOTH CTAs of the pair */
+__device__ __forceinline__ void pp_commit_both(uint64_t *bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster."
+        "multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+        "h"(mask)
+        : "memory");
+}
+/* arrive on the leader CTA's copy of a barrier */
+__device__ __forceinline__ void pp_arrive_leader(uint64_t *bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t"
+        "}\n" ::"r"(smem_u32(bar))
+        : "memory");
+}
+/* kind::f16 instruction descriptor: D fp32, A/B BF16, both K-major, M x N */
+__device__ __forceinline__ uint32_t pp_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void st16(uint16_t *p, uint32_t a, uint32_t b, uint32_t c,
+                                     uint32_t d) {
+    *reinterpret_cast<uint4 *>(p) = make_uint4(a, b, c, d);
+}
+
+/* MODE 0: gate_up + SwiGLU;  MODE 1: down */
+template <int MODE>
+__global__ void __launch_bounds__(PP_THREADS, 1)
+pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (tokens) */
+                 const __grid_constant__ CUtensorMap mapAs,    /* x  | sa */
+                 const __grid_constant__ CUtensorMap mapB,     /* routed weights */
+                 const __grid_constant__ CUtensorMap mapBs,    /* shared g | d */
+                 const __grid_constant__ CUtensorMap mapBs2,   /* shared u */
+                 PairParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int STAGES = PP_STAGES;
+    extern __shared__ unsigned char pp_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(pp_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * PP_STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES;
+    uint64_t *tfull = bars + 2 * STAGES, *tempty = tfull + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tempty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = pp_cta_rank();
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 2 * PP_EPI_WARPS);   /* the epilogue warps of both CTAs */
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == 1) pp_tmem_alloc(tmem_holder, PP_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    pp_cluster_sync();       /* the peer's barriers exist before anything signals them */
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int n_tiles = *p.n_tiles;
+    const int num_kb = p.K / PP_BK;
+
+    if (warp == 0) {
+        /* ---------------- TMA producer (both CTAs) ---------------- */
+        if (lane == 0) {
+            uint32_t kiter = 0;
+            bool alive = true;
+            for (int tile = pair; alive && tile < n_tiles; tile += npairs) {
+                const int4 t = __ldg(&p.tiles[tile]);
+                const bool shared = t.x == p.E;
+                const CUtensorMap *ma = shared ? &mapAs : &mapA;
+                const CUtensorMap *mb;
+                int brow;
+                if (MODE == 0) {
+                    mb = shared ? (rank ? &mapBs2 : &mapBs) : &mapB;
+                    brow = (shared ? 0
+                                   : (t.x - p.e_begin) * p.rows_per_expert +
+                                         (rank ? p.up_off : 0)) +
+                           t.y * 128;
+                } else {
+                    mb = shared ? &mapBs : &mapB;
+                    brow = (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) +
+                           t.y * PP_BN + (int)rank * 128;
+                }
+                const int arow = t.z + (int)rank * PP_BM;
+                /* a CTA whose half of the tile holds no row skips the token load */
+                const bool mine = (int)rank * PP_BM < t.w;
+                const uint32_t bytes_all =
+                    (uint32_t)(2 * PP_HALF_BYTES + (t.w > PP_BM ? 2 : 1) * PP_HALF_BYTES);
+                for (int kb = 0; alive && kb < num_kb; kb++, kiter++) {
+                    const int s = kiter % STAGES;
+                    const uint32_t ph = (kiter / STAGES) & 1u;
+                    if (!pg_wait(&empty[s], ph ^ 1u, abort_flag, p.status, ST_MBAR_TIMEOUT)) {
+                        alive = false;
+                        break;
+                    }
+                    unsigned char *st = smem + (size_t)s * PP_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full[s], bytes_all);
+                    if (mine) pp_tma_load(st, ma, kb * PP_BK, arow, &full[s]);
+                    pp_tma_load(st + PP_HALF_BYTES, mb, kb * PP_BK, brow, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer (leader CTA only) ---------------- */
+        if (rank == 0 && lane == 0) {
+            uint32_t kiter = 0;
+            bool alive = true;
+            const uint32_t idesc = pp_idesc(2 * PP_BM, PP_BN);
+            int it = 0;
+            for (int tile = pair; alive && tile < n_tiles; tile += npairs, it++) {
+                const int acc = it & 1;
+                const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+                if (!pg_wait(&tempty[acc], aph ^ 1u, abort_flag, p.status, ST_TMEM_TIMEOUT))
+                    break;
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + (uint32_t)acc * 256u;
+                for (int kb = 0; kb < num_kb; kb++, kiter++) {
+                    const int s = kiter % STAGES;
+                    const uint32_t ph = (kiter / STAGES) & 1u;
+                    if (!pg_wait(&full[s], ph, abort_flag, p.status, ST_MBAR_TIMEOUT)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * PP_STAGE_BYTES);
+                    const uint64_t da = umma_smem_desc(sa);
+                    const uint64_t db = umma_smem_desc(sa + PP_HALF_BYTES);
+#pragma unroll
+                    for (int k = 0; k < PP_BK / 16; k++)
+                        pp_mma(d0, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+                    pp_commit_both(&empty[s]);       /* frees the stage in both CTAs */
+                }
+                if (alive) pp_commit_both(&tfull[acc]);
+            }
+        }
+    } else {
+        /* ---------------- epilogue (warps 2..9, both CTAs) ---------------- */
+        const int q = warp & 3;                 /* TMEM lane quarter of this warp */
+        const int half = (warp - 2) >> 2;       /* which columns of the tile */
+        const int r = (int)rank * PP_BM + q * 32 + lane;    /* row inside the pair's tile */
+        int it = 0;
+        for (int tile = pair; tile < n_tiles; tile += npairs, it++) {
+            const int4 t = __ldg(&p.tiles[tile]);
+            const bool shared = t.x == p.E;
+            const int acc = it & 1;
+            const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+            const bool valid = r < t.w;
+            int orow = t.z + r;                 /* gate_up, and the shared expert */
+            if (MODE == 1 && !shared && valid) orow = __ldg(&p.perm[t.z + r]);
+            if (!pg_wait(&tfull[acc], aph, abort_flag, p.status, ST_TMEM_TIMEOUT)) break;
+            tc_fence_after();
+            const uint32_t taddr =
+                tmem_base + (uint32_t)acc * 256u + ((uint32_t)(q * 32) << 16);
+            uint16_t *out = shared ? p.out_shared : p.out_routed;
+            const int ld = shared ? p.ld_shared : p.ld_routed;
+            /* a warp whose rows are all past the tile's end has nothing to read */
+            const bool any = (int)rank * PP_BM + q * 32 < t.w;
+            if (MODE == 0) {
+                for (int c0 = half * 64; any && c0 < half * 64 + 64; c0 += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + (uint32_t)c0, g);
+                    tmem_ld32(taddr + 128u + (uint32_t)c0, u);
+                    tmem_ld_wait();
+                    if (valid) {
+                        uint16_t *dst = out + (size_t)orow * ld + t.y * 128 + c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int h = 0; h < 4; h++) {
+                                const float g0 = bf16_round(__uint_as_float(g[j + 2 * h]));
+                                const float u0 = bf16_round(__uint_as_float(u[j + 2 * h]));
+                                const float g1 = bf16_round(__uint_as_float(g[j + 2 * h + 1]));
+                                const float u1 = bf16_round(__uint_as_float(u[j + 2 * h + 1]));
+                                const uint16_t a0 = shared ? silu_mul_bits(g0, u0)
+                                                           : silu_act_bits(g0, u0);
+                                const uint16_t a1 = shared ? silu_mul_bits(g1, u1)
+                                                           : silu_act_bits(g1, u1);
+                                pk[h] = (uint32_t)a0 | ((uint32_t)a1 << 16);
+                            }
+                            st16(dst + j, pk[0], pk[1], pk[2], pk[3]);
+                        }
+                    }
+                }
+            } else {
+                for (int c0 = half * 128; any && c0 < half * 128 + 128; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (valid) {
+                        uint16_t *dst = out + (size_t)orow * ld + t.y * PP_BN + c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            st16(dst + j,
+                                 pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
+                                 pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
+                                 pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
+                                 pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) pp_arrive_leader(&tempty[acc]);
+        }
+    }
+    /* neither CTA may leave (or free its tensor memory) while the other can
+     * still signal its barriers or have MMAs in flight into its TMEM */
+    tc_fence_before();
+    __syncthreads();
+    pp_cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        pp_tmem_dealloc(tmem_base, PP_TMEM_COLS);
+    }
+}
+
+/* ---- host side ---------------------------------------------------------------- */
+inline int g_pp_enable = 1;          /* APUS_CUDA_PAIR=0: never take this path */
+inline int g_pp_min_rows = 96;       /* mean rows per resident expert from which it is taken */
+
+inline bool pair_supported(const ApusCudaMoeCfg &c, int sm_count, int smem_optin) {
+    return g_pp_enable && prefill_supported(c) && c.hidden % PP_BN == 0 &&
+           sm_count >= 2 && pp_smem_bytes() <= smem_optin;
+}
+
+/* tile shapes of this path for the common tile-list builder */
+inline TilePlan pair_tile_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, int A,
+                               void *tiles_ws) {
+    TilePlan p = prefill_tile_plan(c, T, do_shared, A, tiles_ws);
+    p.m_gu = (int)c.moe_inter / 128;
+    p.m_gu_sh = (int)c.shared_inter / 128;
+    p.m_dn = (int)c.hidden / PP_BN;
+    p.bn_gu = p.bn_dn = p.bn_sh_gu = p.bn_sh_dn = 2 * PP_BM;
+    return p;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pair(void (*kernel)(KArgs...), int grid, size_t smem,
+                               cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(PP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_apus_use_pdl ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+/* Routed + shared experts through the two-SM kernels.  Same contract as
+ * run_prefill_experts; the tile lists come from build_tiles_kernel with
+ * pair_tile_plan's shapes. */
+inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
+                            const ApusCudaMoeCfg &c, int e_begin, const uint16_t *x, int T,
+                            int A, int TK, bool do_shared, const DispatchOut &d,
+                            uint16_t *xg, uint16_t *act, uint16_t *sa, uint16_t *eo,
+                            uint16_t *sy, void *tiles_ws, int *status, cudaStream_t st,
+                            int *launches, void (*mark)(int stage)) {
+    const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
+              E = (int)c.experts;
+    if (!maps) {
+        snprintf(g_prefill_err, sizeof g_prefill_err, "tensor maps missing");
+        return 1;
+    }
+    const int smem = pp_smem_bytes();
+    if (smem > smem_optin || Is != I) {
+        snprintf(g_prefill_err, sizeof g_prefill_err,
+                 "two-SM grouped GEMM: %d B shared memory, shared_inter == moe_inter", smem);
+        return 1;
+    }
+    TilePlan plan = pair_tile_plan(c, T, do_shared, A, tiles_ws);
+    launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, (const int32_t *)d.counts,
+             (const int32_t *)d.offsets, E, plan);
+    (*launches)++;
+    const TileLists tl = plan.tl;
+    if (A > 0) {
+        long total = (long)A * (H / 8);
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > sm_count * 16) blocks = sm_count * 16;
+        launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H, TK, xg,
+                 (const int32_t *)(d.offsets + E));
+        (*launches)++;
+    }
+    if (mark) mark(APUS_CUDA_STAGE_GATHER);
+    CUtensorMap m_xg, m_x, m_act, m_sa;
+    int bad = 0;
+    bad |= encode_2d(maps->encode, &m_xg, A > 0 ? (const void *)xg : (const void *)x,
+                     (size_t)(A > 0 ? A : 1), H, PP_BM);
+    bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H, PP_BM);
+    bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
+                     (size_t)(A > 0 ? A : 1), I, PP_BM);
+    bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
+                     (size_t)(do_shared && T > 0 ? T : 1), Is, PP_BM);
+    if (bad) return 1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(pair_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem);
+        cudaFuncSetAttribute(pair_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem);
+        attr_set = true;
+    }
+    const int grid = sm_count & ~1;
+    PairParams p1;
+    memset(&p1, 0, sizeof p1);
+    p1.tiles = tl.gu;
+    p1.n_tiles = tl.n_gu;
+    p1.K = H;
+    p1.E = E;
+    p1.e_begin = e_begin;
+    p1.rows_per_expert = 2 * I;
+    p1.up_off = I;
+    p1.out_routed = act;
+    p1.out_shared = sa;
+    p1.ld_routed = I;
+    p1.ld_shared = Is;
+    p1.perm = d.perm;
+    p1.status = status;
+    launch_pair(pair_gemm_kernel<0>, grid, (size_t)smem, st, m_xg, m_x, maps->w_gu, maps->sh_g,
+                maps->sh_u, p1);
+    (*launches)++;
+    if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
+    PairParams p2 = p1;
+    p2.tiles = tl.dn;
+    p2.n_tiles = tl.n_dn;
+    p2.K = I;
+    p2.rows_per_expert = H;
+    p2.up_off = 0;
+    p2.out_routed = eo;
+    p2.out_shared = sy;
+    p2.ld_routed = H;
+    p2.ld_shared = H;
+    launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem, st, m_act, m_sa, maps->w_d, maps->sh_d,
+                maps->sh_d, p2);
+    (*launches)++;
+    if (mark) mark(APUS_CUDA_STAGE_DOWN);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(g_prefill_err, sizeof g_prefill_err, "two-SM grouped GEMM launch: %s",
+                 cudaGetErrorString(e));
+        return 1;
+    }
+    return 0;
+}
+
+}  // namespace apus

@@ -202,7 +202,11 @@ int apus_cuda_layer_upload(ApusCudaLayer *layer, int which, const uint16_t *src,
  * tcgen05 grouped GEMMs (gate/up, down) -> combine when the shape fits the MMA
  * tiles (H, I, Is multiples of 128, Is == I), else the grouped-GEMV kernels.
  * APUS_CUDA_DECODE_MAX_T (default 4) is the largest T that still takes the
- * grouped-GEMV kernels on a shape the GEMM supports.
+ * grouped-GEMV kernels on a shape the GEMM supports.  From a mean of
+ * APUS_CUDA_PAIR_MIN_ROWS (default 96) rows per expert on, and H a multiple of
+ * 256, the two GEMMs run with a pair of SMs per tile (cta_group::2: tokens
+ * 256 per pair, each SM loading half of the weight tile); APUS_CUDA_PAIR=0
+ * keeps the one-SM kernels.
  *
  * Shared state.  Every device-pointer entry point of this header (the block,
  * the expert-parallel steps, route_dev, dispatch_dev) works in ONE per-process
@@ -227,6 +231,14 @@ int apus_cuda_reserve(const ApusCudaMoeCfg *c, size_t T);
 /* Kernels one apus_cuda_moe_block_dev call launched last time (for the
  * benchmark's launch count). */
 int apus_cuda_last_block_launches(void);
+/* Which kernels the last apus_cuda_moe_block[_dev] call took (-1: none yet). */
+enum {
+    APUS_CUDA_PATH_FUSED = 0,      /* one cooperative kernel (a handful of tokens) */
+    APUS_CUDA_PATH_GEMV = 1,       /* grouped-GEMV kernels (shapes the MMA tiles do not fit) */
+    APUS_CUDA_PATH_GEMM = 2,       /* tcgen05 grouped GEMM, one SM per tile */
+    APUS_CUDA_PATH_GEMM_2SM = 3    /* tcgen05 grouped GEMM, a pair of SMs per tile */
+};
+int apus_cuda_last_block_path(void);
 /* Per-stage device times of the block (benchmarks): with timing enabled,
  * apus_cuda_moe_block_dev brackets each stage with CUDA events on the stream
  * it launches on; apus_cuda_last_stage_ms waits for the last call's events

@@ -246,3 +246,32 @@ def test_block_few_tokens_without_gathered_rows(be, orc, synth, qwen_weights, T,
     for k in ("idx", "w", "routed", "shared", "out"):
         assert np.array_equal(outs["1"][k], outs["0"][k]), k
     check_block(outs["1"], orc.moe_block(cfg, qwen_weights, x), f"direct T={T}")
+
+
+@pytest.mark.parametrize("T,E,TK,skew", [(300, 8, 4, False), (257, 8, 4, False),
+                                         (1000, 8, 4, False), (1500, 16, 8, True),
+                                         (129, 4, 4, False)])
+def test_block_two_sm_gemm_path(be, orc, synth, monkeypatch, T, E, TK, skew):
+    """Many rows per expert: the GEMMs in which a pair of SMs shares a tile
+    (tokens as the MMA's M, 256 per pair).  Checked against the CPU checker and,
+    bit for bit, against the one-SM kernels on the same inputs (a row's result
+    must not depend on the tiling)."""
+    cfg = dict(hidden=512, experts=E, moe_inter=128, shared_inter=128, top_k=TK)
+    W = synth.host_weights(be, cfg, seed=60 + T, sigma=0.05)
+    x = synth.host_x(be, T, cfg["hidden"], seed=60 + T)
+    if skew:
+        W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=3, beta=0.6))
+    exp = orc.moe_block(cfg, W, x)
+    res = {}
+    for pair in ("1", "0"):
+        monkeypatch.setenv("APUS_CUDA_PAIR", pair)
+        be.enable()
+        try:
+            res[pair] = be.moe_block(cfg, W, x)
+            assert be.last_block_status() == 0
+            assert be.last_block_path() == (3 if pair == "1" else 2)
+        finally:
+            be.disable()
+        check_block(res[pair], exp, f"pair={pair} T={T}")
+    for k in ("idx", "w", "shared", "routed", "out"):
+        assert np.array_equal(res["1"][k], res["0"][k]), k
