@@ -210,6 +210,8 @@ static int ctx_init() {
     g_pg_direct = (int)env_long("APUS_CUDA_GEMM_DIRECT", 1);
     g_pp_enable = (int)env_long("APUS_CUDA_PAIR", 1);
     g_pp_min_rows = (int)env_long("APUS_CUDA_PAIR_MIN_ROWS", 96);
+    g_pp_prefetch = (int)env_long("APUS_CUDA_PAIR_PREFETCH", 0);
+    g_pp_gather = (int)env_long("APUS_CUDA_PAIR_GATHER", 0);
     g_ctx = c;
     return 0;
 }

@@ -26,6 +26,13 @@
  *
  * A thread owns one token row, so its outputs are contiguous: 16-byte stores.
  *
+ * The kernel is bound by the bytes an SM can take in from L2 (about 38 bytes
+ * per clock measured), so a tile's rows are split evenly between the two CTAs
+ * and each CTA fetches a token box just tall enough for its share (32, 64, 96
+ * or 128 rows): an expert with 100 rows costs each CTA 16 KB of weights and
+ * 8 KB of tokens per k-block instead of 32 KB.  (The MMA always spans 256
+ * rows; rows past a CTA's share hold stale data whose results are not stored.)
+ *
  * One persistent cluster of two CTAs per SM pair, 10 warps per CTA: warp 0
  * issues TMA loads (no multicast: each CTA loads its own operands; the
  * completion bytes of both CTAs are counted on the leader's barrier), warp 1 of
@@ -59,6 +66,16 @@ constexpr uint32_t PP_PEER_MASK = 0xFEFFFFFFu;      /* cluster address of CTA 0'
 
 inline int pp_smem_bytes() { return PP_STAGES * PP_STAGE_BYTES + 1024 + 256; }
 
+/* token-side tensor maps: the same tensor with boxes of 32, 64, 96, 128 rows */
+struct PairMaps {
+    CUtensorMap m[4];
+};
+/* rows of a c-row tile that CTA `rank` owns: the first ceil(c/2) or the rest */
+__host__ __device__ __forceinline__ int pp_rows_of(int c, int rank) {
+    const int n0 = (c + 1) >> 1;
+    return rank ? c - n0 : n0;
+}
+
 struct PairParams {
     const int4 *tiles;       /* {expert or E, n-tile, first row, rows <= 256} */
     const int *n_tiles;
@@ -70,6 +87,11 @@ struct PairParams {
     int ld_routed, ld_shared;
     const int32_t *perm;     /* down: sorted position -> flat assignment */
     int *status;
+    int prefetch;            /* bit 0: next tile's weights to L2; bit 1: its tokens too */
+    /* gate_up: token rows of the routed tiles fetched straight from the block
+     * input by index (row perm[p] / gather_tk), four rows per TMA instruction,
+     * instead of from a permuted copy */
+    int gather_tk;           /* 0: off */
 };
 
 __device__ __forceinline__ uint32_t pp_cta_rank() {
@@ -91,6 +113,27 @@ __device__ __forceinline__ void pp_tma_load(void *dst, const CUtensorMap *map, i
         "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PP_PEER_MASK), "r"(x),
         "r"(y)
         : "memory");
+}
+/* Four arbitrary rows of a 2-D tensor (64 columns of each) into four consecutive
+ * 128-byte rows of this CTA's shared memory; the tensor map's box is 64 x 1.
+ * Completion bytes go to the leader CTA's barrier, as for pp_tma_load. */
+__device__ __forceinline__ void pp_tma_gather4(void *dst, const CUtensorMap *map, int x,
+                                               int r0, int r1, int r2, int r3,
+                                               uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::"
+        "complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PP_PEER_MASK), "r"(x),
+        "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+        : "memory");
+}
+/* bring a tile of a tensor into L2 ahead of its use (no shared memory, no barrier) */
+__device__ __forceinline__ void pp_prefetch_l2(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y)
+                 : "memory");
 }
 __device__ __forceinline__ void pp_tmem_alloc(uint32_t *holder, uint32_t cols) {
     asm volatile(
@@ -149,11 +192,12 @@ __device__ __forceinline__ void st16(uint16_t *p, uint32_t a, uint32_t b, uint32
 /* MODE 0: gate_up + SwiGLU;  MODE 1: down */
 template <int MODE>
 __global__ void __launch_bounds__(PP_THREADS, 1)
-pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (tokens) */
-                 const __grid_constant__ CUtensorMap mapAs,    /* x  | sa */
+pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (tokens) */
+                 const __grid_constant__ PairMaps mapAs,       /* x  | sa */
                  const __grid_constant__ CUtensorMap mapB,     /* routed weights */
                  const __grid_constant__ CUtensorMap mapBs,    /* shared g | d */
                  const __grid_constant__ CUtensorMap mapBs2,   /* shared u */
+                 const __grid_constant__ CUtensorMap mapG,     /* block input, 64 x 1 boxes */
                  PairParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int STAGES = PP_STAGES;
@@ -193,44 +237,90 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (to
     const int num_kb = p.K / PP_BK;
 
     if (warp == 0) {
-        /* ---------------- TMA producer (both CTAs) ---------------- */
-        if (lane == 0) {
-            uint32_t kiter = 0;
-            bool alive = true;
-            for (int tile = pair; alive && tile < n_tiles; tile += npairs) {
-                const int4 t = __ldg(&p.tiles[tile]);
-                const bool shared = t.x == p.E;
-                const CUtensorMap *ma = shared ? &mapAs : &mapA;
-                const CUtensorMap *mb;
-                int brow;
-                if (MODE == 0) {
-                    mb = shared ? (rank ? &mapBs2 : &mapBs) : &mapB;
-                    brow = (shared ? 0
+        /* ---------------- TMA producer (both CTAs; the whole warp when the
+         *                  token rows are gathered by index) ---------------- */
+        uint32_t kiter = 0;
+        bool alive = true;
+        /* operand coordinates of a tile for this CTA */
+        struct Ops {
+            const CUtensorMap *ma, *mb;
+            int arow, brow, n_mine, n0, n1;
+            bool mine, shared;
+        };
+        auto ops_of = [&](const int4 t) -> Ops {
+            Ops o;
+            o.shared = t.x == p.E;
+            /* this CTA's share of the tile's rows and the box that covers it */
+            o.n0 = pp_rows_of(t.w, 0);
+            o.n1 = pp_rows_of(t.w, 1);
+            o.n_mine = rank ? o.n1 : o.n0;
+            const int hb_mine = (o.n_mine + 31) >> 5;
+            o.ma = o.shared ? &mapAs.m[hb_mine ? hb_mine - 1 : 0]
+                            : &mapA.m[hb_mine ? hb_mine - 1 : 0];
+            if (MODE == 0) {
+                o.mb = o.shared ? (rank ? &mapBs2 : &mapBs) : &mapB;
+                o.brow = (o.shared ? 0
                                    : (t.x - p.e_begin) * p.rows_per_expert +
                                          (rank ? p.up_off : 0)) +
-                           t.y * 128;
-                } else {
-                    mb = shared ? &mapBs : &mapB;
-                    brow = (shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) +
-                           t.y * PP_BN + (int)rank * 128;
+                         t.y * 128;
+            } else {
+                o.mb = o.shared ? &mapBs : &mapB;
+                o.brow = (o.shared ? 0 : (t.x - p.e_begin) * p.rows_per_expert) +
+                         t.y * PP_BN + (int)rank * 128;
+            }
+            o.arow = t.z + (rank ? o.n0 : 0);
+            /* a CTA without a row of the tile skips the token load */
+            o.mine = o.n_mine > 0;
+            return o;
+        };
+        for (int tile = pair; alive && tile < n_tiles; tile += npairs) {
+            const Ops o = ops_of(__ldg(&p.tiles[tile]));
+            const bool gath = MODE == 0 && p.gather_tk > 0 && !o.shared;
+            /* lane l fetches rows 4l .. 4l+3 of this CTA's share */
+            int g4[4] = {0, 0, 0, 0};
+            const int ng_mine = (o.n_mine + 3) >> 2;
+            if (gath && lane < ng_mine) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int rr = 4 * lane + j;
+                    if (rr < o.n_mine) g4[j] = __ldg(&p.perm[o.arow + rr]) / p.gather_tk;
                 }
-                const int arow = t.z + (int)rank * PP_BM;
-                /* a CTA whose half of the tile holds no row skips the token load */
-                const bool mine = (int)rank * PP_BM < t.w;
-                const uint32_t bytes_all =
-                    (uint32_t)(2 * PP_HALF_BYTES + (t.w > PP_BM ? 2 : 1) * PP_HALF_BYTES);
-                for (int kb = 0; alive && kb < num_kb; kb++, kiter++) {
-                    const int s = kiter % STAGES;
-                    const uint32_t ph = (kiter / STAGES) & 1u;
-                    if (!pg_wait(&empty[s], ph ^ 1u, abort_flag, p.status, ST_MBAR_TIMEOUT)) {
-                        alive = false;
-                        break;
-                    }
-                    unsigned char *st = smem + (size_t)s * PP_STAGE_BYTES;
+            }
+            const uint32_t bytes_all =
+                (uint32_t)(2 * PP_HALF_BYTES) +
+                (gath ? (uint32_t)(((o.n0 + 3) >> 2) + ((o.n1 + 3) >> 2)) * 4u * PP_BK * 2u
+                      : (uint32_t)(((o.n0 + 31) >> 5) + ((o.n1 + 31) >> 5)) * 32u * PP_BK * 2u);
+            /* The operands of the NEXT tile can be asked into L2 a tile time
+             * ahead (measured: no gain, the extra requests cost more than the
+             * DRAM latency they hide; off by default). */
+            if (p.prefetch && lane == 0 && tile + npairs < n_tiles) {
+                const Ops nx = ops_of(__ldg(&p.tiles[tile + npairs]));
+                for (int kb = 0; kb < num_kb; kb++) {
+                    pp_prefetch_l2(nx.mb, kb * PP_BK, nx.brow);
+                    if (nx.mine && (p.prefetch & 2)) pp_prefetch_l2(nx.ma, kb * PP_BK, nx.arow);
+                }
+            }
+            for (int kb = 0; alive && kb < num_kb; kb++, kiter++) {
+                const int s = kiter % STAGES;
+                const uint32_t ph = (kiter / STAGES) & 1u;
+                int ok = 1;
+                if (lane == 0)
+                    ok = pg_wait(&empty[s], ph ^ 1u, abort_flag, p.status, ST_MBAR_TIMEOUT) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    alive = false;
+                    break;
+                }
+                unsigned char *st = smem + (size_t)s * PP_STAGE_BYTES;
+                if (lane == 0) {
                     if (rank == 0) mbar_expect_tx(&full[s], bytes_all);
-                    if (mine) pp_tma_load(st, ma, kb * PP_BK, arow, &full[s]);
-                    pp_tma_load(st + PP_HALF_BYTES, mb, kb * PP_BK, brow, &full[s]);
+                    if (!gath && o.mine) pp_tma_load(st, o.ma, kb * PP_BK, o.arow, &full[s]);
+                    pp_tma_load(st + PP_HALF_BYTES, o.mb, kb * PP_BK, o.brow, &full[s]);
                 }
+                if (gath && lane < ng_mine)
+                    pp_tma_gather4(st + (size_t)lane * 4 * PP_BK * 2, &mapG, kb * PP_BK, g4[0],
+                                   g4[1], g4[2], g4[3], &full[s]);
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
@@ -270,14 +360,16 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (to
         /* ---------------- epilogue (warps 2..9, both CTAs) ---------------- */
         const int q = warp & 3;                 /* TMEM lane quarter of this warp */
         const int half = (warp - 2) >> 2;       /* which columns of the tile */
-        const int r = (int)rank * PP_BM + q * 32 + lane;    /* row inside the pair's tile */
+        const int rl = q * 32 + lane;           /* this thread's row among the CTA's rows */
         int it = 0;
         for (int tile = pair; tile < n_tiles; tile += npairs, it++) {
             const int4 t = __ldg(&p.tiles[tile]);
             const bool shared = t.x == p.E;
             const int acc = it & 1;
             const uint32_t aph = (uint32_t)(it >> 1) & 1u;
-            const bool valid = r < t.w;
+            const int n_mine = pp_rows_of(t.w, (int)rank);
+            const int r = (rank ? pp_rows_of(t.w, 0) : 0) + rl;   /* row inside the tile */
+            const bool valid = rl < n_mine;
             int orow = t.z + r;                 /* gate_up, and the shared expert */
             if (MODE == 1 && !shared && valid) orow = __ldg(&p.perm[t.z + r]);
             if (!pg_wait(&tfull[acc], aph, abort_flag, p.status, ST_TMEM_TIMEOUT)) break;
@@ -287,7 +379,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (to
             uint16_t *out = shared ? p.out_shared : p.out_routed;
             const int ld = shared ? p.ld_shared : p.ld_routed;
             /* a warp whose rows are all past the tile's end has nothing to read */
-            const bool any = (int)rank * PP_BM + q * 32 < t.w;
+            const bool any = q * 32 < n_mine;
             if (MODE == 0) {
                 for (int c0 = half * 64; any && c0 < half * 64 + 64; c0 += 32) {
                     uint32_t g[32], u[32];
@@ -351,6 +443,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* xg | act   (to
 /* ---- host side ---------------------------------------------------------------- */
 inline int g_pp_enable = 1;          /* APUS_CUDA_PAIR=0: never take this path */
 inline int g_pp_min_rows = 96;       /* mean rows per resident expert from which it is taken */
+inline int g_pp_gather = 0;          /* APUS_CUDA_PAIR_GATHER=1: rows by TMA gather4 instead of a permuted copy
+                                      * (measured 2.4x slower: 32 four-row requests per k-block) */
+inline int g_pp_prefetch = 0;        /* APUS_CUDA_PAIR_PREFETCH: see PairParams::prefetch */
 
 inline bool pair_supported(const ApusCudaMoeCfg &c, int sm_count, int smem_optin) {
     return g_pp_enable && prefill_supported(c) && c.hidden % PP_BN == 0 &&
@@ -414,7 +509,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
              (const int32_t *)d.offsets, E, plan);
     (*launches)++;
     const TileLists tl = plan.tl;
-    if (A > 0) {
+    const bool gather = g_pp_gather != 0;
+    if (A > 0 && !gather) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
@@ -423,15 +519,22 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         (*launches)++;
     }
     if (mark) mark(APUS_CUDA_STAGE_GATHER);
-    CUtensorMap m_xg, m_x, m_act, m_sa;
-    int bad = 0;
-    bad |= encode_2d(maps->encode, &m_xg, A > 0 ? (const void *)xg : (const void *)x,
-                     (size_t)(A > 0 ? A : 1), H, PP_BM);
-    bad |= encode_2d(maps->encode, &m_x, x, (size_t)(T > 0 ? T : 1), H, PP_BM);
-    bad |= encode_2d(maps->encode, &m_act, A > 0 ? (const void *)act : (const void *)sa,
-                     (size_t)(A > 0 ? A : 1), I, PP_BM);
-    bad |= encode_2d(maps->encode, &m_sa, do_shared ? (const void *)sa : (const void *)x,
-                     (size_t)(do_shared && T > 0 ? T : 1), Is, PP_BM);
+    PairMaps m_xg, m_x, m_act, m_sa;
+    CUtensorMap m_g;
+    int bad = encode_2d(maps->encode, &m_g, x, (size_t)(T > 0 ? T : 1), H, 1);
+    for (int h = 0; h < 4; h++) {
+        const int box = 32 * (h + 1);
+        bad |= encode_2d(maps->encode, &m_xg.m[h],
+                         A > 0 && !gather ? (const void *)xg : (const void *)x,
+                         (size_t)(A > 0 && !gather ? A : (T > 0 ? T : 1)), H, box);
+        bad |= encode_2d(maps->encode, &m_x.m[h], x, (size_t)(T > 0 ? T : 1), H, box);
+        bad |= encode_2d(maps->encode, &m_act.m[h],
+                         A > 0 ? (const void *)act : (const void *)sa, (size_t)(A > 0 ? A : 1),
+                         I, box);
+        bad |= encode_2d(maps->encode, &m_sa.m[h],
+                         do_shared ? (const void *)sa : (const void *)x,
+                         (size_t)(do_shared && T > 0 ? T : 1), Is, box);
+    }
     if (bad) return 1;
     static bool attr_set = false;
     if (!attr_set) {
@@ -457,8 +560,10 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_shared = Is;
     p1.perm = d.perm;
     p1.status = status;
+    p1.prefetch = g_pp_prefetch;
+    p1.gather_tk = gather && A > 0 ? TK : 0;
     launch_pair(pair_gemm_kernel<0>, grid, (size_t)smem, st, m_xg, m_x, maps->w_gu, maps->sh_g,
-                maps->sh_u, p1);
+                maps->sh_u, m_g, p1);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
     PairParams p2 = p1;
@@ -471,8 +576,9 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.out_shared = sy;
     p2.ld_routed = H;
     p2.ld_shared = H;
+    p2.gather_tk = 0;
     launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem, st, m_act, m_sa, maps->w_d, maps->sh_d,
-                maps->sh_d, p2);
+                maps->sh_d, m_g, p2);
     (*launches)++;
     if (mark) mark(APUS_CUDA_STAGE_DOWN);
     cudaError_t e = cudaGetLastError();
