@@ -181,6 +181,9 @@ static int ctx_init() {
     Ctx *c = new Ctx();
     c->device = dev;
     c->sm_count = prop.multiProcessorCount;
+    /* experiments: run the persistent kernels on fewer SMs */
+    if (env_long("APUS_CUDA_SMS", 0) > 0 && env_long("APUS_CUDA_SMS", 0) < c->sm_count)
+        c->sm_count = (int)env_long("APUS_CUDA_SMS", 0);
     c->smem_optin = (int)prop.sharedMemPerBlockOptin;
     CU_OK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     CU_OK(cudaMalloc(&c->d_status, 256));
@@ -209,9 +212,9 @@ static int ctx_init() {
     g_pg_dynamic = (int)env_long("APUS_CUDA_GEMM_DYNAMIC", 3);
     g_pg_direct = (int)env_long("APUS_CUDA_GEMM_DIRECT", 1);
     g_pp_enable = (int)env_long("APUS_CUDA_PAIR", 1);
-    g_pp_min_rows = (int)env_long("APUS_CUDA_PAIR_MIN_ROWS", 96);
-    g_pp_prefetch = (int)env_long("APUS_CUDA_PAIR_PREFETCH", 0);
+    g_pp_min_rows = (int)env_long("APUS_CUDA_PAIR_MIN_ROWS", 192);
     g_pp_gather = (int)env_long("APUS_CUDA_PAIR_GATHER", 0);
+    g_pp_solo_below = (int)env_long("APUS_CUDA_PAIR_SOLO_BELOW", 160);
     g_ctx = c;
     return 0;
 }

@@ -48,6 +48,40 @@ __device__ __forceinline__ uint16_t silu_mul_bits(float g, float u) {
     return bf16_bits(__fmul_rn(__fmul_rn(g, sigmoid_f32(g)), u));
 }
 
+/* ---- the same roundings for the tensor-core epilogues ----------------------
+ * At thousands of tokens the gate/up GEMM is bound by its epilogue's
+ * instruction count, not by the MMAs (37.7 M SwiGLU evaluations per 8192-token
+ * block), so the epilogues narrow with the hardware conversion (cvt.rn: the
+ * same round-to-nearest-even as the integer rule above for every finite value
+ * and infinity; NaN payloads, outside the engine's contract, come out
+ * canonical) two values at a time, and evaluate the sigmoid with ex2.approx /
+ * rcp.approx (about 2 ulp of fp32 each, invisible after the BF16 narrowing in
+ * all but ~1e-4 of the values, where the result moves by one BF16 step). */
+__device__ __forceinline__ uint32_t pack_bf16_rn(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+/* both values narrowed to BF16 and widened again */
+__device__ __forceinline__ void bf16_round2(float &a, float &b) {
+    const uint32_t p = pack_bf16_rn(a, b);
+    a = __uint_as_float(p << 16);
+    b = __uint_as_float(p & 0xffff0000u);
+}
+__device__ __forceinline__ float silu_fast(float g) {
+    return __fmul_rn(g, __fdividef(1.0f, __fadd_rn(1.0f, __expf(-g))));
+}
+/* two routed activations, packed: rnd(rnd(silu(g)) * u)  (g, u already BF16 values) */
+__device__ __forceinline__ uint32_t silu_act_pack2(float g0, float u0, float g1, float u1) {
+    float a0 = silu_fast(g0), a1 = silu_fast(g1);
+    bf16_round2(a0, a1);
+    return pack_bf16_rn(__fmul_rn(a0, u0), __fmul_rn(a1, u1));
+}
+/* two shared activations, packed: rnd(silu(g) * u), single rounding */
+__device__ __forceinline__ uint32_t silu_mul_pack2(float g0, float u0, float g1, float u1) {
+    return pack_bf16_rn(__fmul_rn(silu_fast(g0), u0), __fmul_rn(silu_fast(g1), u1));
+}
+
 /* ---- device status word --------------------------------------------------
  * Kernels never trap or spin without limit.  A wait that runs out records a
  * code here and the kernel returns; the host reads the word after the call. */

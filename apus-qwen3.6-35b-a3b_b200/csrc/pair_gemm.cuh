@@ -87,7 +87,6 @@ struct PairParams {
     int ld_routed, ld_shared;
     const int32_t *perm;     /* down: sorted position -> flat assignment */
     int *status;
-    int prefetch;            /* bit 0: next tile's weights to L2; bit 1: its tokens too */
     /* gate_up: token rows of the routed tiles fetched straight from the block
      * input by index (row perm[p] / gather_tk), four rows per TMA instruction,
      * instead of from a permuted copy */
@@ -127,13 +126,6 @@ __device__ __forceinline__ void pp_tma_gather4(void *dst, const CUtensorMap *map
         "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PP_PEER_MASK), "r"(x),
         "r"(r0), "r"(r1), "r"(r2), "r"(r3)
         : "memory");
-}
-/* bring a tile of a tensor into L2 ahead of its use (no shared memory, no barrier) */
-__device__ __forceinline__ void pp_prefetch_l2(const CUtensorMap *map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
-                     reinterpret_cast<uint64_t>(map)),
-                 "r"(x), "r"(y)
-                 : "memory");
 }
 __device__ __forceinline__ void pp_tmem_alloc(uint32_t *holder, uint32_t cols) {
     asm volatile(
@@ -184,9 +176,13 @@ __device__ __forceinline__ uint32_t pp_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void st16(uint16_t *p, uint32_t a, uint32_t b, uint32_t c,
-                                     uint32_t d) {
-    *reinterpret_cast<uint4 *>(p) = make_uint4(a, b, c, d);
+/* 32 bytes (one whole sector) per store: a thread owns a row, so a warp's store
+ * touches 32 rows whatever its width; half as many, complete sectors */
+__device__ __forceinline__ void st32(uint16_t *p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+                 "r"(v[7])
+                 : "memory");
 }
 
 /* MODE 0: gate_up + SwiGLU;  MODE 1: down */
@@ -290,16 +286,6 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                 (uint32_t)(2 * PP_HALF_BYTES) +
                 (gath ? (uint32_t)(((o.n0 + 3) >> 2) + ((o.n1 + 3) >> 2)) * 4u * PP_BK * 2u
                       : (uint32_t)(((o.n0 + 31) >> 5) + ((o.n1 + 31) >> 5)) * 32u * PP_BK * 2u);
-            /* The operands of the NEXT tile can be asked into L2 a tile time
-             * ahead (measured: no gain, the extra requests cost more than the
-             * DRAM latency they hide; off by default). */
-            if (p.prefetch && lane == 0 && tile + npairs < n_tiles) {
-                const Ops nx = ops_of(__ldg(&p.tiles[tile + npairs]));
-                for (int kb = 0; kb < num_kb; kb++) {
-                    pp_prefetch_l2(nx.mb, kb * PP_BK, nx.brow);
-                    if (nx.mine && (p.prefetch & 2)) pp_prefetch_l2(nx.ma, kb * PP_BK, nx.arow);
-                }
-            }
             for (int kb = 0; alive && kb < num_kb; kb++, kiter++) {
                 const int s = kiter % STAGES;
                 const uint32_t ph = (kiter / STAGES) & 1u;
@@ -389,21 +375,20 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                     if (valid) {
                         uint16_t *dst = out + (size_t)orow * ld + t.y * 128 + c0;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint32_t pk[4];
+                        for (int j = 0; j < 32; j += 16) {
+                            uint32_t pk[8];
 #pragma unroll
-                            for (int h = 0; h < 4; h++) {
-                                const float g0 = bf16_round(__uint_as_float(g[j + 2 * h]));
-                                const float u0 = bf16_round(__uint_as_float(u[j + 2 * h]));
-                                const float g1 = bf16_round(__uint_as_float(g[j + 2 * h + 1]));
-                                const float u1 = bf16_round(__uint_as_float(u[j + 2 * h + 1]));
-                                const uint16_t a0 = shared ? silu_mul_bits(g0, u0)
-                                                           : silu_act_bits(g0, u0);
-                                const uint16_t a1 = shared ? silu_mul_bits(g1, u1)
-                                                           : silu_act_bits(g1, u1);
-                                pk[h] = (uint32_t)a0 | ((uint32_t)a1 << 16);
+                            for (int h = 0; h < 8; h++) {
+                                float g0 = __uint_as_float(g[j + 2 * h]),
+                                      g1 = __uint_as_float(g[j + 2 * h + 1]),
+                                      u0 = __uint_as_float(u[j + 2 * h]),
+                                      u1 = __uint_as_float(u[j + 2 * h + 1]);
+                                bf16_round2(g0, g1);
+                                bf16_round2(u0, u1);
+                                pk[h] = shared ? silu_mul_pack2(g0, u0, g1, u1)
+                                               : silu_act_pack2(g0, u0, g1, u1);
                             }
-                            st16(dst + j, pk[0], pk[1], pk[2], pk[3]);
+                            st32(dst + j, pk);
                         }
                     }
                 }
@@ -415,12 +400,14 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                     if (valid) {
                         uint16_t *dst = out + (size_t)orow * ld + t.y * PP_BN + c0;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            st16(dst + j,
-                                 pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
-                                 pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
-                                 pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
-                                 pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+                        for (int j = 0; j < 32; j += 16) {
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int h = 0; h < 8; h++)
+                                pk[h] = pack_bf16_rn(__uint_as_float(v[j + 2 * h]),
+                                                     __uint_as_float(v[j + 2 * h + 1]));
+                            st32(dst + j, pk);
+                        }
                     }
                 }
             }
@@ -442,10 +429,11 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
 
 /* ---- host side ---------------------------------------------------------------- */
 inline int g_pp_enable = 1;          /* APUS_CUDA_PAIR=0: never take this path */
-inline int g_pp_min_rows = 96;       /* mean rows per resident expert from which it is taken */
+inline int g_pp_min_rows = 192;      /* mean rows per resident expert from which it is taken */
+inline int g_pp_solo_below = 160;    /* APUS_CUDA_PAIR_SOLO_BELOW: see build_hybrid_tiles_kernel
+                                      * (0: every chunk to the pair kernels) */
 inline int g_pp_gather = 0;          /* APUS_CUDA_PAIR_GATHER=1: rows by TMA gather4 instead of a permuted copy
                                       * (measured 2.4x slower: 32 four-row requests per k-block) */
-inline int g_pp_prefetch = 0;        /* APUS_CUDA_PAIR_PREFETCH: see PairParams::prefetch */
 
 inline bool pair_supported(const ApusCudaMoeCfg &c, int sm_count, int smem_optin) {
     return g_pp_enable && prefill_supported(c) && c.hidden % PP_BN == 0 &&
@@ -461,6 +449,136 @@ inline TilePlan pair_tile_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, i
     p.m_dn = (int)c.hidden / PP_BN;
     p.bn_gu = p.bn_dn = p.bn_sh_gu = p.bn_sh_dn = 2 * PP_BM;
     return p;
+}
+
+
+/* ---- tile lists for the two-SM path ------------------------------------------
+ * The pair's MMA always spans 256 token rows, so a tile with few rows wastes
+ * tensor work (and, under the power cap, clock).  An expert's rows are therefore
+ * cut into chunks of 256; a last chunk of at least `solo_below` rows still goes
+ * to the pair kernels, a smaller remainder goes to the one-SM kernels of
+ * prefill_gemm.cuh, whose MMA is exactly as wide as the rows it is given.
+ * Four lists: pair gate_up / down (shared-expert tiles first), one-SM gate_up /
+ * down (remainders only).  One CTA of 1024 threads, thread e = expert e. */
+struct HybridLists {
+    int4 *pair_gu, *pair_dn, *solo_gu, *solo_dn;
+    int *n_pair_gu, *n_pair_dn, *n_solo_gu, *n_solo_dn;
+    int *sched;              /* two counters of the one-SM kernels' tile hand-out */
+};
+struct HybridPlan {
+    int T;                   /* tokens of the shared expert (0: none) */
+    int m_gu, m_gu_sh, m_dn; /* pair N-tiles: gate_up, shared gate_up, down */
+    int sm_gu, sm_dn;        /* one-SM weight-row tiles: gate_up, down */
+    int solo_bn_gu, solo_bn_dn;   /* token rows per one-SM tile */
+    int solo_below;          /* remainders below this many rows go to the one-SM kernels */
+    HybridLists l;
+};
+
+__global__ void __launch_bounds__(1024)
+build_hybrid_tiles_kernel(const int32_t *__restrict__ counts,
+                          const int32_t *__restrict__ offsets, int E, HybridPlan hp) {
+    pdl_enter();
+    __shared__ int wt[3][32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cnt = tid < E ? counts[tid] : 0, off = tid < E ? offsets[tid] : 0;
+    const int full = cnt / (2 * PP_BM), rem = cnt - full * 2 * PP_BM;
+    const bool rem_pair = rem >= hp.solo_below;
+    const int n_pair = full + (rem_pair ? 1 : 0);             /* 256-row chunks */
+    const int solo = rem_pair ? 0 : rem;                      /* rows for the one-SM kernels */
+    const int n_sg = (solo + hp.solo_bn_gu - 1) / hp.solo_bn_gu;
+    const int n_sd = (solo + hp.solo_bn_dn - 1) / hp.solo_bn_dn;
+    int inc[3] = {n_pair, n_sg, n_sd};
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1)
+#pragma unroll
+        for (int q = 0; q < 3; q++) {
+            const int v = __shfl_up_sync(0xffffffffu, inc[q], d);
+            if (lane >= d) inc[q] += v;
+        }
+    if (lane == 31)
+        for (int q = 0; q < 3; q++) wt[q][warp] = inc[q];
+    __syncthreads();
+    int base[3] = {0, 0, 0}, total[3] = {0, 0, 0};
+    for (int w = 0; w < 32; w++)
+        for (int q = 0; q < 3; q++) {
+            if (w < warp) base[q] += wt[q][w];
+            total[q] += wt[q][w];
+        }
+    const int first_p = base[0] + inc[0] - n_pair, first_sg = base[1] + inc[1] - n_sg,
+              first_sd = base[2] + inc[2] - n_sd;
+    const int nts = (hp.T + 2 * PP_BM - 1) / (2 * PP_BM);
+    const int sh_gu = nts * hp.m_gu_sh, sh_dn = nts * hp.m_dn;
+    const HybridLists &l = hp.l;
+    if (tid < E) {
+        for (int n = 0; n < n_pair; n++) {
+            const int rows = min(2 * PP_BM, cnt - n * 2 * PP_BM), r0 = off + n * 2 * PP_BM;
+            for (int m = 0; m < hp.m_gu; m++)
+                l.pair_gu[(size_t)sh_gu + (size_t)(first_p + n) * hp.m_gu + m] =
+                    make_int4(tid, m, r0, rows);
+            for (int m = 0; m < hp.m_dn; m++)
+                l.pair_dn[(size_t)sh_dn + (size_t)(first_p + n) * hp.m_dn + m] =
+                    make_int4(tid, m, r0, rows);
+        }
+        const int s0 = off + full * 2 * PP_BM;
+        for (int m = 0; m < hp.sm_gu; m++)
+            for (int n = 0; n < n_sg; n++)
+                l.solo_gu[(size_t)first_sg * hp.sm_gu + (size_t)m * n_sg + n] = make_int4(
+                    tid, m, s0 + n * hp.solo_bn_gu, min(hp.solo_bn_gu, solo - n * hp.solo_bn_gu));
+        for (int m = 0; m < hp.sm_dn; m++)
+            for (int n = 0; n < n_sd; n++)
+                l.solo_dn[(size_t)first_sd * hp.sm_dn + (size_t)m * n_sd + n] = make_int4(
+                    tid, m, s0 + n * hp.solo_bn_dn, min(hp.solo_bn_dn, solo - n * hp.solo_bn_dn));
+    }
+    for (int i = tid; i < sh_gu; i += blockDim.x) {
+        const int n = i / hp.m_gu_sh, m = i - n * hp.m_gu_sh;
+        l.pair_gu[i] = make_int4(E, m, n * 2 * PP_BM, min(2 * PP_BM, hp.T - n * 2 * PP_BM));
+    }
+    for (int i = tid; i < sh_dn; i += blockDim.x) {
+        const int n = i / hp.m_dn, m = i - n * hp.m_dn;
+        l.pair_dn[i] = make_int4(E, m, n * 2 * PP_BM, min(2 * PP_BM, hp.T - n * 2 * PP_BM));
+    }
+    if (tid == 0) {
+        *l.n_pair_gu = sh_gu + total[0] * hp.m_gu;
+        *l.n_pair_dn = sh_dn + total[0] * hp.m_dn;
+        *l.n_solo_gu = total[1] * hp.sm_gu;
+        *l.n_solo_dn = total[2] * hp.sm_dn;
+        l.sched[0] = 0;
+        l.sched[1] = 0;
+    }
+}
+
+/* list storage inside the block's tile workspace (prefill_tiles_bytes_for) */
+inline bool hybrid_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, int A, void *ws,
+                        size_t ws_bytes, HybridPlan *out) {
+    const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
+              E = (int)c.experts;
+    HybridPlan p;
+    memset(&p, 0, sizeof p);
+    p.T = do_shared ? T : 0;
+    p.m_gu = I / 128;
+    p.m_gu_sh = Is / 128;
+    p.m_dn = H / PP_BN;
+    p.sm_gu = I / PG_BM;
+    p.sm_dn = H / PG_BM;
+    p.solo_bn_gu = PG_BN_GU;
+    p.solo_bn_dn = PG_BN_DN;
+    p.solo_below = g_pp_solo_below;
+    const size_t chunks = (size_t)A / (2 * PP_BM) + E + (size_t)T / (2 * PP_BM) + 1;
+    const size_t n_pg = chunks * (size_t)(p.m_gu > p.m_gu_sh ? p.m_gu : p.m_gu_sh),
+                 n_pd = chunks * p.m_dn, n_sg = (size_t)E * 2 * p.sm_gu,
+                 n_sd = (size_t)E * p.sm_dn;
+    if ((n_pg + n_pd + n_sg + n_sd) * sizeof(int4) + 64 > ws_bytes) return false;
+    p.l.pair_gu = reinterpret_cast<int4 *>(ws);
+    p.l.pair_dn = p.l.pair_gu + n_pg;
+    p.l.solo_gu = p.l.pair_dn + n_pd;
+    p.l.solo_dn = p.l.solo_gu + n_sg;
+    p.l.n_pair_gu = reinterpret_cast<int *>(p.l.solo_dn + n_sd);
+    p.l.n_pair_dn = p.l.n_pair_gu + 1;
+    p.l.n_solo_gu = p.l.n_pair_gu + 2;
+    p.l.n_solo_dn = p.l.n_pair_gu + 3;
+    p.l.sched = p.l.n_pair_gu + 4;
+    *out = p;
+    return true;
 }
 
 template <typename... KArgs, typename... Args>
@@ -504,12 +622,19 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                  "two-SM grouped GEMM: %d B shared memory, shared_inter == moe_inter", smem);
         return 1;
     }
-    TilePlan plan = pair_tile_plan(c, T, do_shared, A, tiles_ws);
-    launch_k(build_tiles_kernel, dim3(1), dim3(1024), 0, st, (const int32_t *)d.counts,
-             (const int32_t *)d.offsets, E, plan);
+    HybridPlan plan;
+    if (!hybrid_plan(c, T, do_shared, A, tiles_ws,
+                     prefill_tiles_bytes_for(c, (size_t)A, (size_t)T), &plan)) {
+        snprintf(g_prefill_err, sizeof g_prefill_err, "tile workspace too small");
+        return 1;
+    }
+    launch_k(build_hybrid_tiles_kernel, dim3(1), dim3(1024), 0, st,
+             (const int32_t *)d.counts, (const int32_t *)d.offsets, E, plan);
     (*launches)++;
-    const TileLists tl = plan.tl;
-    const bool gather = g_pp_gather != 0;
+    const HybridLists tl = plan.l;
+    const bool solo = plan.solo_below > 0 && A > 0;
+    /* the one-SM kernels read the permuted copy, so it is made whenever they run */
+    const bool gather = g_pp_gather != 0 && !solo;
     if (A > 0 && !gather) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
@@ -547,8 +672,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     const int grid = sm_count & ~1;
     PairParams p1;
     memset(&p1, 0, sizeof p1);
-    p1.tiles = tl.gu;
-    p1.n_tiles = tl.n_gu;
+    p1.tiles = tl.pair_gu;
+    p1.n_tiles = tl.n_pair_gu;
     p1.K = H;
     p1.E = E;
     p1.e_begin = e_begin;
@@ -560,15 +685,49 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p1.ld_shared = Is;
     p1.perm = d.perm;
     p1.status = status;
-    p1.prefetch = g_pp_prefetch;
+    /* the one-SM kernels for the small remainders */
+    CUtensorMap s_xg, s_act;
+    GemmParams g1;
+    memset(&g1, 0, sizeof g1);
+    if (solo) {
+        const int s1 = pg_smem_bytes(true);
+        if (encode_2d(maps->encode, &s_xg, xg, (size_t)A, H, PG_BN_GU) ||
+            encode_2d(maps->encode, &s_act, act, (size_t)A, I, PG_BN_DN))
+            return 1;
+        cudaFuncSetAttribute(grouped_gemm_kernel<0>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
+        cudaFuncSetAttribute(grouped_gemm_kernel<1>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, s1);
+        g1.tiles = tl.solo_gu;
+        g1.n_tiles = tl.n_solo_gu;
+        g1.K = H;
+        g1.E = E;
+        g1.e_begin = e_begin;
+        g1.rows_per_expert = 2 * I;
+        g1.up_off = I;
+        g1.out_routed = act;
+        g1.out_shared = sa;
+        g1.ld_routed = I;
+        g1.ld_shared = Is;
+        g1.status = status;
+        g1.bn_rows = PG_BN_GU;
+        g1.perm = d.perm;
+        g1.sched = tl.sched;
+    }
     p1.gather_tk = gather && A > 0 ? TK : 0;
     launch_pair(pair_gemm_kernel<0>, grid, (size_t)smem, st, m_xg, m_x, maps->w_gu, maps->sh_g,
                 maps->sh_u, m_g, p1);
     (*launches)++;
+    if (solo) {
+        launch_k(grouped_gemm_kernel<0>, dim3(sm_count), dim3(PG_THREADS),
+                 (size_t)pg_smem_bytes(true), st, maps->w_gu, maps->sh_g, maps->sh_u, s_xg,
+                 s_xg, g1);
+        (*launches)++;
+    }
     if (mark) mark(APUS_CUDA_STAGE_GATE_UP);
     PairParams p2 = p1;
-    p2.tiles = tl.dn;
-    p2.n_tiles = tl.n_dn;
+    p2.tiles = tl.pair_dn;
+    p2.n_tiles = tl.n_pair_dn;
     p2.K = I;
     p2.rows_per_expert = H;
     p2.up_off = 0;
@@ -580,6 +739,24 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem, st, m_act, m_sa, maps->w_d, maps->sh_d,
                 maps->sh_d, m_g, p2);
     (*launches)++;
+    if (solo) {
+        GemmParams g2 = g1;
+        g2.tiles = tl.solo_dn;
+        g2.n_tiles = tl.n_solo_dn;
+        g2.K = I;
+        g2.rows_per_expert = H;
+        g2.up_off = 0;
+        g2.out_routed = eo;
+        g2.out_shared = sy;
+        g2.ld_routed = H;
+        g2.ld_shared = H;
+        g2.bn_rows = PG_BN_DN;
+        g2.sched = tl.sched + 1;
+        launch_k(grouped_gemm_kernel<1>, dim3(sm_count), dim3(PG_THREADS),
+                 (size_t)pg_smem_bytes(false), st, maps->w_d, maps->sh_d, maps->sh_d, s_act,
+                 s_act, g2);
+        (*launches)++;
+    }
     if (mark) mark(APUS_CUDA_STAGE_DOWN);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

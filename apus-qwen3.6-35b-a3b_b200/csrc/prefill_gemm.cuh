@@ -517,9 +517,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                         const uint32_t g1 = tmem_ld1(taddr + (uint32_t)tok);
                         const uint32_t u1 = tmem_ld1(taddr + 128u + (uint32_t)tok);
                         tmem_ld_wait();
-                        const float gv = bf16_round(__uint_as_float(g1));
-                        const float uv = bf16_round(__uint_as_float(u1));
-                        out[(size_t)(t.z + n) * ld + col] = silu_act_bits(gv, uv);
+                        float gv = __uint_as_float(g1), uv = __uint_as_float(u1);
+                        bf16_round2(gv, uv);
+                        out[(size_t)(t.z + n) * ld + col] =
+                            (uint16_t)silu_act_pack2(gv, uv, 0.0f, 0.0f);
                     }
                 }
             } else
@@ -531,14 +532,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     tmem_ld32(taddr + 128u + (uint32_t)c0, u);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
+                    for (int j = 0; j < 32; j += 2) {
                         const int n = c0 + j;
                         if (n < t.w) {
-                            const float gv = bf16_round(__uint_as_float(g[j]));
-                            const float uv = bf16_round(__uint_as_float(u[j]));
-                            out[(size_t)(t.z + n) * ld + col] =
-                                shared ? silu_mul_bits(gv, uv)
-                                       : silu_act_bits(gv, uv);
+                            float g0 = __uint_as_float(g[j]), g1 = __uint_as_float(g[j + 1]),
+                                  u0 = __uint_as_float(u[j]), u1 = __uint_as_float(u[j + 1]);
+                            bf16_round2(g0, g1);
+                            bf16_round2(u0, u1);
+                            const uint32_t pk = shared ? silu_mul_pack2(g0, u0, g1, u1)
+                                                       : silu_act_pack2(g0, u0, g1, u1);
+                            out[(size_t)(t.z + n) * ld + col] = (uint16_t)pk;
+                            if (n + 1 < t.w)
+                                out[(size_t)(t.z + n + 1) * ld + col] = (uint16_t)(pk >> 16);
                         }
                     }
                 } else if (MODE == 2) {
@@ -557,11 +562,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                                          : __ldg(&p.perm[t.z + c0 + lane]);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int orow = __shfl_sync(0xffffffffu, my_orow, j);
-                        if (c0 + j < t.w)
-                            out[(size_t)orow * ld + col] =
-                                bf16_bits(__uint_as_float(g[j]));
+                    for (int j = 0; j < 32; j += 2) {
+                        const int orow0 = __shfl_sync(0xffffffffu, my_orow, j);
+                        const int orow1 = __shfl_sync(0xffffffffu, my_orow, j + 1);
+                        const uint32_t pk =
+                            pack_bf16_rn(__uint_as_float(g[j]), __uint_as_float(g[j + 1]));
+                        if (c0 + j < t.w) out[(size_t)orow0 * ld + col] = (uint16_t)pk;
+                        if (c0 + j + 1 < t.w)
+                            out[(size_t)orow1 * ld + col] = (uint16_t)(pk >> 16);
                     }
                 }
             }

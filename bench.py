@@ -873,8 +873,10 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
     dist.all_reduce(launches, op=dist.ReduceOp.SUM)
 
     # ---- output check on rank 0 -------------------------------------------
+    # rows travel as bytes: 16-bit integers are not an NCCL datatype
     gathered = [torch.empty_like(out_keep) for _ in range(world)] if rank == 0 else None
-    dist.gather(out_keep, gathered, dst=0)
+    dist.gather(out_keep.view(torch.uint8),
+                [g.view(torch.uint8) for g in gathered] if rank == 0 else None, dst=0)
     parity, rows_per_rank, sent_rows = None, None, None
     if rank == 0 and not getattr(args, "no_check", False):
         ep_out = torch.cat(gathered).cpu().numpy().view(np.uint16)

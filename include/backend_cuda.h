@@ -203,7 +203,7 @@ int apus_cuda_layer_upload(ApusCudaLayer *layer, int which, const uint16_t *src,
  * tiles (H, I, Is multiples of 128, Is == I), else the grouped-GEMV kernels.
  * APUS_CUDA_DECODE_MAX_T (default 4) is the largest T that still takes the
  * grouped-GEMV kernels on a shape the GEMM supports.  From a mean of
- * APUS_CUDA_PAIR_MIN_ROWS (default 96) rows per expert on, and H a multiple of
+ * APUS_CUDA_PAIR_MIN_ROWS (default 192) rows per expert on, and H a multiple of
  * 256, the two GEMMs run with a pair of SMs per tile (cta_group::2: tokens
  * 256 per pair, each SM loading half of the weight tile); APUS_CUDA_PAIR=0
  * keeps the one-SM kernels.

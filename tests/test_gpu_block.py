@@ -263,6 +263,7 @@ def test_block_two_sm_gemm_path(be, orc, synth, monkeypatch, T, E, TK, skew):
         W, x = synth.apply_router_bias(W, x, synth.zipf_bias(cfg, seed=3, beta=0.6))
     exp = orc.moe_block(cfg, W, x)
     res = {}
+    monkeypatch.setenv("APUS_CUDA_PAIR_MIN_ROWS", "64")   # default: 192 rows per expert
     for pair in ("1", "0"):
         monkeypatch.setenv("APUS_CUDA_PAIR", pair)
         be.enable()
