@@ -61,6 +61,7 @@ SYMBOLS = [
     "apus_cuda_moe_block", "apus_cuda_block_hooks", "apus_cuda_layer_create",
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
     "apus_cuda_layer_refresh", "apus_cuda_layer_upload",
+    "apus_cuda_layer_load_slabs",
     "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_path",
     "apus_cuda_last_block_status",
@@ -76,7 +77,8 @@ SYMBOLS = [
     "apus_cuda_ep_shared_dev", "apus_cuda_ep_combine_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
     "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
-    "apus_cuda_resadd_dev", "apus_synth_fill_host", "apus_synth_fill_dev",
+    "apus_cuda_resadd_dev", "apus_cuda_bf16_gemv_dev", "apus_synth_fill_host",
+    "apus_synth_fill_dev",
 ]
 
 STAGES = ("router", "dispatch", "gather", "gate_up", "down", "finalize")
@@ -125,6 +127,7 @@ class Backend:
         L.apus_cuda_layer_tensor.restype = vp
         L.apus_cuda_layer_refresh.argtypes = [vp]
         L.apus_cuda_layer_upload.argtypes = [vp, C.c_int, u16p, sz, sz]
+        L.apus_cuda_layer_load_slabs.argtypes = [vp, C.c_char_p, C.c_int]
         L.apus_cuda_debug_fast_logits.argtypes = [u16p, u16p, sz, sz, sz, f32p,
                                                   f32p, f32p, f32p]
         L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
@@ -158,6 +161,7 @@ class Backend:
         L.apus_cuda_ep_combine_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
+        L.apus_cuda_bf16_gemv_dev.argtypes = [vp, vp, vp, sz, sz, sz, vp]
         L.apus_synth_fill_host.argtypes = [u16p, sz, C.c_uint64, C.c_uint32,
                                            C.c_uint32, C.c_uint64, C.c_double]
         L.apus_synth_fill_host.restype = None
@@ -329,6 +333,13 @@ class Backend:
         self._check(self.lib.apus_cuda_layer_upload(
             layer, TENSOR_IDS[name], _ptr(src, u16p), first, src.size),
             "apus_cuda_layer_upload")
+
+    def layer_load_slabs(self, layer, container_dir, layer_index):
+        """Routed experts of the layer's resident range from the engine's
+        weight container (apus.index.json + shards)."""
+        self._check(self.lib.apus_cuda_layer_load_slabs(
+            layer, str(container_dir).encode(), layer_index),
+            "apus_cuda_layer_load_slabs")
 
     def debug_fast_logits(self, x, wg):
         """(fast [T,E] f32, xnorm [T], wnorm [E+1], cbound) of the many-token
@@ -503,6 +514,10 @@ class Backend:
     def resadd_dev(self, d_a, d_b, d_out, n, stream=None):
         self._check(self.lib.apus_cuda_resadd_dev(d_a, d_b, d_out, n, stream),
                     "apus_cuda_resadd_dev")
+
+    def bf16_gemv_dev(self, d_w, d_x, d_y, M, O, K, stream=None):
+        self._check(self.lib.apus_cuda_bf16_gemv_dev(d_w, d_x, d_y, M, O, K, stream),
+                    "apus_cuda_bf16_gemv_dev")
 
     # ---- synthetic tensors -------------------------------------------------------
     def synth_fill_host(self, n, seed, layer, tensor_id, sigma, first=0):

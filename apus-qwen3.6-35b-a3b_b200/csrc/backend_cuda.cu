@@ -31,6 +31,7 @@
 #include "prefill_gemm.cuh"
 #include "pair_gemm.cuh"
 #include "router.cuh"
+#include "slab_loader.h"
 
 using namespace apus;
 
@@ -934,6 +935,22 @@ extern "C" int apus_cuda_layer_upload(ApusCudaLayer *L, int which,
     CU_OK(cudaMemcpy(dst + first, src, n * 2, cudaMemcpyHostToDevice));
     g_ctx->bytes_uploaded += n * 2;
     if (which == 1 || which == 7) return layer_router_stats(g_ctx, L);
+    return 0;
+}
+
+extern "C" int apus_cuda_layer_load_slabs(ApusCudaLayer *L, const char *container_dir,
+                                          int layer_index) {
+    if (!L || !container_dir || layer_index < 0) return fail("layer_load_slabs: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    if (L->e_end == L->e_begin) return 0;
+    CU_OK(cudaDeviceSynchronize());
+    char err[400] = "";
+    const long long n = load_layer_slabs(container_dir, layer_index, L->e_begin, L->e_end,
+                                         L->cfg.hidden, L->cfg.moe_inter, L->exp_gu, L->exp_d,
+                                         err, sizeof err);
+    if (n < 0) return fail("layer_load_slabs: %s", err);
+    g_ctx->bytes_uploaded += (uint64_t)n;
     return 0;
 }
 
@@ -2041,6 +2058,47 @@ extern "C" int apus_cuda_rmsnorm_dev(const uint16_t *d_x, const uint16_t *d_w,
     }
     rmsnorm_kernel<<<(unsigned)((T + 3) / 4), 128, smem, st>>>(d_x, d_w, d_y,
                                                                (int)T, (int)N);
+    LAUNCHED();
+    return 0;
+}
+
+template <int M>
+static int launch_gemv_stream(Ctx *c, const uint16_t *w, const uint16_t *x, uint16_t *y,
+                              size_t O, size_t K, cudaStream_t st) {
+    const size_t smem = (size_t)M * K * sizeof(float);
+    if (smem > (size_t)c->smem_optin) return fail("gemv_dev: M * K too large");
+    if (smem > 48 * 1024)
+        CU_OK(cudaFuncSetAttribute(gemv_stream_kernel<M>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    size_t blocks = (O + 15) / 16;                 /* 8 warps x 2 rows per CTA pass */
+    const size_t cap = (size_t)c->sm_count * (smem > 64 * 1024 ? 1 : (smem > 24 * 1024 ? 3 : 6));
+    if (blocks > cap) blocks = cap;
+    gemv_stream_kernel<M><<<(unsigned)blocks, 256, smem, st>>>(w, x, y, (long)O, (int)K);
+    return 0;
+}
+
+extern "C" int apus_cuda_bf16_gemv_dev(const uint16_t *d_w, const uint16_t *d_x,
+                                       uint16_t *d_y, size_t M, size_t O, size_t K,
+                                       void *stream) {
+    if (!d_w || !d_x || !d_y || !M || !O || !K) return fail("gemv_dev: bad args");
+    if (M > 8 || K % 256 || (((uintptr_t)d_w) & 15))
+        return fail("gemv_dev: needs M <= 8, K a multiple of 256, 16-byte aligned weights");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = 1;
+    switch (M) {
+        case 1: rc = launch_gemv_stream<1>(c, d_w, d_x, d_y, O, K, st); break;
+        case 2: rc = launch_gemv_stream<2>(c, d_w, d_x, d_y, O, K, st); break;
+        case 3: rc = launch_gemv_stream<3>(c, d_w, d_x, d_y, O, K, st); break;
+        case 4: rc = launch_gemv_stream<4>(c, d_w, d_x, d_y, O, K, st); break;
+        case 5: rc = launch_gemv_stream<5>(c, d_w, d_x, d_y, O, K, st); break;
+        case 6: rc = launch_gemv_stream<6>(c, d_w, d_x, d_y, O, K, st); break;
+        case 7: rc = launch_gemv_stream<7>(c, d_w, d_x, d_y, O, K, st); break;
+        default: rc = launch_gemv_stream<8>(c, d_w, d_x, d_y, O, K, st); break;
+    }
+    if (rc) return 1;
     LAUNCHED();
     return 0;
 }

@@ -59,6 +59,60 @@ exact_matvec_f32_kernel(const uint16_t *__restrict__ w,
         y[o] = exact_dot(w + o * K, x, K);
 }
 
+/* y[m,o] = rnd(sum_k W[o,k] x[m,k]) as a weight STREAM (the engine's largest
+ * dense product per token is the output head, 248320 x 2048 = 1 GB of weights,
+ * c/model.h:667-688): device pointers, one warp per pair of weight rows, 16-byte
+ * coalesced loads with eight in flight per lane, the M <= 8 activation rows in
+ * shared memory as fp32, lane-strided fp32 partial sums closed by shuffles.
+ * The summation order differs from the engine's sequential chain, so the result
+ * agrees to BF16 tolerance, not bitwise; the exact-order form is
+ * exact_gemm_kernel behind the host-pointer hooks. */
+template <int M>
+__global__ void __launch_bounds__(256)
+gemv_stream_kernel(const uint16_t *__restrict__ w, const uint16_t *__restrict__ x,
+                   uint16_t *__restrict__ y, long O, int K) {
+    extern __shared__ float gs_x[];          /* [M][K] */
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) gs_x[i] = bf16_f32(x[i]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long nwarps = ((long)gridDim.x * blockDim.x) >> 5;
+    for (long o0 = warp * 2; o0 < O; o0 += nwarps * 2) {
+        const bool two = o0 + 1 < O;
+        const uint16_t *r0 = w + o0 * K, *r1 = w + (two ? o0 + 1 : o0) * K;
+        float a0[M], a1[M];
+#pragma unroll
+        for (int m = 0; m < M; m++) a0[m] = a1[m] = 0.0f;
+#pragma unroll 4
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 v0 = ldg16(r0 + k), v1 = ldg16(r1 + k);
+            const float f0[8] = {bf16lo(v0.x), bf16hi(v0.x), bf16lo(v0.y), bf16hi(v0.y),
+                                 bf16lo(v0.z), bf16hi(v0.z), bf16lo(v0.w), bf16hi(v0.w)};
+            const float f1[8] = {bf16lo(v1.x), bf16hi(v1.x), bf16lo(v1.y), bf16hi(v1.y),
+                                 bf16lo(v1.z), bf16hi(v1.z), bf16lo(v1.w), bf16hi(v1.w)};
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float4 xa = *reinterpret_cast<const float4 *>(gs_x + (size_t)m * K + k);
+                const float4 xb = *reinterpret_cast<const float4 *>(gs_x + (size_t)m * K + k + 4);
+                const float xf[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    a0[m] = fmaf(f0[j], xf[j], a0[m]);
+                    a1[m] = fmaf(f1[j], xf[j], a1[m]);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            const float s0 = warp_sum(a0[m]), s1 = warp_sum(a1[m]);
+            if (lane == 0) {
+                y[(size_t)m * O + o0] = bf16_bits(s0);
+                if (two) y[(size_t)m * O + o0 + 1] = bf16_bits(s1);
+            }
+        }
+    }
+}
+
 /* RMSNorm with (1+w) gain, single rounding (c/attn.h:175-186): the sum of
  * squares is the ascending sequential fp32 chain; one warp per row, lane 0
  * walks the chain over the row staged in shared memory. */

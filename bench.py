@@ -499,6 +499,52 @@ def measure_stack(env, layers, T, chain, steps, warmup, sustain_s, seed,
     return res
 
 
+def measure_output_head(env, steps, warmup, seed):
+    """The engine's largest dense product per token as a weight stream: the
+    output head, 248320 x 2048 BF16 (c/model.h:667-688), one token, through
+    apus_cuda_bf16_gemv_dev.  1 GB of weights per step: larger than L2."""
+    import numpy as np
+    be, torch, stream, pk = env["be"], env["torch"], env["stream"], env["pk"]
+    synth = env["synth"]
+    sp = stream.cuda_stream
+    O, K = 248320, 2048
+    d_w = torch.empty((O, K), dtype=torch.int16, device="cuda")
+    be.synth_fill_dev(d_w.data_ptr(), O * K, seed, 0, 9, synth.W_SIGMA, stream=sp)
+    x = synth.host_x(be, 1, K, seed=seed)
+    d_x = torch.from_numpy(x.view(np.int16)).cuda()
+    d_y = torch.empty((1, O), dtype=torch.int16, device="cuda")
+
+    def step():
+        be.bf16_gemv_dev(d_w.data_ptr(), d_x.data_ptr(), d_y.data_ptr(), 1, O, K, stream=sp)
+    for _ in range(max(3, warmup)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(torch, stream, step, max(steps, 20))
+    clocks = sampler.finish()
+    nbytes = O * K * 2 + K * 2 + O * 2
+    ach = nbytes / (ms * 1e-3) / 1e9
+    # a sample of rows against the exact chain of the CPU checker
+    from oracle import oracle
+    orc = oracle.Restatement()
+    rows = np.arange(0, O, O // 64)[:64]
+    w_rows = np.stack([be.synth_fill_host(K, seed, 0, 9, synth.W_SIGMA, first=int(r) * K)
+                       for r in rows])
+    exp = synth.bf16_to_f32(orc.gemv(w_rows, x[0]))
+    got = synth.bf16_to_f32(d_y.cpu().numpy().view(np.uint16)[0, rows])
+    return {"ms_per_step": ms, "tokens_per_s": 1.0 / (ms * 1e-3), "clocks": clocks,
+            "launch": "host launch (one kernel)",
+            "config": {"workload": "output head as a weight stream: y = W x, W 248320 x 2048 "
+                                   "BF16, one token, device pointers", "tokens_per_step": 1,
+                       "l2_policy": "inputs larger than L2 (1 GB of weights per step)"},
+            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<1>", "achieved": ach,
+                         "peak": pk["hbm_gbs"], "peak_source": pk["_source"], "unit": "GB/s",
+                         "frac": ach / pk["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes_per_launch": nbytes},
+            "parity": {"rows": 64, "max_abs": float(np.abs(got - exp).max()),
+                       "checker": "oracle.Restatement().gemv (exact sequential chain)"}}
+
+
 def strip(res):
     return {k: v for k, v in res.items() if not k.startswith("_")}
 
@@ -605,6 +651,9 @@ def run_headline(args, cfg, pkg, synth):
             r = measure_stack(env, stack, B, True, st, wu, args.sustain / 2, args.seed)
             subs[f"config2_40_layers_chained_B{B}"] = dict(
                 r, config=workload_config(B, False, args.seed, 40, True))
+        for h in stack:
+            be.layer_destroy(h)
+        subs["next_output_head_gemv"] = measure_output_head(env, st, wu, args.seed)
         line["configs"] = subs
     print(json.dumps(line))
 

@@ -192,6 +192,19 @@ int apus_cuda_layer_refresh(ApusCudaLayer *layer);
  * Writing rtr_w or sh_gate refreshes the router statistics. */
 int apus_cuda_layer_upload(ApusCudaLayer *layer, int which, const uint16_t *src,
                            size_t first, size_t n);
+/* Fill exp_gu / exp_d of the layer's resident expert range straight from the
+ * engine's weight container in `container_dir`: the manifest apus.index.json
+ * (format_version 2) locates each expert's slab {gate_up [2I,H] | down [H,I]}
+ * by {layer, expert, shard, offset, nbytes} (c/cache.h:13-23); each slab is
+ * read once into pinned staging and copied to HBM.  Takes the place of the
+ * engine's eager load, which concatenates all experts of a layer into two host
+ * arrays first (c/model.h:505-537); a rank of an expert-parallel server reads
+ * only its own experts.  Router, shared expert and shared gate still come
+ * through apus_cuda_layer_create / _upload.  Synchronous.  Nonzero with
+ * apus_cuda_last_error() set on a missing or malformed manifest, a version
+ * other than 2, a missing record or a slab of the wrong size. */
+int apus_cuda_layer_load_slabs(ApusCudaLayer *layer, const char *container_dir,
+                               int layer_index);
 
 /* The block on device pointers: d_ln2 [T,H] -> d_out [T,H]; d_tr members are
  * device pointers (or NULL).  Enqueued on `stream` (a cudaStream_t; NULL is the
@@ -426,6 +439,17 @@ int apus_cuda_rmsnorm_dev(const uint16_t *d_x, const uint16_t *d_w,
                           uint16_t *d_y, size_t T, size_t N, void *stream);
 int apus_cuda_resadd_dev(const uint16_t *d_a, const uint16_t *d_b,
                          uint16_t *d_out, size_t n, void *stream);
+
+/* ---- the engine's largest dense product as a weight stream -------------- */
+/* y[m,o] = rnd(sum_k W[o,k] x[m,k]) on DEVICE pointers, W [O,K], x [M,K],
+ * y [M,O], M <= 8, K a multiple of 256: the bandwidth-bound form of the
+ * bf16_gemv / bf16_gemm hooks for resident weights and activations (the
+ * output head is 248320 x 2048, 1 GB of weights per token, c/model.h:667-688).
+ * fp32 accumulation in a lane-strided order, so the result agrees with the
+ * engine's sequential chain to BF16 tolerance, not bitwise; callers that need
+ * the chain's exact bits (the router) use the host-pointer entry points. */
+int apus_cuda_bf16_gemv_dev(const uint16_t *d_w, const uint16_t *d_x, uint16_t *d_y,
+                            size_t M, size_t O, size_t K, void *stream);
 
 /* ---- synthetic tensors (benchmarks and tests) ---------------------------- */
 /* Fill n BF16 elements with the counter-based approximately-normal stream

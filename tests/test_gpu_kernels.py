@@ -244,3 +244,26 @@ def test_rmsnorm_and_residual_add_bitwise(gpu, orc, be, synth, T, N):
     gpu.resadd_dev(d_x.data_ptr(), d_b.data_ptr(), d_y.data_ptr(), T * N, stream=sp)
     torch.cuda.synchronize()
     assert np.array_equal(d_y.cpu().numpy().view(np.uint16), orc.resadd(x, b))
+
+
+# ---- the dense weight stream on device pointers --------------------------------
+
+@pytest.mark.parametrize("M,O,K", [(1, 4096, 2048), (3, 1000, 512), (8, 777, 256),
+                                   (1, 1, 256), (2, 33, 2048)])
+def test_gemv_stream_dev(gpu, orc, M, O, K):
+    """apus_cuda_bf16_gemv_dev against the CPU anchor: same products, another
+    summation order, so BF16 tolerance (the hooks keep the exact bits)."""
+    import torch
+    rng = np.random.default_rng(M * 1000 + O)
+    w, x = rng_codes(rng, (O, K), 0.05), rng_codes(rng, (M, K), 1.0)
+    d_w = torch.from_numpy(w.view(np.int16)).cuda()
+    d_x = torch.from_numpy(x.view(np.int16)).cuda()
+    d_y = torch.zeros((M, O), dtype=torch.int16, device="cuda")
+    gpu.bf16_gemv_dev(d_w.data_ptr(), d_x.data_ptr(), d_y.data_ptr(), M, O, K,
+                      stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = f32(d_y.cpu().numpy().view(np.uint16))
+    exp = f32(orc.gemm(w, x))
+    scale = np.abs(exp).max() + 1e-9
+    assert np.abs(got - exp).max() <= 1e-2 * scale
+    assert (got.view(np.uint32) != exp.view(np.uint32)).mean() <= 0.2
