@@ -53,6 +53,7 @@ ZIPF_S = 1.1
 # mean load at 8192 tokens (2579 rows against 256), then frozen
 ZIPF_BETA = 0.27
 MAX_T = 8448          # largest token count any workload of this file runs
+CONFIG4_T = 8448      # 256 decode tokens + 4 chunked-prefill chunks of 2048
 L2_BYTES = 126 << 20
 DTYPE = "bf16 storage, fp32 accumulate"
 
@@ -651,6 +652,16 @@ def run_headline(args, cfg, pkg, synth):
             r = measure_stack(env, stack, B, True, st, wu, args.sustain / 2, args.seed)
             subs[f"config2_40_layers_chained_B{B}"] = dict(
                 r, config=workload_config(B, False, args.seed, 40, True))
+        r = measure_stack(env, stack, CONFIG4_T, True, max(3, st // 4), 3, 0.0, args.seed,
+                          want_e2e=False)
+        subs["config4_shape_on_one_gpu_40_layers_chained_T8448"] = dict(
+            r, config=workload_config(CONFIG4_T, False, args.seed, 40, True),
+            note="configuration 4's step (256 decode tokens + 4 prefill chunks of 2048 "
+                 "= 8448 tokens per layer, 40 layers) on ONE GPU with every expert "
+                 "resident; the 8-GPU expert-parallel form is a sub-measurement of "
+                 "the multi-GPU line",
+            tensor_frac_of_measured_burst=40 * flops(cfg, CONFIG4_T) / (r["ms_per_step"] * 1e-3)
+                                          / 1e12 / env["pk"]["bf16_tflops"])
         for h in stack:
             be.layer_destroy(h)
         subs["next_output_head_gemv"] = measure_output_head(env, st, wu, args.seed)
@@ -981,6 +992,11 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
         parity["ok"] = bool(parity["idx_exact"] and parity["idx_exact_all_tokens"]
                             and bad == 0 and parity["max_abs"] <= 2e-2
                             and parity["rel_l2"] <= 1e-2)
+    # ---- configuration 4: the 40-layer mixed serving step, expert-parallel ----
+    config4 = None
+    if not getattr(args, "no_sub", False) and exchange == "peer" and CONFIG4_T % world == 0:
+        config4 = run_config4(args, cfg, pkg, synth, be, ep, blk, rank, world, stream,
+                              peaks, clock_sampler, local)
     if rank == 0:
         cfgline = dict(config)
         cfgline["parallelism"] = f"ep{world}"
@@ -1021,6 +1037,8 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
             line["sustained"] = sustained
         if parity is not None:
             line["parity"] = parity
+        if config4 is not None:
+            line["configs"] = {"config4_40_layers_mixed_step_T8448": config4}
         # The batch is tensor-bound at these sizes: all flops of the step over
         # what N GPUs could do at the measured dense rate in the step's time.
         ach = wl["flops"] / (ms * 1e-3) / 1e12
@@ -1040,6 +1058,137 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
         raise SystemExit(f"device status {status} on some rank (a bounded wait gave up)")
     if rank == 0 and parity is not None and not parity["ok"]:
         raise SystemExit("expert-parallel output check failed: " + json.dumps(parity))
+
+
+def run_config4(args, cfg, pkg, synth, be, ep, blk0, rank, world, stream, peaks,
+                clock_sampler, local):
+    """40 MoE layers with independent weights, 8448 tokens per layer (256 decode
+    tokens + 4 prefill chunks of 2048; the block is position-agnostic, so the
+    step is one batch), uniform router, chained x <- x + moe(rmsnorm(x)); rank r
+    holds experts [r*E/N, (r+1)*E/N) of every layer and 8448/N tokens.  One
+    window serves all layers (a layer's step begins after the returns of the
+    layer before).  The whole step is one CUDA graph."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    H, E, TK = cfg["hidden"], cfg["experts"], cfg["top_k"]
+    L, Tg = 40, CONFIG4_T
+    T, per = Tg // world, E // world
+    sp = stream.cuda_stream
+    if T > blk0.max_tokens:
+        win = be.ep_window_create(T, TK, H, E, world, rank)
+        mine = be.ep_window_handle(win)
+        handles = [None] * world
+        dist.all_gather_object(handles, mine)
+        for r in range(world):
+            if r != rank:
+                be.ep_window_attach(win, r, handles[r])
+        owned = True
+    else:
+        win, owned = blk0.win, False
+    layers, blks = [], []
+    for l in range(L):
+        h = be.layer_create(cfg, None, rank * per, (rank + 1) * per)
+        synth.device_weights(be, h, cfg, seed=args.seed, layer=l, expert_begin=rank * per,
+                             stream=sp)
+        layers.append(h)
+        blks.append(ep.PeerWindowBlock(be, h, cfg, rank, world, T, window=win,
+                                       device_epoch=True))
+    x_all = synth.host_x(be, Tg, H, seed=args.seed, layer=1)
+    x_loc = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
+    d_x = torch.from_numpy(x_loc).cuda()
+    d_h = torch.empty_like(d_x)
+    d_ln = torch.empty_like(d_x)
+    first = {}
+
+    def one_pass(keep=False):
+        d_h.copy_(d_x)
+        for l, b in enumerate(blks):
+            be.rmsnorm_dev(d_h.data_ptr(), None, d_ln.data_ptr(), T, H, stream=sp)
+            moe = b.forward(d_ln)
+            if keep and l == 0:
+                first["ln"], first["moe"] = d_ln.clone(), moe.clone()
+            be.resadd_dev(d_h.data_ptr(), moe.data_ptr(), d_h.data_ptr(), T * H, stream=sp)
+
+    one_pass(keep=True)
+    torch.cuda.synchronize()
+    l0 = be.launches()
+    one_pass()
+    per_step = be.launches() - l0
+    torch.cuda.synchronize()
+    dist.barrier()
+    step, mode = one_pass, "host launches"
+    ok = torch.ones(1, device="cuda")
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+    except Exception as e:
+        print(f"rank {rank}: config 4 graph capture failed ({e})", file=sys.stderr)
+        ok.zero_()
+    torch.cuda.synchronize()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if float(ok.item()) != 0.0:
+        step, mode = graph.replay, "cuda graph replay"
+    for _ in range(3):
+        step()
+    steps = max(3, args.steps // 4)
+    sampler = clock_sampler(local) if rank == 0 and clock_sampler is not None else None
+    if sampler is not None:
+        sampler.start()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    clocks = sampler.finish() if sampler is not None else None
+    st = torch.tensor([float(be.last_block_status())], device="cuda")
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    # layer 0 of the chain on rank 0's tokens against the CPU checker
+    parity = None
+    if rank == 0 and not getattr(args, "no_check", False):
+        from oracle import oracle
+        orc = oracle.Restatement()
+        W = synth.host_weights(be, cfg, seed=args.seed, layer=0)
+        rows = np.sort(np.random.default_rng(args.seed + 4).choice(T, 16, replace=False))
+        ln = first["ln"].cpu().numpy().view(np.uint16)
+        exp_ln = orc.rmsnorm(x_all[rows])
+        exp = orc.moe_block(cfg, W, np.ascontiguousarray(ln[rows]))
+        got = first["moe"].cpu().numpy().view(np.uint16)[rows]
+        a = synth.bf16_to_f32(got).astype(np.float64)
+        b = synth.bf16_to_f32(exp["out"]).astype(np.float64)
+        parity = {"rows": 16, "layer": 0,
+                  "rmsnorm_bit_exact": bool(np.array_equal(ln[rows], exp_ln)),
+                  "max_abs": float(np.abs(a - b).max()),
+                  "rel_l2": float(np.linalg.norm(a - b) / (np.linalg.norm(b) + 1e-30)),
+                  "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2},
+                  "checker": "oracle.Restatement(): rmsnorm and moe_block of the first "
+                             "layer on sampled rows of rank 0 (teacher-forced)"}
+        parity["ok"] = bool(parity["rmsnorm_bit_exact"] and parity["max_abs"] <= 2e-2
+                            and parity["rel_l2"] <= 1e-2)
+    for h in layers:
+        be.layer_destroy(h)
+    if owned:
+        be.ep_window_destroy(win)
+    fl = L * flops(cfg, Tg)
+    return {"ms_per_step": ms, "tokens_per_s": Tg / (ms * 1e-3),
+            "token_layers_per_s": Tg * L / (ms * 1e-3), "layers": L,
+            "tokens_per_layer": Tg, "tokens_per_gpu": T, "launch": mode, "steps": steps,
+            "gpu_launches_per_step": per_step * world, "clocks": clocks,
+            "device_status": int(st.item()), "parity": parity,
+            "config": workload_config(Tg, False, args.seed, L, True),
+            "roofline": {"bound": "tensor", "kernel": "whole step on all GPUs",
+                         "achieved": fl / (ms * 1e-3) / 1e12,
+                         "peak": world * peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "peak_source": peaks["_source"],
+                         "frac": fl / (ms * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
+                         "traffic": None, "algorithmic_flops_per_launch": fl}}
 
 
 def main():
