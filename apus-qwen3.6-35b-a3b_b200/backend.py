@@ -67,6 +67,7 @@ SYMBOLS = [
     "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
     "apus_cuda_fused_timeline", "apus_cuda_router_exact_chains",
+    "apus_cuda_router_timeline",
     "apus_cuda_ep_route_dev", "apus_cuda_ep_pack_dev", "apus_cuda_experts_dev",
     "apus_cuda_ep_finish_dev",
     "apus_cuda_ep_window_create", "apus_cuda_ep_window_destroy",
@@ -391,6 +392,15 @@ class Backend:
         if n < 0:
             return None
         return np.array(buf[:n], dtype=np.uint64).reshape(-1, 8)
+
+    def router_timeline(self):
+        """(ns from start: candidates known, chains done, end; chains walked)
+        of the certified router's first CTA in its last launch."""
+        out = (C.c_uint * 5)()
+        if self.lib.apus_cuda_router_timeline(out) != 0:
+            return None
+        t0 = out[0]
+        return [(int(out[i]) - int(t0)) & 0xffffffff for i in (1, 2, 3)] + [int(out[4])]
 
     def router_exact_chains(self):
         self.lib.apus_cuda_router_exact_chains.restype = C.c_long

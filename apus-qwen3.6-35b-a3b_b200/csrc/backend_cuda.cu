@@ -1454,6 +1454,20 @@ extern "C" int apus_cuda_fused_timeline(unsigned long long *out, int cap) {
     return n;
 }
 
+/* phase boundaries of the certified router's first CTA in its last launch:
+ * out[0..3] = start, candidates known, chains done, end (ns, low 32 bits of the
+ * global timer), out[4] = chains that CTA walked */
+extern "C" int apus_cuda_router_timeline(unsigned int *out) {
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (!g_ctx || !out) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    unsigned int v[16];
+    if (cudaMemcpy(v, g_ctx->d_rc_stats, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -1;
+    for (int i = 0; i < 5; i++) out[i] = v[2 + i];
+    return 0;
+}
+
 extern "C" long apus_cuda_router_exact_chains(void) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (!g_ctx) return -1;

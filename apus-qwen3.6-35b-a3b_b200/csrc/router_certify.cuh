@@ -41,14 +41,17 @@
 
 namespace apus {
 
-constexpr int RC_TT = 8;            /* tokens per CTA */
+constexpr int RC_TT = 8;            /* tokens per CTA (6 with deeper prefetch measured the same) */
 constexpr int RC_THREADS = 256;      /* one warp per token in the first phase */
 constexpr int RC_XPAD = 4;          /* floats between token rows: rows on
                                      * different bank groups */
 constexpr int RC_CW = 4;            /* warps that walk chains: 128 pairs in one round (8 tokens
                                      * give 86 on average; a second round doubles the latency) */
 constexpr int RC_BLK = 32;          /* weights per staged row block */
-constexpr int RC_AHEAD = 2;         /* row blocks requested ahead of the one in use */
+constexpr int RC_AHEAD = 2;         /* row blocks requested ahead of the one in use (4 ahead
+                                     * measured the same: the chain is bound by its
+                                     * dependent adds and shared-memory reads, ~12 cycles a
+                                     * step, not by the copies) */
 constexpr int RC_NBUF = RC_AHEAD + 1;
 constexpr int RC_WPITCH = RC_BLK * 2 + 16;   /* bytes per staged row block */
 constexpr int ST_BOUND_VIOLATED = 5;
@@ -184,7 +187,10 @@ __device__ __forceinline__ float rc_walk(const uint16_t *const *rows, unsigned c
  * E <= 1024.  Dynamic shared memory:
  *   xs    float  [RC_TT][K + RC_XPAD]   tokens
  *   af    float  [RC_TT][E]             fast logits
- *   pairs int    [RC_TT * (E + 1)]      (token << 16 | row)
+ *   pairs uint16 [RC_TT * (E + 1)]      (token << 11 | row); 16-bit so that TWO
+ *                                        CTAs fit the SM's shared memory (one
+ *                                        CTA per SM left the chain warps' idle
+ *                                        phases uncovered: 7 waves of 22 us)
  *   wn    float  [E + 1]                row norms
  *   wbuf  [RC_CW][RC_NBUF][32][80 B]    staged weight blocks of the chain warps
  *
@@ -194,7 +200,7 @@ __device__ __forceinline__ float rc_walk(const uint16_t *const *rows, unsigned c
  * rows into shared memory cooperatively (four lanes per row, cp.async, three
  * blocks in flight) and every lane then reads its row from there.
  */
-__global__ void __launch_bounds__(RC_THREADS)
+__global__ void __launch_bounds__(RC_THREADS, 2)
 router_certify_kernel(CertifyArgs a) {
     /* the next kernel may be scheduled; this kernel's own wait for the fast-logit
      * GEMM comes after the tokens are staged (they are the GEMM's input, complete
@@ -208,14 +214,24 @@ router_certify_kernel(CertifyArgs a) {
     const int xp = K + RC_XPAD;
     float *xs = reinterpret_cast<float *>(rc_smem);
     float *af = xs + (size_t)RC_TT * xp;
-    int *pairs = reinterpret_cast<int *>(af + (size_t)RC_TT * E);
-    float *wn = reinterpret_cast<float *>(pairs + (size_t)RC_TT * (E + 1));
+    uint16_t *pairs = reinterpret_cast<uint16_t *>(af + (size_t)RC_TT * E);
+    float *wn = reinterpret_cast<float *>(
+        (reinterpret_cast<uintptr_t>(pairs + (size_t)RC_TT * (E + 1)) + 15) & ~(uintptr_t)15);
     unsigned char *wbuf = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(wn + E + 1) + 15) & ~(uintptr_t)15);
     __shared__ const uint16_t *s_rowptr[RC_CW][32];
     __shared__ int s_npairs;
     __shared__ unsigned int s_xmin;
     __shared__ float s_xnorm[RC_TT];
+    auto mark = [&](int k) {
+        /* phase boundaries of CTA 0 (global timer, ns) for the profiling notes */
+        if (a.stats && blockIdx.x == 0 && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            a.stats[2 + k] = (unsigned int)t;
+        }
+    };
+    mark(0);
     if (tid == 0) {
         s_npairs = 0;
         s_xmin = 0x7f800000u;
@@ -320,12 +336,15 @@ router_certify_kernel(CertifyArgs a) {
             int base = 0;
             if (lane == 0 && m) base = atomicAdd(&s_npairs, __popc(m));
             base = __shfl_sync(0xffffffffu, base, 0);
-            if (cand) pairs[base + __popc(m & ((1u << lane) - 1u))] = (tl << 16) | e;
+            if (cand)
+                pairs[base + __popc(m & ((1u << lane) - 1u))] = (uint16_t)((tl << 11) | e);
         }
-        if (a.extra_row && lane == 0) pairs[atomicAdd(&s_npairs, 1)] = (tl << 16) | E;
+        if (a.extra_row && lane == 0)
+            pairs[atomicAdd(&s_npairs, 1)] = (uint16_t)((tl << 11) | E);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");   /* warps without a token */
     __syncthreads();
+    mark(1);
 
     /* ---- exact chains, one lane per pair ---- */
     const int npairs = s_npairs;
@@ -338,7 +357,7 @@ router_certify_kernel(CertifyArgs a) {
         for (int base = warp * 32; base < npairs; base += RC_CW * 32) {
             const int p = base + lane;
             const bool valid = p < npairs;
-            const int pr = pairs[valid ? p : base], tl = pr >> 16, e = pr & 0xffff;
+            const int pr = pairs[valid ? p : base], tl = pr >> 11, e = pr & 0x7ff;
             const uint16_t *wrow = (e == E) ? a.extra_row : a.w + (size_t)e * K;
             __syncwarp();                     /* the previous round is done with these */
             s_rowptr[warp][lane] = wrow;
@@ -366,6 +385,8 @@ router_certify_kernel(CertifyArgs a) {
 
     /* ---- softmax / top-k on the merged logits, one warp per token ---- */
     __syncthreads();
+    mark(2);
+    if (a.stats && blockIdx.x == 0 && tid == 0) a.stats[6] = (unsigned)npairs;
     for (int tl = warp; tl < nt; tl += RC_THREADS / 32) {
         float *pt = af + (size_t)tl * E;
         for (int e = lane; e < E; e += 32) pt[e] = bf16_round(pt[e]);
@@ -374,11 +395,13 @@ router_certify_kernel(CertifyArgs a) {
         router_softmax_topk(pt, E, a.topk, lane, a.idx_out + (size_t)t * a.topk,
                             a.w_out ? a.w_out + (size_t)t * a.topk : nullptr);
     }
+    __syncthreads();
+    mark(3);
 }
 
 inline size_t router_certify_smem(int E, int K) {
     return (size_t)RC_TT * (K + RC_XPAD) * 4 + (size_t)RC_TT * E * 4 +
-           (size_t)RC_TT * (E + 1) * 4 + (size_t)(E + 1) * 4 + 16 +
+           (size_t)RC_TT * (E + 1) * 2 + 16 + (size_t)(E + 1) * 4 + 16 +
            (size_t)RC_CW * RC_NBUF * 32 * RC_WPITCH;
 }
 

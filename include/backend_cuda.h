@@ -280,6 +280,11 @@ int apus_cuda_fused_timeline(unsigned long long *out, int cap);
  * run since enable (256 per token would be the plain exact router), -1 when
  * not enabled.  APUS_CUDA_ROUTER_CERTIFY=0 selects the plain exact router. */
 long apus_cuda_router_exact_chains(void);
+/* Diagnostic: phase boundaries of the many-token router's first CTA in its
+ * last launch, out[0..3] = start, candidates known, exact chains done, end
+ * (nanoseconds, low 32 bits of the device's global timer), out[4] = chains that
+ * CTA walked.  Returns 0, or -1 when not enabled. */
+int apus_cuda_router_timeline(unsigned int *out);
 /* Diagnostic for the same router (host pointers, synchronous): the fast
  * tensor-core logits of every (token, expert) pair, fast [T,E] fp32, summed
  * over the K slices as the router does, together with the three factors of
