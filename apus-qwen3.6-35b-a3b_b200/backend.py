@@ -62,7 +62,8 @@ SYMBOLS = [
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
     "apus_cuda_layer_refresh", "apus_cuda_layer_upload",
     "apus_cuda_layer_load_slabs",
-    "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev", "apus_cuda_reserve",
+    "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev",
+    "apus_cuda_moe_layer_dev", "apus_cuda_moe_stack_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_path",
     "apus_cuda_last_block_status",
     "apus_cuda_stage_timing", "apus_cuda_last_stage_ms",
@@ -133,6 +134,8 @@ class Backend:
                                                   f32p, f32p, f32p]
         L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
                                               C.POINTER(MoeTrace), vp]
+        L.apus_cuda_moe_layer_dev.argtypes = [vp, vp, vp, vp, sz, C.POINTER(MoeTrace), vp]
+        L.apus_cuda_moe_stack_dev.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, vp]
         L.apus_cuda_reserve.argtypes = [C.POINTER(MoeCfg), sz]
         L.apus_cuda_last_stage_ms.argtypes = [C.POINTER(C.c_float), C.c_int]
         L.apus_cuda_route_dev.argtypes = [vp, vp, sz, vp, vp, vp]
@@ -373,6 +376,24 @@ class Backend:
                                               C.byref(tr) if tr else None,
                                               stream)
         self._check(rc, "apus_cuda_moe_block_dev")
+
+    def moe_layer_dev(self, layer, d_res, d_ln_w, d_res_out, T, stream=None, d_trace=None):
+        """d_res_out = rnd(d_res + moe_block(rmsnorm(d_res, 1 + d_ln_w)))"""
+        tr = None
+        if d_trace:
+            tr = MoeTrace(d_trace.get("idx"), d_trace.get("w"), d_trace.get("routed"),
+                          d_trace.get("shared"), d_trace.get("out"))
+        self._check(self.lib.apus_cuda_moe_layer_dev(
+            layer, d_res, d_ln_w, d_res_out, T, C.byref(tr) if tr else None, stream),
+            "apus_cuda_moe_layer_dev")
+
+    def moe_stack_dev(self, layers, d_res, T, d_ln_w=None, stream=None):
+        """In place over a stack of layers: d_res <- d_res + moe_l(rmsnorm(d_res))."""
+        n = len(layers)
+        arr = (vp * n)(*layers)
+        gains = (vp * n)(*d_ln_w) if d_ln_w is not None else None
+        self._check(self.lib.apus_cuda_moe_stack_dev(arr, gains, n, d_res, T, stream),
+                    "apus_cuda_moe_stack_dev")
 
     def stage_timing(self, enable):
         self._check(self.lib.apus_cuda_stage_timing(1 if enable else 0),

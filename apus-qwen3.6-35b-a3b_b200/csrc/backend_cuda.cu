@@ -1100,7 +1100,7 @@ extern "C" int apus_cuda_reserve(const ApusCudaMoeCfg *cfg, size_t T) {
     block_layout(*cfg, T, nullptr, &b, true);
     g_ctx->cur_capturing = false;
     if (fused_scratch(g_ctx, *cfg)) return 1;
-    return arena_reserve(g_ctx->ws, b.total);
+    return arena_reserve(g_ctx->ws, b.total + al256(T * cfg->hidden * 2) + 256);
 }
 
 static int decode_smem_bytes(const ApusCudaMoeCfg &c, bool down) {
@@ -1174,9 +1174,12 @@ static int run_finalize(Ctx *c, const ApusCudaMoeCfg &cfg, int T,
                         const uint16_t *eo, const int32_t *pos,
                         const uint16_t *rw, const uint16_t *sy,
                         const uint16_t *sgl, uint16_t *d_out,
-                        const ApusCudaMoeTrace *tr, cudaStream_t st) {
+                        const ApusCudaMoeTrace *tr, cudaStream_t st,
+                        const uint16_t *res = nullptr, uint16_t *res_out = nullptr) {
     FinalizeArgs f;
     memset(&f, 0, sizeof f);
+    f.res = res;
+    f.res_out = res_out;
     f.T = T;
     f.H = (int)cfg.hidden;
     f.TK = (int)cfg.top_k;
@@ -1219,9 +1222,15 @@ static int fused_scratch(Ctx *c, const ApusCudaMoeCfg &cfg) {
 }
 
 /* The one-kernel path for a handful of tokens (cooperative launch). */
+/* the two neighbours of the block folded into it (apus_cuda_moe_layer_dev) */
+struct Residual {
+    const uint16_t *res = nullptr, *ln_w = nullptr;
+    uint16_t *res_out = nullptr;
+};
+
 static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
                             uint16_t *d_out, int T, const ApusCudaMoeTrace *tr,
-                            cudaStream_t st) {
+                            cudaStream_t st, const Residual *rz = nullptr) {
     const ApusCudaMoeCfg &cfg = L->cfg;
     const int H = (int)cfg.hidden, I = (int)cfg.moe_inter,
               Is = (int)cfg.shared_inter, E = (int)cfg.experts,
@@ -1239,6 +1248,11 @@ static int run_fused_decode(Ctx *c, ApusCudaLayer *L, const uint16_t *d_ln2,
     a.wmin = L->wmin;
     a.wmin_gate = L->wmin_gate;
     a.x = d_ln2;
+    if (rz) {
+        a.res = rz->res;
+        a.ln_w = rz->ln_w;
+        a.res_out = rz->res_out;
+    }
     a.rtr_w = L->rtr_w; a.exp_gu = L->exp_gu; a.exp_d = L->exp_d;
     a.sh_g = L->sh_g; a.sh_u = L->sh_u; a.sh_d = L->sh_d; a.sh_gate = L->sh_gate;
     a.logits_ws = c->d_df_logits; a.sgl_ws = c->d_df_sgl;
@@ -1288,7 +1302,8 @@ static bool fused_supported(Ctx *c, const ApusCudaMoeCfg &cfg, size_t T) {
 
 static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
                             uint16_t *d_out, size_t T,
-                            const ApusCudaMoeTrace *d_tr, cudaStream_t st) {
+                            const ApusCudaMoeTrace *d_tr, cudaStream_t st,
+                            const Residual *rz = nullptr) {
     Ctx *c = g_ctx;
     const ApusCudaMoeCfg &cfg = L->cfg;
     if (L->e_begin != 0 || L->e_end != cfg.experts)
@@ -1298,13 +1313,30 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     c->df_timeline_valid = false;
     if (fused_supported(c, cfg, T)) {
         c->last_block_path = APUS_CUDA_PATH_FUSED;
-        return run_fused_decode(c, L, d_ln2, d_out, (int)T, d_tr, st);
+        return run_fused_decode(c, L, d_ln2, d_out, (int)T, d_tr, st, rz);
     }
     const bool prefill = (int)T > c->decode_max_t && prefill_supported(cfg);
     BlockBufs b;
     block_layout(cfg, T, nullptr, &b, prefill);
-    if (arena_reserve(c->ws, b.total)) return 1;
+    /* with the neighbours folded in, the normalised input lives behind the
+     * block's own buffers */
+    const size_t ln_bytes = rz ? al256(T * cfg.hidden * 2) + 256 : 0;
+    if (arena_reserve(c->ws, b.total + ln_bytes)) return 1;
     if (block_layout(cfg, T, &c->ws, &b, prefill)) return 1;
+    if (rz) {
+        uint16_t *ln = (uint16_t *)c->ws.take(T * cfg.hidden * 2);
+        if (!ln) return fail("workspace arena too small");
+        const size_t smem = 4 * cfg.hidden * sizeof(float);
+        if (smem > 48 * 1024) {
+            if (smem > (size_t)c->smem_optin) return fail("rmsnorm: hidden too large");
+            CU_OK(cudaFuncSetAttribute(rmsnorm_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
+        rmsnorm_kernel<<<(unsigned)((T + 3) / 4), 128, smem, st>>>(rz->res, rz->ln_w, ln, (int)T,
+                                                                   (int)cfg.hidden);
+        LAUNCHED();
+        d_ln2 = ln;
+    }
     const int Ti = (int)T, E = (int)cfg.experts, H = (int)cfg.hidden,
               TK = (int)cfg.top_k;
     c->n_ev = 0;
@@ -1358,7 +1390,8 @@ static int block_dev_locked(ApusCudaLayer *L, const uint16_t *d_ln2,
     } else {
         if (run_decode_experts(c, L, d_ln2, Ti, TK, 0, b, true, b.eo, st)) return 1;
     }
-    if (run_finalize(c, cfg, Ti, b.eo, nullptr, b.rw, b.sy, b.sgl, d_out, d_tr, st))
+    if (run_finalize(c, cfg, Ti, b.eo, nullptr, b.rw, b.sy, b.sgl, d_out, d_tr, st,
+                     rz ? rz->res : nullptr, rz ? rz->res_out : nullptr))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_FINALIZE, st);
     if (d_tr && d_tr->rtr_idx)
@@ -1389,6 +1422,57 @@ extern "C" int apus_cuda_moe_block_dev(ApusCudaLayer *layer,
         if (!layer->maps) return fail("%s", prefill_last_error());
     }
     return block_dev_locked(layer, d_ln2, d_out, T, d_tr, st);
+}
+
+static int layer_dev(ApusCudaLayer *layer, const uint16_t *d_res, const uint16_t *d_ln_w,
+                     uint16_t *d_res_out, size_t T, const ApusCudaMoeTrace *d_tr,
+                     cudaStream_t st) {
+    if (layer->maps == nullptr && prefill_supported(layer->cfg) &&
+        (int)T > g_ctx->decode_max_t) {
+        layer->maps = prefill_maps_create(layer->cfg, layer->exp_gu, layer->exp_d, layer->sh_g,
+                                          layer->sh_u, layer->sh_d,
+                                          layer->e_end - layer->e_begin);
+        if (!layer->maps) return fail("%s", prefill_last_error());
+    }
+    Residual rz;
+    rz.res = d_res;
+    rz.ln_w = d_ln_w;
+    rz.res_out = d_res_out;
+    return block_dev_locked(layer, nullptr, nullptr, T, d_tr, st, &rz);
+}
+
+extern "C" int apus_cuda_moe_layer_dev(ApusCudaLayer *layer, const uint16_t *d_res,
+                                       const uint16_t *d_ln_w, uint16_t *d_res_out, size_t T,
+                                       const ApusCudaMoeTrace *d_tr, void *stream) {
+    if (!layer || !d_res || !d_res_out || !T) return fail("moe_layer_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(g_ctx, st);
+    if (ord.rc) return 1;
+    return layer_dev(layer, d_res, d_ln_w, d_res_out, T, d_tr, st);
+}
+
+extern "C" int apus_cuda_moe_stack_dev(ApusCudaLayer *const *layers,
+                                       const uint16_t *const *d_ln_w, size_t n_layers,
+                                       uint16_t *d_res, size_t T, void *stream) {
+    if (!layers || !n_layers || !d_res || !T) return fail("moe_stack_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(g_ctx, st);
+    if (ord.rc) return 1;
+    int launches = 0;
+    for (size_t l = 0; l < n_layers; l++) {
+        if (!layers[l]) return fail("moe_stack_dev: layer %zu is null", l);
+        /* in place: a layer reads the stream's row (t, h) only in the thread
+         * that then writes it, after everything else of the layer */
+        if (layer_dev(layers[l], d_res, d_ln_w ? d_ln_w[l] : nullptr, d_res, T, nullptr, st))
+            return 1;
+        launches += g_ctx->last_block_launches;
+    }
+    g_ctx->last_block_launches = launches;
+    return 0;
 }
 
 extern "C" int apus_cuda_stage_timing(int enable) {

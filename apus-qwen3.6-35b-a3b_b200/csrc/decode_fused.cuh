@@ -46,7 +46,13 @@ constexpr int DF_STAGE_BYTES = 8192;    /* a gate+up row pair, or 8 down rows */
 struct FusedArgs {
     int T, H, I, Is, E, TK, stages;
     float wmin, wmin_gate;              /* smallest nonzero |w|: router, shared-gate row */
-    const uint16_t *x;                  /* [T, H] */
+    const uint16_t *x;                  /* [T, H] block input; or, with res set, unused */
+    /* the two steps either side of the block folded in (c/layer.h:386,388):
+     * res [T,H] is the residual stream, the block input is rmsnorm(res, 1 + ln_w)
+     * (c/attn.h:175-186, every CTA computes it for itself: 4 KB per token and
+     * one sequential chain per token, no exchange), and res_out = rnd(res + moe_out) */
+    const uint16_t *res, *ln_w;
+    uint16_t *res_out;
     const uint16_t *rtr_w, *exp_gu, *exp_d, *sh_g, *sh_u, *sh_d, *sh_gate;
     /* global scratch owned by the backend */
     float *logits_ws;                   /* [DF_MAX_T][E] */
@@ -189,6 +195,42 @@ __device__ __forceinline__ void df_down8_n(int nt, const uint16_t *ws,
 }
 
 
+/* xs[t][:] = rmsnorm(res[t][:], 1 + ln_w) for t < T, bit for bit the engine's
+ * (c/attn.h:175-186): the sum of squares is one ascending fp32 chain (lane 0 of
+ * warp t walks it over the row staged in shared memory, operands converted on
+ * the fly: the dependent add is the critical path), then y = rnd((x*rs)*(1+w)).
+ * All threads call it; ends with a CTA barrier. */
+__device__ __forceinline__ void df_rmsnorm_to_smem(const FusedArgs &a, uint16_t *xs) {
+    const int T = a.T, H = a.H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int c = tid; c < T * (H / 8); c += DF_THREADS)
+        reinterpret_cast<uint4 *>(xs)[c] = ldg16(a.res + (size_t)c * 8);
+    __syncthreads();
+    if (warp < T) {
+        uint16_t *row = xs + (size_t)warp * H;
+        float ss = 0.0f;
+        if (lane == 0) {
+            const uint4 *r4 = reinterpret_cast<const uint4 *>(row);
+#pragma unroll 2
+            for (int i = 0; i < H / 8; i++) {
+                const uint4 v = r4[i];
+                const float f[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
+                                    bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+#pragma unroll
+                for (int j = 0; j < 8; j++) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+            }
+        }
+        ss = __shfl_sync(0xffffffffu, ss, 0);
+        const float rs =
+            __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), 1e-6f)));
+        for (int i = lane; i < H; i += 32) {
+            const float g = __fadd_rn(1.0f, a.ln_w ? bf16_f32(__ldg(a.ln_w + i)) : 0.0f);
+            row[i] = bf16_bits(__fmul_rn(__fmul_rn(bf16_f32(row[i]), rs), g));
+        }
+    }
+    __syncthreads();
+}
+
 /* A warp's private ring of bulk copies.  issue() is called by lane 0 only. */
 struct WarpRing {
     unsigned char *base;     /* stages * DF_STAGE_BYTES */
@@ -289,8 +331,12 @@ decode_fused_kernel(FusedArgs a) {
             }
         }
         unsigned int xmin = 0x7f800000u;
+        /* with the norm folded in, the block input is computed here (every CTA
+         * does, the router CTAs first of all: their chains start from it) */
+        if (a.res) df_rmsnorm_to_smem(a, xs);
         for (int c = tid; c < T * (H / 8); c += DF_THREADS) {
-            const uint4 v = ldg16(a.x + (size_t)c * 8);
+            const uint4 v = a.res ? reinterpret_cast<const uint4 *>(xs)[c]
+                                  : ldg16(a.x + (size_t)c * 8);
             const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
             const int tt = c / (H / 8), cc = c - tt * (H / 8);
             float4 *d = reinterpret_cast<float4 *>(xf + (size_t)tt * xpitch + cc * 8);
@@ -347,8 +393,12 @@ decode_fused_kernel(FusedArgs a) {
 
     df_mark(a, 1);                          /* router chains done (router CTAs) */
     /* ---------------- phase A: tokens to shared; shared gate/up ---------------- */
-    for (int c = tid; c < T * (H / 8); c += DF_THREADS)
-        reinterpret_cast<uint4 *>(xs)[c] = ldg16(a.x + (size_t)c * 8);
+    if (a.res) {
+        if (!is_router) df_rmsnorm_to_smem(a, xs);    /* router CTAs hold it already */
+    } else {
+        for (int c = tid; c < T * (H / 8); c += DF_THREADS)
+            reinterpret_cast<uint4 *>(xs)[c] = ldg16(a.x + (size_t)c * 8);
+    }
     __syncthreads();
     {
         const int lo = (int)((long)Is * blockIdx.x / G);
@@ -648,7 +698,9 @@ decode_fused_kernel(FusedArgs a) {
             bf16_round(__fmul_rn(bf16_f32(ytab[(DF_MAX_A + t) * 16 + hl]), sgat));
         const uint16_t o = bf16_bits(__fadd_rn(routed, shared));
         const size_t at = (size_t)t * H + (size_t)b_lo * 8 + hl;
-        a.out[at] = o;
+        if (a.out) a.out[at] = o;
+        if (a.res_out)                          /* c/layer.h:230-234,388 */
+            a.res_out[at] = bf16_bits(__fadd_rn(bf16_f32(__ldg(a.res + at)), bf16_f32(o)));
         if (a.tr_out) a.tr_out[at] = o;
         if (a.tr_routed) a.tr_routed[at] = bf16_bits(routed);
         if (a.tr_shared) a.tr_shared[at] = bf16_bits(shared);

@@ -422,8 +422,12 @@ struct FinalizeArgs {
     const uint16_t *rw;      /* [T, TK] */
     const uint16_t *sy;      /* [T, H] (NULL: no shared expert term) */
     const uint16_t *sgl;     /* [T] shared-gate logits */
-    uint16_t *out;           /* [T, H] */
+    uint16_t *out;           /* [T, H] (optional when res_out is set) */
     uint16_t *tr_routed, *tr_shared, *tr_out;   /* optional */
+    /* the residual add after the block folded in (c/layer.h:230-234,388):
+     * res_out = rnd(res + rnd(moe_out)) */
+    const uint16_t *res;
+    uint16_t *res_out;
 };
 
 __global__ void __launch_bounds__(256)
@@ -484,9 +488,19 @@ moe_finalize_kernel(FinalizeArgs a) {
         for (int j = 0; j < 8; j++)
             outv[j] = __fadd_rn(routed[j], shared[j]);
         const size_t o = (size_t)t * a.H + (size_t)c * 8;
-        *reinterpret_cast<uint4 *>(a.out + o) =
-            make_uint4(pack_bf16(outv[0], outv[1]), pack_bf16(outv[2], outv[3]),
-                       pack_bf16(outv[4], outv[5]), pack_bf16(outv[6], outv[7]));
+        if (a.out)
+            *reinterpret_cast<uint4 *>(a.out + o) =
+                make_uint4(pack_bf16(outv[0], outv[1]), pack_bf16(outv[2], outv[3]),
+                           pack_bf16(outv[4], outv[5]), pack_bf16(outv[6], outv[7]));
+        if (a.res_out) {
+            float r[8];
+            unpack8(ldg16(a.res + o), r);
+#pragma unroll
+            for (int j = 0; j < 8; j++) r[j] = __fadd_rn(r[j], bf16_round(outv[j]));
+            *reinterpret_cast<uint4 *>(a.res_out + o) =
+                make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]),
+                           pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+        }
         if (a.tr_out)
             *reinterpret_cast<uint4 *>(a.tr_out + o) = make_uint4(
                 pack_bf16(outv[0], outv[1]), pack_bf16(outv[2], outv[3]),

@@ -416,6 +416,11 @@ def measure_stack(env, layers, T, chain, steps, warmup, sustain_s, seed,
     def one_pass(trace_uniq=None, timing=None):
         if chain:
             d_h.copy_(d_x)
+        if chain and trace_uniq is None and timing is None:
+            # the MoE half of the step as ONE call: norm and residual add are
+            # folded into each layer's kernels (apus_cuda_moe_stack_dev)
+            be.moe_stack_dev(layers, d_h.data_ptr(), T, stream=sp)
+            return
         for l, lay in enumerate(layers):
             tr = {"idx": d_idx.data_ptr()} if trace_uniq is not None else None
             if chain:
@@ -438,8 +443,12 @@ def measure_stack(env, layers, T, chain, steps, warmup, sustain_s, seed,
     uniq = []
     one_pass(trace_uniq=uniq)
     torch.cuda.synchronize()
-    launches_per_layer = be.last_block_launches() + (2 if chain else 0)
     fused = be.last_block_launches() == 1
+    launches_per_layer = be.last_block_launches() + (2 if chain else 0)
+    if chain:
+        one_pass()
+        torch.cuda.synchronize()
+        launches_per_layer = be.last_block_launches() // L
     step, mode = capture(torch, stream, one_pass, env["no_graph"])
     for _ in range(max(3, warmup)):
         step()

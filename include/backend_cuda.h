@@ -238,6 +238,26 @@ int apus_cuda_layer_load_slabs(ApusCudaLayer *layer, const char *container_dir,
 int apus_cuda_moe_block_dev(ApusCudaLayer *layer, const uint16_t *d_ln2,
                             uint16_t *d_out, size_t T,
                             const ApusCudaMoeTrace *d_tr, void *stream);
+/* The block with the two steps either side of it folded in (c/layer.h:386-388):
+ *     d_res_out = rnd(d_res + moe_block(rmsnorm(d_res, gain 1 + d_ln_w)))
+ * d_res [T,H] is the residual stream after the attention half, d_ln_w [H] the
+ * post-attention norm's gain offsets (NULL = zero).  Norm and add are bit for
+ * bit the engine's (c/attn.h:175-186, c/layer.h:230-234).  Up to
+ * APUS_CUDA_FUSED_MAX_T tokens all of it is the one cooperative kernel (every
+ * CTA normalises the tokens for itself; the add is in the combine): no extra
+ * launch.  Above, the norm is one launch of its own and the add is part of the
+ * combine kernel.  d_res_out may equal d_res.  d_tr->moe_out receives the
+ * block's own output. */
+int apus_cuda_moe_layer_dev(ApusCudaLayer *layer, const uint16_t *d_res,
+                            const uint16_t *d_ln_w, uint16_t *d_res_out, size_t T,
+                            const ApusCudaMoeTrace *d_tr, void *stream);
+/* n_layers of the above back to back on one residual stream, in place:
+ * d_res <- d_res + moe_l(rmsnorm(d_res, 1 + d_ln_w[l])) for l = 0 .. n_layers-1
+ * (d_ln_w NULL, or an entry NULL = zero gain offsets).  The MoE half of a
+ * decode step over a stack of layers as one call (and one CUDA graph when
+ * captured). */
+int apus_cuda_moe_stack_dev(ApusCudaLayer *const *layers, const uint16_t *const *d_ln_w,
+                            size_t n_layers, uint16_t *d_res, size_t T, void *stream);
 /* Grow the workspace arena for blocks of up to T tokens of this shape (and
  * allocate the one-kernel path's scratch for it). */
 int apus_cuda_reserve(const ApusCudaMoeCfg *c, size_t T);
