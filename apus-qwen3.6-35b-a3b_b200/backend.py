@@ -61,7 +61,7 @@ SYMBOLS = [
     "apus_cuda_moe_block", "apus_cuda_block_hooks", "apus_cuda_layer_create",
     "apus_cuda_layer_destroy", "apus_cuda_layer_tensor",
     "apus_cuda_layer_refresh", "apus_cuda_layer_upload",
-    "apus_cuda_layer_load_slabs",
+    "apus_cuda_layer_load_slabs", "apus_cuda_register_layer_slabs",
     "apus_cuda_debug_fast_logits", "apus_cuda_moe_block_dev",
     "apus_cuda_moe_layer_dev", "apus_cuda_moe_stack_dev", "apus_cuda_reserve",
     "apus_cuda_last_block_launches", "apus_cuda_last_block_path",
@@ -130,6 +130,8 @@ class Backend:
         L.apus_cuda_layer_refresh.argtypes = [vp]
         L.apus_cuda_layer_upload.argtypes = [vp, C.c_int, u16p, sz, sz]
         L.apus_cuda_layer_load_slabs.argtypes = [vp, C.c_char_p, C.c_int]
+        L.apus_cuda_register_layer_slabs.argtypes = [C.POINTER(MoeCfg), C.POINTER(MoeW),
+                                                     C.c_char_p, C.c_int]
         L.apus_cuda_debug_fast_logits.argtypes = [u16p, u16p, sz, sz, sz, f32p,
                                                   f32p, f32p, f32p]
         L.apus_cuda_moe_block_dev.argtypes = [vp, vp, vp, sz,
@@ -279,7 +281,7 @@ class Backend:
         T, H = ln2.shape
         TK = cfg["top_k"]
         c = MoeCfg.from_dict(cfg)
-        w = MoeW(*[W[k].ctypes.data for k in
+        w = MoeW(*[W[k].ctypes.data if W.get(k) is not None else None for k in
                    ("rtr_w", "exp_gu", "exp_d", "sh_g", "sh_u", "sh_d",
                     "sh_gate")])
         out = np.zeros((T, H), np.uint16)
@@ -344,6 +346,16 @@ class Backend:
         self._check(self.lib.apus_cuda_layer_load_slabs(
             layer, str(container_dir).encode(), layer_index),
             "apus_cuda_layer_load_slabs")
+
+    def register_layer_slabs(self, cfg, W, container_dir, layer_index):
+        """Tiered mode: W holds router / shared expert / gate host arrays (the
+        rtr_w address is the key), the routed experts come from the container."""
+        c = MoeCfg.from_dict(cfg)
+        w = MoeW(W["rtr_w"].ctypes.data, None, None, W["sh_g"].ctypes.data,
+                 W["sh_u"].ctypes.data, W["sh_d"].ctypes.data, W["sh_gate"].ctypes.data)
+        self._check(self.lib.apus_cuda_register_layer_slabs(
+            C.byref(c), C.byref(w), str(container_dir).encode(), layer_index),
+            "apus_cuda_register_layer_slabs")
 
     def debug_fast_logits(self, x, wg):
         """(fast [T,E] f32, xnorm [T], wnorm [E+1], cbound) of the many-token

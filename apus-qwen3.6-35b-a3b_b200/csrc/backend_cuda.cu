@@ -1585,8 +1585,8 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
                                    uint16_t *moe_out, size_t T,
                                    const ApusCudaMoeTrace *tr) {
     if (cfg_check(cfg)) return 1;
-    if (!w || !w->rtr_w || !w->exp_gu || !w->exp_d || !w->sh_g || !w->sh_u ||
-        !w->sh_d || !w->sh_gate || !ln2 || !moe_out || !T)
+    if (!w || !w->rtr_w || !w->sh_g || !w->sh_u || !w->sh_d || !w->sh_gate || !ln2 ||
+        !moe_out || !T)
         return fail("moe_block: null argument or T == 0");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
@@ -1598,6 +1598,11 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
         if (memcmp(&L->cfg, cfg, sizeof *cfg) != 0)
             return fail("moe_block: layer key reused with a different shape");
     } else {
+        /* experts as host arrays, unless the layer was registered from the
+         * weight container (apus_cuda_register_layer_slabs) */
+        if (!w->exp_gu || !w->exp_d)
+            return fail("moe_block: exp_gu / exp_d are NULL and the layer is not "
+                        "registered (apus_cuda_register_layer_slabs)");
         if (apus_cuda_layer_create(cfg, w, 0, cfg->experts, &L)) return 1;
         c->layers.emplace(w->rtr_w, L);
     }
@@ -1648,6 +1653,34 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
     return 0;
 }
 
+
+/* A layer whose routed experts never exist as host arrays (the engine's tiered
+ * mode leaves exp_gu / exp_d NULL and resolves experts from its store,
+ * c/model.h:499-503, c/cache.h:1498-1545): registered under the residency key
+ * w->rtr_w with the experts read from the weight container, then served by
+ * apus_cuda_moe_block like any other layer. */
+extern "C" int apus_cuda_register_layer_slabs(const ApusCudaMoeCfg *cfg, const ApusCudaMoeW *w,
+                                              const char *container_dir, int layer_index) {
+    if (cfg_check(cfg)) return 1;
+    if (!w || !w->rtr_w || !w->sh_g || !w->sh_u || !w->sh_d || !w->sh_gate || !container_dir)
+        return fail("register_layer_slabs: null argument");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    if (c->layers.count(w->rtr_w)) return 0;           /* already resident */
+    /* router, shared expert and gate from the host; expert tensors allocated only */
+    ApusCudaMoeW w0 = *w;
+    w0.exp_gu = nullptr;
+    w0.exp_d = nullptr;
+    ApusCudaLayer *L = nullptr;
+    if (apus_cuda_layer_create(cfg, &w0, 0, cfg->experts, &L)) return 1;
+    if (apus_cuda_layer_load_slabs(L, container_dir, layer_index)) {
+        layer_free(L);
+        return 1;
+    }
+    c->layers.emplace(w->rtr_w, L);
+    return 0;
+}
 
 /* ------------------------------------------------------------------------ */
 /* expert parallelism                                                        */

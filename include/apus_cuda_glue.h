@@ -47,6 +47,12 @@ __attribute__((weak)) uint64_t apus_cuda_launches(void) { return 0; }
 __attribute__((weak)) const char *apus_cuda_last_error(void) {
     return "cuda backend not compiled in";
 }
+__attribute__((weak)) int apus_cuda_moe_route_topn(const uint16_t *x, const uint16_t *wg,
+                                                   int32_t *idx, size_t n, size_t E,
+                                                   size_t K) {
+    (void)x; (void)wg; (void)idx; (void)n; (void)E; (void)K;
+    return 1;
+}
 __attribute__((weak)) ApusCudaBlockHooks apus_cuda_block_hooks;
 #endif
 
@@ -77,6 +83,28 @@ static inline int apus_layer_moe_cuda(const ApusLayerCfg *c, const ApusLayerW *w
         exit(2);                      /* hard error: no silent CPU path */
     }
     return 0;
+}
+
+/* The tiered mirrors (c/cache.h:1498 apus_store_moe, :1659 apus_store_prefill)
+ * call this on their first line, exactly as the eager functions call the shim
+ * above: in tiered mode w->exp_gu / exp_d are NULL, and the layer must have been
+ * registered once at load with apus_cuda_register_layer_slabs (experts read from
+ * the container the store would have streamed from).  rtr_idx, when the store's
+ * router_actual hook wants the selection (c/cache.h:1510-1512), comes back
+ * through tr.  Returns 1 when the block hook is not installed. */
+static inline int apus_store_moe_cuda(const ApusLayerCfg *c, const ApusLayerW *w,
+                                      const uint16_t *ln2, uint16_t *moe_out, size_t T,
+                                      ApusLayerTrace *tr) {
+    return apus_layer_moe_cuda(c, w, ln2, moe_out, T, tr, 0);
+}
+
+/* The prefetch predictor's deeper truncation of the router (c/pilot.h:280-284):
+ * ids of the first n experts in selection order.  Returns 0 when the backend
+ * produced them, 1 otherwise (the caller then runs apus_moe_route_topn). */
+static inline int apus_moe_route_topn_cuda(const uint16_t *x, const uint16_t *wg,
+                                           int32_t *idx, size_t n, size_t E, size_t K) {
+    if (!apus_cuda_is_enabled()) return 1;
+    return apus_cuda_moe_route_topn(x, wg, idx, n, E, K) ? 1 : 0;
 }
 
 #endif /* APUS_CUDA_GLUE_H */

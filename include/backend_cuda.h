@@ -147,11 +147,23 @@ typedef struct {
 /* Host-pointer block operator: argument meaning identical to
  * apus_layer_moe_batch (c/layer.h:570-573).  The layer's weights are uploaded
  * on first sight of w->rtr_w (the residency key) and stay in HBM until
- * apus_cuda_disable.  Synchronous: moe_out and the trace rows are complete on
+ * apus_cuda_disable (exp_gu / exp_d may be NULL for a layer registered with
+ * apus_cuda_register_layer_slabs).  Synchronous: moe_out and the trace rows are complete on
  * return.  Returns 0, or nonzero with apus_cuda_last_error() set. */
 int apus_cuda_moe_block(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
                         const uint16_t *ln2, uint16_t *moe_out, size_t T,
                         const ApusCudaMoeTrace *tr);
+
+/* The engine's tiered mode keeps no expert arrays on the host (exp_gu / exp_d
+ * are NULL, c/model.h:499-503) and resolves experts from its NVMe store inside
+ * the mirrors apus_store_moe / apus_store_prefill (c/cache.h:1498-1545,
+ * 1659-1779).  With every expert resident in HBM that store has nothing left to
+ * do: register each layer once — router, shared expert and gate from the host
+ * pointers of w, the routed experts read from the weight container's slabs
+ * (apus_cuda_layer_load_slabs) — and apus_cuda_moe_block then serves it under
+ * the same key w->rtr_w with exp_gu / exp_d NULL.  Idempotent per key. */
+int apus_cuda_register_layer_slabs(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
+                                   const char *container_dir, int layer_index);
 
 /* Second hook table, for the block operator.  Kept apart from the engine's
  * three-slot table so that table's layout is untouched.  The engine-side

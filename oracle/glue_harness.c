@@ -21,6 +21,8 @@
  *       (launch counter moved) and whether it is bitwise the scalar anchor.
  *       Under APUS_CUDA_DENSE_MB=1 a large weight makes the hook return
  *       nonzero and the engine falls back (c/backend_metal.h:65-67).
+ *   glue_test topn E K n the predictor's router truncation (c/pilot.h:280-284)
+ *       through apus_moe_route_topn_cuda against the engine's apus_moe_route_topn.
  *   glue_test stubs      (glue_test_cpu) apus_cuda_enable must fail with
  *       "not compiled in" and the shim must return 1.
  */
@@ -177,6 +179,25 @@ static int cmd_budget(int argc, char **argv) {
     return 0;
 }
 
+/* the predictor's router truncation through the glue against the engine's own */
+static int cmd_topn(int argc, char **argv) {
+    if (argc < 5) return 2;
+    const size_t E = (size_t)atol(argv[2]), K = (size_t)atol(argv[3]), n = (size_t)atol(argv[4]);
+    char err[256] = "";
+    if (apus_cuda_enable(err, sizeof err)) {
+        printf("{\"error\": \"%s\"}\n", err);
+        return 1;
+    }
+    uint16_t *wg = fill(E * K, APUS_SYNTH_RTR_W, 0.05), *x = fill(K, APUS_SYNTH_X, 1.0);
+    int32_t a[64], b[64];
+    apus_moe_route_topn(x, wg, a, n, E, K);
+    const int rc = apus_moe_route_topn_cuda(x, wg, b, n, E, K);
+    printf("{\"rc\": %d, \"equal\": %d, \"launches\": %llu}\n", rc,
+           !memcmp(a, b, n * sizeof(int32_t)), (unsigned long long)apus_cuda_launches());
+    apus_cuda_disable();
+    return 0;
+}
+
 static int cmd_stubs(void) {
     char err[256] = "";
     const int rc = apus_cuda_enable(err, sizeof err);
@@ -184,9 +205,13 @@ static int cmd_stubs(void) {
     ApusLayerW w;
     memset(&c, 0, sizeof c);
     memset(&w, 0, sizeof w);
-    const int shim = apus_layer_moe_cuda(&c, &w, NULL, NULL, 1, NULL, 0);
-    printf("{\"enable_rc\": %d, \"err\": \"%s\", \"shim_rc\": %d, \"enabled\": %d}\n",
-           rc, err, shim, apus_cuda_is_enabled());
+    const int shim = apus_layer_moe_cuda(&c, &w, NULL, NULL, 1, NULL, 0) +
+                     apus_store_moe_cuda(&c, &w, NULL, NULL, 1, NULL) - 1;
+    int32_t ids[8];
+    const int topn = apus_moe_route_topn_cuda(NULL, NULL, ids, 8, 16, 16);
+    printf("{\"enable_rc\": %d, \"err\": \"%s\", \"shim_rc\": %d, \"topn_rc\": %d, "
+           "\"enabled\": %d}\n",
+           rc, err, shim, topn, apus_cuda_is_enabled());
     return 0;
 }
 
@@ -196,5 +221,6 @@ int main(int argc, char **argv) {
     if (!strcmp(argv[1], "slots")) return cmd_slots();
     if (!strcmp(argv[1], "budget")) return cmd_budget(argc, argv);
     if (!strcmp(argv[1], "stubs")) return cmd_stubs();
+    if (!strcmp(argv[1], "topn")) return cmd_topn(argc, argv);
     return 2;
 }

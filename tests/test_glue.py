@@ -46,7 +46,7 @@ def test_cpu_only_binary_links_and_says_not_compiled_in():
     rc, j, _ = run(GLUE_CPU, "stubs")
     assert rc == 0
     assert j["enable_rc"] == -1 and "not compiled in" in j["err"]
-    assert j["shim_rc"] == 1 and j["enabled"] == 0
+    assert j["shim_rc"] == 1 and j["topn_rc"] == 1 and j["enabled"] == 0
 
 
 def test_cuda_binary_without_a_device_fails_loudly():
@@ -99,3 +99,12 @@ def test_budget_exhausted_hook_declines_and_the_engine_falls_back():
     assert rc == 0, err
     assert j["hook_took_it"] == 0 and j["bitwise_scalar"] == 1
     assert j["bytes_resident"] == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("E,K,n", [(16, 128, 4), (256, 2048, 8), (256, 2048, 12)])
+def test_predictor_router_truncation_through_the_glue(E, K, n):
+    """c/pilot.h:280-284: the first n expert ids in selection order."""
+    rc, j, err = run(GLUE, "topn", E, K, n)
+    assert rc == 0, err
+    assert j["rc"] == 0 and j["equal"] == 1 and j["launches"] > 0

@@ -100,3 +100,27 @@ def test_bad_containers_are_refused(gpu, be, synth, tmp_path, kind):
     assert want in msg, msg
     # the backend stays usable
     gpu.layer_destroy(lay)
+
+
+def test_tiered_layer_registered_from_the_container(gpu, orc, be, synth, tmp_path):
+    """The engine's tiered mode has no expert arrays on the host; the layer is
+    registered once from the container and the host-pointer block call then
+    serves it under the same key with exp_gu / exp_d NULL: same result, bit for
+    bit, as the eager call with the arrays."""
+    Ws, layers = _layers(be, synth, 1)
+    W = Ws[0]
+    write_container(tmp_path, layers, CFG["hidden"], CFG["moe_inter"])
+    x = synth.host_x(be, 33, CFG["hidden"], seed=9)
+    eager = gpu.moe_block(CFG, W, x)
+    # a second set of host pointers for the non-expert tensors = a second key
+    Wt = {k: (v.copy() if k not in ("exp_gu", "exp_d") else None) for k, v in W.items()}
+    with pytest.raises(Exception) as ei:
+        gpu.moe_block(CFG, Wt, x)
+    assert "register_layer_slabs" in str(ei.value)
+    gpu.register_layer_slabs(CFG, Wt, tmp_path, 0)
+    gpu.register_layer_slabs(CFG, Wt, tmp_path, 0)        # idempotent
+    tiered = gpu.moe_block(CFG, Wt, x)
+    for k in ("idx", "w", "routed", "shared", "out"):
+        assert np.array_equal(eager[k], tiered[k]), k
+    exp = orc.moe_block(CFG, W, x)
+    assert np.array_equal(tiered["idx"], exp["idx"])
