@@ -77,6 +77,7 @@ SYMBOLS = [
     "apus_cuda_ep_push_dev", "apus_cuda_ep_wait_dev",
     "apus_cuda_ep_window_experts_dev", "apus_cuda_ep_return_dev",
     "apus_cuda_ep_shared_dev", "apus_cuda_ep_combine_dev",
+    "apus_cuda_ep_publish_dev", "apus_cuda_ep_pull_experts_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
     "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_cuda_bf16_gemv_dev", "apus_synth_fill_host",
@@ -164,6 +165,8 @@ class Backend:
         L.apus_cuda_ep_window_experts_dev.argtypes = [vp, vp, vp]
         L.apus_cuda_ep_return_dev.argtypes = [vp, C.c_uint32, vp]
         L.apus_cuda_ep_shared_dev.argtypes = [vp, vp, sz, vp, vp]
+        L.apus_cuda_ep_publish_dev.argtypes = [vp, vp, vp, sz, C.c_uint32, vp]
+        L.apus_cuda_ep_pull_experts_dev.argtypes = [vp, vp, C.c_uint32, vp]
         L.apus_cuda_ep_combine_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
@@ -537,6 +540,16 @@ class Backend:
     def ep_return_dev(self, w, epoch, stream=None):
         self._check(self.lib.apus_cuda_ep_return_dev(w, epoch, stream),
                     "apus_cuda_ep_return_dev")
+
+    def ep_publish_dev(self, w, d_x, d_idx, T, epoch, stream=None):
+        self._check(self.lib.apus_cuda_ep_publish_dev(w, d_x, d_idx, T, epoch,
+                                                      stream),
+                    "apus_cuda_ep_publish_dev")
+
+    def ep_pull_experts_dev(self, w, layer, epoch, stream=None):
+        self._check(self.lib.apus_cuda_ep_pull_experts_dev(w, layer, epoch,
+                                                           stream),
+                    "apus_cuda_ep_pull_experts_dev")
 
     def ep_shared_dev(self, layer, d_x, T, d_sy, stream=None):
         self._check(self.lib.apus_cuda_ep_shared_dev(layer, d_x, T, d_sy,

@@ -1769,11 +1769,10 @@ extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
     return 0;
 }
 
-extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
-                                     const int32_t *d_e, size_t R,
-                                     uint16_t *d_y, void *stream) {
-    if (!L || !d_x || !d_e || !d_y) return fail("experts_dev: bad args");
-    if (!R) return 0;
+/* peer (expert parallelism, pull form): the rows are loaded from and the
+ * outputs stored to other GPUs' memory; d_x and d_y are then unused. */
+static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_e, size_t R,
+                        uint16_t *d_y, void *stream, const PeerRows *peer) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
@@ -1786,12 +1785,19 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     ApusCudaMoeCfg cx = L->cfg;       /* the shape dispatch and tiling see */
     cx.experts = ne;
     cx.top_k = 1;
-    const bool prefill = (int)R > c->decode_max_t && prefill_supported(L->cfg);
+    const bool prefill = ((int)R > c->decode_max_t || peer) && prefill_supported(L->cfg);
+    if (peer && !prefill)
+        return fail("experts over peer memory need the tensor-core path (hidden and "
+                    "moe_inter multiples of 128, shared_inter == moe_inter)");
     if (prefill && ensure_maps(L)) return 1;
     BlockBufs b;
     block_layout(cx, R, nullptr, &b, prefill);
     if (arena_reserve(c->ws, b.total)) return 1;
     if (block_layout(cx, R, &c->ws, &b, prefill)) return 1;
+    if (peer) {
+        d_x = b.xg;          /* a valid local address for the unused token maps */
+        d_y = b.eo;
+    }
     if (prefill) {
         b.d.grp_expert = nullptr;
         b.d.grp_first = nullptr;
@@ -1805,14 +1811,20 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     TilePlan plan;
     memset(&plan, 0, sizeof plan);
     if (prefill && !pair) plan = prefill_tile_plan(cx, (int)R, false, (int)R, b.tiles);
+    /* stage marks (apus_cuda_stage_timing): dispatch, gather, gate_up, down */
+    c->n_ev = 0;
+    stage_mark(c, -1, st);
+    g_mark_stream = st;
     if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
                         DispatchKey{(int)L->e_begin, 1}, prefill && !pair ? &plan : nullptr))
         return 1;
+    stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (pair) {
         const int before = c->last_block_launches;
         if (run_pair_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x, (int)R, (int)R,
-                             1, false, b.d, b.xg, b.act, b.sa, d_y, b.sy, b.tiles,
-                             c->d_status, st, &c->last_block_launches, nullptr))
+                             peer ? (int)L->cfg.top_k : 1, false, b.d, b.xg, b.act, b.sa, d_y,
+                             b.sy, b.tiles, c->d_status, st, &c->last_block_launches, mark_cb,
+                             peer))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
         return 0;
@@ -1820,15 +1832,23 @@ extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
     if (prefill) {
         const int before = c->last_block_launches;
         if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x,
-                                (int)R, (int)R, 1, false, b.d, b.xg, b.act, b.sa,
-                                d_y, b.sy, b.tiles, c->d_status, st,
-                                &c->last_block_launches, nullptr,
-                                plan.on ? &plan : nullptr))
+                                (int)R, (int)R, peer ? (int)L->cfg.top_k : 1, false, b.d,
+                                b.xg, b.act, b.sa, d_y, b.sy, b.tiles, c->d_status, st,
+                                &c->last_block_launches, mark_cb,
+                                plan.on ? &plan : nullptr, peer))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
         return 0;
     }
     return run_decode_experts(c, L, d_x, (int)R, 1, 0, b, false, d_y, st);
+}
+
+extern "C" int apus_cuda_experts_dev(ApusCudaLayer *L, const uint16_t *d_x,
+                                     const int32_t *d_e, size_t R,
+                                     uint16_t *d_y, void *stream) {
+    if (!L || !d_x || !d_e || !d_y) return fail("experts_dev: bad args");
+    if (!R) return 0;
+    return experts_core(L, d_x, d_e, R, d_y, stream, nullptr);
 }
 
 extern "C" int apus_cuda_ep_finish_dev(ApusCudaLayer *L, const uint16_t *d_x,
@@ -1890,6 +1910,9 @@ struct ApusCudaEpWindow {
     int32_t *uh;                     /* dispatch scratch */
     unsigned int *counter;           /* [2] finished-CTA counters */
     uint32_t *d_epoch;               /* step number for calls made with epoch 0 */
+    int32_t *pulled;                 /* [n*cap] ids of the resident experts, by flat slot */
+    unsigned long long *tbl;         /* [2][EPW_MAX_RANKS] addresses of every rank's xs, by */
+    bool tbl_ready;
 };
 
 extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t H,
@@ -1903,13 +1926,14 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     ApusCudaEpWindow *w = new ApusCudaEpWindow();
     memset(w, 0, sizeof *w);
     const size_t cap = max_tokens * topk;
-    w->l = epw_layout((int)n_ranks, (int)cap, (int)H);
+    w->l = epw_layout((int)n_ranks, (int)cap, (int)H, (int)max_tokens);
     w->me = (int)rank;
     w->topk = (int)topk;
     w->E = (int)E;
     const size_t A = cap;
     const size_t local = n_ranks * cap * H * 2 + (n_ranks + 1) * 4 + A * 4 +
-                         n_ranks * 4 + dispatch_scratch_bytes(A, n_ranks) + 8192;
+                         n_ranks * 4 + n_ranks * cap * 4 + 2 * EPW_MAX_RANKS * 8 +
+                         dispatch_scratch_bytes(A, n_ranks) + 8192;
     unsigned char *loc = nullptr;
     if (cudaMalloc(&w->base, w->l.total) != cudaSuccess ||
         cudaMalloc(&loc, local) != cudaSuccess) {
@@ -1928,6 +1952,8 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     w->counts = (int32_t *)(loc + o);    o = up(o + n_ranks * 4);
     w->counter = (unsigned int *)(loc + o); o = up(o + 8);
     w->d_epoch = (uint32_t *)(loc + o);  o = up(o + 4);
+    w->pulled = (int32_t *)(loc + o);    o = up(o + n_ranks * cap * 4);
+    w->tbl = (unsigned long long *)(loc + o); o = up(o + 2 * EPW_MAX_RANKS * 8);
     w->uh = (int32_t *)(loc + o);
     w->peers.base[rank] = w->base;
     CU_OK(cudaDeviceSynchronize());
@@ -1968,6 +1994,7 @@ extern "C" int apus_cuda_ep_window_attach(ApusCudaEpWindow *w, size_t peer,
     CU_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
     w->peers.base[peer] = (unsigned char *)p;
     w->opened[peer] = true;
+    w->tbl_ready = false;
     return 0;
 }
 
@@ -1976,6 +2003,7 @@ extern "C" int apus_cuda_ep_window_attach_local(ApusCudaEpWindow *w, size_t peer
     if (!w || !other || peer >= (size_t)w->l.n || other->l.total != w->l.total)
         return fail("ep_window_attach_local: bad args");
     w->peers.base[peer] = other->base;
+    w->tbl_ready = false;
     return 0;
 }
 
@@ -2066,6 +2094,73 @@ extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
     return 0;
 }
 
+/* ---- the pull form of the step (ep_window.cuh) ---- */
+extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
+                                        const int32_t *d_idx, size_t T, uint32_t epoch,
+                                        void *stream) {
+    if (epw_ready(w, "ep_publish_dev")) return 1;
+    if (!d_x || !d_idx || !T || T > (size_t)w->l.tokens)
+        return fail("ep_publish_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    c->last_block_launches = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    Ordered ord(c, st);
+    if (ord.rc) return 1;
+    long total = (long)T * (w->l.H / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > c->sm_count * 4) blocks = c->sm_count * 4;
+    launch_k(epw_publish_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx, (int)T, w->topk,
+             w->l, w->peers, w->me, epoch, w->counter, w->d_epoch);
+    LAUNCHED();
+    return 0;
+}
+
+extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *L,
+                                             uint32_t epoch, void *stream) {
+    if (epw_ready(w, "ep_pull_experts_dev")) return 1;
+    if (!L || (size_t)w->l.H != L->cfg.hidden || (size_t)w->topk != L->cfg.top_k)
+        return fail("ep_pull_experts_dev: bad args");
+    cudaStream_t st = (cudaStream_t)stream;
+    {
+        std::lock_guard<std::recursive_mutex> lk(g_mu);
+        if (ctx_init()) return 1;
+        Ctx *c = g_ctx;
+        Ordered ord(c, st);
+        if (ord.rc) return 1;
+        if (!w->tbl_ready) {
+            if (c->cur_capturing)
+                return fail("ep_pull_experts_dev: run one step before capturing a graph");
+            unsigned long long h[2 * EPW_MAX_RANKS] = {0};
+            for (int r = 0; r < w->l.n; r++) {
+                h[r] = (unsigned long long)(uintptr_t)(w->peers.base[r] + w->l.xs);
+                h[EPW_MAX_RANKS + r] = (unsigned long long)(uintptr_t)(w->peers.base[r] + w->l.by);
+            }
+            CU_OK(cudaMemcpyAsync(w->tbl, h, sizeof h, cudaMemcpyHostToDevice, st));
+            CU_OK(cudaStreamSynchronize(st));
+            w->tbl_ready = true;
+        }
+        const long total = (long)w->l.n * w->l.cap;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > c->sm_count * 4) blocks = c->sm_count * 4;
+        launch_k(epw_pull_ids_kernel, dim3(blocks), dim3(256), 0, st, w->l, w->peers,
+                 (int)L->e_begin, (int)L->e_end, w->pulled);
+        LAUNCHED();
+        /* of the n * cap slots about cap hold a resident expert */
+        c->ep_rows_hint = (size_t)w->l.cap;
+    }
+    PeerRows pr = {w->tbl, w->tbl + EPW_MAX_RANKS, w->l.cap};
+    if (experts_core(L, nullptr, w->pulled, (size_t)w->l.n * w->l.cap, nullptr, stream, &pr))
+        return 1;
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    /* a plain launch: it starts only when the GEMMs before it have ended */
+    epw_signal_kernel<<<1, 32, 0, st>>>(w->l, w->peers, w->me, epoch,
+                                        (const uint32_t *)w->d_epoch);
+    LAUNCHED();
+    return 0;
+}
+
 /* The shared expert of the rank's own tokens: d_sy [T,H] BF16 (c/layer.h:350-353). */
 extern "C" int apus_cuda_ep_shared_dev(ApusCudaLayer *L, const uint16_t *d_x, size_t T,
                                        uint16_t *d_sy, void *stream) {
@@ -2111,7 +2206,7 @@ extern "C" int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *L, s
                                         const uint16_t *d_sy, const uint16_t *d_sgl,
                                         uint16_t *d_out, void *stream) {
     if (epw_ready(w, "ep_combine_dev")) return 1;
-    if (!L || !T || !d_pos || !d_w || !d_sy || !d_sgl || !d_out ||
+    if (!L || !T || !d_w || !d_sy || !d_sgl || !d_out ||
         T * L->cfg.top_k > (size_t)w->l.cap)
         return fail("ep_combine_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);

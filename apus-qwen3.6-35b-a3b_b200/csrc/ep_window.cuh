@@ -40,6 +40,28 @@
  * have read rx; peers write by[] for step k+1 only after this rank's push of
  * step k+1, which follows its own read of by[] in stream order.
  *
+ * The second form of the step ("pull") moves each row across NVLink exactly
+ * once in each direction and has no exchange kernel of its own:
+ *
+ *   xs   [T_max][H]   BF16   this rank's token rows, published for its peers
+ *   ids  [cap]        int32  their expert ids (flat t * topk + j; -1 = none)
+ *
+ *   publish copy x and the ids into the own window, then fin[me] = epoch in
+ *           every peer's window.
+ *   wait    as above.
+ *   experts read every source's ids (512 KB in all), keep those of the resident
+ *           experts, sort; the gather kernel loads each needed token row
+ *           straight from its source's xs; gate_up as on one GPU; the down
+ *           GEMM's epilogue stores every output row straight into by[] of the
+ *           source rank, at the flat position t * topk + j the source's
+ *           combine reads it from; one more launch (fence, fbk[me] = epoch in
+ *           every peer) follows the GEMM.
+ *   wait, combine as above, with no position table.
+ *
+ * Reuse: a rank overwrites xs/ids for step k+1 only after its combine of step
+ * k, which follows every peer's fbk of step k, which follows that peer's last
+ * read of xs/ids.
+ *
  * No kernel here waits on a kernel of the same GPU, so N windows in one process
  * on one GPU (the tests' emulation) work as long as all pushes are launched
  * before the first wait.
@@ -54,10 +76,10 @@ constexpr int ST_PEER_TIMEOUT = 6;      /* a peer's flag never reached the epoch
 constexpr uint32_t EPW_WAIT_POLLS = 1u << 21;   /* x ~1 us: about two seconds */
 
 struct EpwLayout {
-    size_t rx, re, hdr, fin, by, fbk, total;
-    int cap, H, n;
+    size_t rx, re, hdr, fin, by, fbk, xs, ids, total;
+    int cap, H, n, tokens;
 };
-inline EpwLayout epw_layout(int n, int cap, int H) {
+inline EpwLayout epw_layout(int n, int cap, int H, int tokens) {
     EpwLayout l;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     size_t o = 0;
@@ -67,7 +89,10 @@ inline EpwLayout epw_layout(int n, int cap, int H) {
     l.fin = o; o = up(o + (size_t)n * 4);
     l.by = o;  o = up(o + (size_t)cap * H * 2);
     l.fbk = o; o = up(o + (size_t)n * 4);
+    l.xs = o;  o = up(o + (size_t)tokens * H * 2);
+    l.ids = o; o = up(o + (size_t)cap * 4);
     l.total = o;
+    l.tokens = tokens;
     l.cap = cap;
     l.H = H;
     l.n = n;
@@ -216,6 +241,58 @@ epw_return_kernel(const uint16_t *__restrict__ y, EpwLayout l, EpwPeers peers, i
     }
     if (epw_last_cta(counter) && threadIdx.x < l.n)
         st_release_sys(reinterpret_cast<uint32_t *>(s_base[threadIdx.x] + l.fbk) + me, epoch);
+}
+
+
+/* xs <- x [T,H]; ids <- idx [T*TK], -1 up to cap; then the push flag. */
+__global__ void __launch_bounds__(256)
+epw_publish_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ idx, int T,
+                   int TK, EpwLayout l, EpwPeers peers, int me, uint32_t epoch,
+                   unsigned int *counter, uint32_t *d_epoch) {
+    pdl_enter();
+    if (epoch == 0) epoch = *d_epoch + 1;
+    unsigned char *mine = peers.base[me];
+    const long stride = (long)gridDim.x * blockDim.x;
+    const long first = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long n16 = (long)T * (l.H / 8);
+    uint4 *xs = reinterpret_cast<uint4 *>(mine + l.xs);
+    for (long i = first; i < n16; i += stride)
+        xs[i] = ldg16(x + (size_t)i * 8);
+    int32_t *ids = reinterpret_cast<int32_t *>(mine + l.ids);
+    for (long i = first; i < l.cap; i += stride) ids[i] = i < (long)T * TK ? idx[i] : -1;
+    if (epw_last_cta(counter) && threadIdx.x < l.n) {
+        if (threadIdx.x == 0) *d_epoch = epoch;
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t *>(peers.base[threadIdx.x] + l.fin) + me,
+                       epoch);
+    }
+}
+
+/* re[s*cap + i] = ids of source s at i if that expert is resident here, else -1 */
+__global__ void __launch_bounds__(256)
+epw_pull_ids_kernel(EpwLayout l, EpwPeers peers, int e_begin, int e_end,
+                    int32_t *__restrict__ re) {
+    pdl_enter();
+    const long total = (long)l.n * l.cap;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        const int s = (int)(i / l.cap), k = (int)(i - (long)s * l.cap);
+        const int e = reinterpret_cast<const int32_t *>(peers.base[s] + l.ids)[k];
+        re[i] = (e >= e_begin && e < e_end) ? e : -1;
+    }
+}
+
+/* After the down GEMM whose epilogue stored into the peers: everything this GPU
+ * wrote before this launch is ordered before the flags. */
+__global__ void __launch_bounds__(32)
+epw_signal_kernel(EpwLayout l, EpwPeers peers, int me, uint32_t epoch,
+                  const uint32_t *d_epoch) {
+    pdl_enter();
+    if (epoch == 0) epoch = *d_epoch;
+    __threadfence_system();
+    if ((int)threadIdx.x < l.n)
+        st_release_sys(reinterpret_cast<uint32_t *>(peers.base[threadIdx.x] + l.fbk) + me,
+                       epoch);
 }
 
 }  // namespace apus

@@ -86,6 +86,10 @@ struct PairParams {
     uint16_t *out_routed, *out_shared;
     int ld_routed, ld_shared;
     const int32_t *perm;     /* down: sorted position -> flat assignment */
+    /* down, expert parallelism: routed output row a is row a % peer_cap of the
+     * buffer at peer_dst[a / peer_cap], in another GPU's memory (null: off) */
+    const unsigned long long *peer_dst;
+    int peer_cap;
     int *status;
     /* gate_up: token rows of the routed tiles fetched straight from the block
      * input by index (row perm[p] / gather_tk), four rows per TMA instruction,
@@ -393,12 +397,19 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                     }
                 }
             } else {
+                /* the row's home: this GPU's buffer, or the source rank's */
+                uint16_t *out_row = out + (size_t)orow * ld;
+                if (p.peer_dst && !shared && valid) {
+                    const int s = orow / p.peer_cap;
+                    out_row = reinterpret_cast<uint16_t *>(__ldg(p.peer_dst + s)) +
+                              (size_t)(orow - s * p.peer_cap) * ld;
+                }
                 for (int c0 = half * 128; any && c0 < half * 128 + 128; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld32(taddr + (uint32_t)c0, v);
                     tmem_ld_wait();
                     if (valid) {
-                        uint16_t *dst = out + (size_t)orow * ld + t.y * PP_BN + c0;
+                        uint16_t *dst = out_row + t.y * PP_BN + c0;
 #pragma unroll
                         for (int j = 0; j < 32; j += 16) {
                             uint32_t pk[8];
@@ -609,7 +620,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                             int A, int TK, bool do_shared, const DispatchOut &d,
                             uint16_t *xg, uint16_t *act, uint16_t *sa, uint16_t *eo,
                             uint16_t *sy, void *tiles_ws, int *status, cudaStream_t st,
-                            int *launches, void (*mark)(int stage)) {
+                            int *launches, void (*mark)(int stage),
+                            const PeerRows *peer = nullptr) {
     const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
               E = (int)c.experts;
     if (!maps) {
@@ -634,13 +646,18 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     const HybridLists tl = plan.l;
     const bool solo = plan.solo_below > 0 && A > 0;
     /* the one-SM kernels read the permuted copy, so it is made whenever they run */
-    const bool gather = g_pp_gather != 0 && !solo;
+    const bool gather = g_pp_gather != 0 && !solo && !peer;
     if (A > 0 && !gather) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
-        launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H, TK, xg,
-                 (const int32_t *)(d.offsets + E));
+        if (peer)
+            launch_k(gather_rows_peer_kernel, dim3(blocks), dim3(256), 0, st, peer->src,
+                     peer->cap, (const int32_t *)d.perm, A, H, TK, xg,
+                     (const int32_t *)(d.offsets + E));
+        else
+            launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H, TK,
+                     xg, (const int32_t *)(d.offsets + E));
         (*launches)++;
     }
     if (mark) mark(APUS_CUDA_STAGE_GATHER);
@@ -736,6 +753,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_routed = H;
     p2.ld_shared = H;
     p2.gather_tk = 0;
+    p2.peer_dst = peer ? peer->dst : nullptr;
+    p2.peer_cap = peer ? peer->cap : 0;
     launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem, st, m_act, m_sa, maps->w_d, maps->sh_d,
                 maps->sh_d, m_g, p2);
     (*launches)++;
@@ -752,6 +771,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         g2.ld_shared = H;
         g2.bn_rows = PG_BN_DN;
         g2.sched = tl.sched + 1;
+        g2.peer_dst = p2.peer_dst;
+        g2.peer_cap = p2.peer_cap;
         launch_k(grouped_gemm_kernel<1>, dim3(sm_count), dim3(PG_THREADS),
                  (size_t)pg_smem_bytes(false), st, maps->w_d, maps->sh_d, maps->sh_d, s_act,
                  s_act, g2);

@@ -214,6 +214,40 @@ gather_rows_kernel(const uint16_t *__restrict__ x,
     }
 }
 
+/* The block's rows live in other GPUs' memory (expert parallelism by peer
+ * loads and stores; net-new, the reference engine is one process).  The flat
+ * assignment a = s * cap + t * TK + j names slot j of token t of source rank
+ * s; src[s] is the address of that rank's published token rows [tokens, H] and
+ * dst[s] the address of its buffer of returned expert outputs [cap, H], both
+ * mapped into this process. */
+struct PeerRows {
+    const unsigned long long *src;   /* device table [ranks] */
+    const unsigned long long *dst;   /* device table [ranks] */
+    int cap;
+};
+
+/* xg[p, :] = token row of assignment perm[p], loaded from its source rank
+ * (NVLink reads for the remote ones). */
+__global__ void __launch_bounds__(256)
+gather_rows_peer_kernel(const unsigned long long *__restrict__ src, int cap,
+                        const int32_t *__restrict__ perm, int A, int H, int TK,
+                        uint16_t *__restrict__ xg, const int32_t *__restrict__ n_valid) {
+    pdl_enter();
+    const int c8 = H / 8;
+    if (n_valid) A = min(A, max(*n_valid, 0));
+    /* one row per 256-thread pass when H = 2048: consecutive rows of a CTA come
+     * from whatever sources the sort put side by side */
+    const long total = (long)A * c8;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        const int p = (int)(i / c8), c = (int)(i - (long)p * c8);
+        const int a = perm[p];
+        const int s = a / cap, tok = (a - s * cap) / TK;
+        const uint16_t *row = reinterpret_cast<const uint16_t *>(__ldg(src + s));
+        reinterpret_cast<uint4 *>(xg)[i] = ldg16(row + (size_t)tok * H + (size_t)c * 8);
+    }
+}
+
 /* ---- the grouped GEMM -------------------------------------------------------- */
 struct GemmParams {
     const int4 *tiles;
@@ -227,6 +261,11 @@ struct GemmParams {
     uint16_t *out_shared;  /* sa [T, ld_shared]   or  sy [T, ld_shared] */
     int ld_routed, ld_shared;
     const int32_t *perm;   /* down: sorted position -> flat assignment */
+    /* down, expert parallelism: routed output row a goes to row a % peer_cap of
+     * the buffer at peer_dst[a / peer_cap] (another GPU's memory) instead of
+     * row a of out_routed.  Null: off. */
+    const unsigned long long *peer_dst;
+    int peer_cap;
     int *status;
     /* Overlap of the two expert kernels.  When `done` is set, every epilogue
      * warp of the gate_up kernel counts a finished tile on done[expert] after
@@ -560,6 +599,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap mapA,     /* routed W */
                     if (c0 + lane < t.w)
                         my_orow = shared ? t.z + c0 + lane
                                          : __ldg(&p.perm[t.z + c0 + lane]);
+                    if (p.peer_dst && !shared) {
+                        /* each output row has its own home: the address travels
+                         * by shuffle instead of the row number */
+                        unsigned long long my_row = 0;
+                        if (c0 + lane < t.w) {
+                            const int s = my_orow / p.peer_cap;
+                            my_row = __ldg(p.peer_dst + s) +
+                                     (unsigned long long)(my_orow - s * p.peer_cap) * ld * 2ull;
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            uint16_t *r0 = reinterpret_cast<uint16_t *>(
+                                __shfl_sync(0xffffffffu, my_row, j));
+                            uint16_t *r1 = reinterpret_cast<uint16_t *>(
+                                __shfl_sync(0xffffffffu, my_row, j + 1));
+                            const uint32_t pk = pack_bf16_rn(__uint_as_float(g[j]),
+                                                             __uint_as_float(g[j + 1]));
+                            if (c0 + j < t.w) r0[col] = (uint16_t)pk;
+                            if (c0 + j + 1 < t.w) r1[col] = (uint16_t)(pk >> 16);
+                        }
+                        continue;
+                    }
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
@@ -741,7 +803,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
                                uint16_t *sa, uint16_t *eo, uint16_t *sy,
                                void *tiles_ws, int *status, cudaStream_t st,
                                int *launches, void (*mark)(int stage),
-                               const TilePlan *built = nullptr) {
+                               const TilePlan *built = nullptr,
+                               const PeerRows *peer = nullptr) {
     const int H = (int)c.hidden, I = (int)c.moe_inter, Is = (int)c.shared_inter,
               E = (int)c.experts;
     if (!maps) {
@@ -770,15 +833,20 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     const bool overlap = g_pg_overlap != 0;
     const int dynamic = g_pg_dynamic;
     /* a handful of tokens: the gate_up kernel reads the block input itself */
-    const bool direct = A > 0 && T <= 2 * PG_BN_MIN && g_pg_direct != 0;
+    const bool direct = A > 0 && T <= 2 * PG_BN_MIN && g_pg_direct != 0 && !peer;
     const int box_gu = direct ? (T <= PG_BN_MIN ? PG_BN_MIN : 2 * PG_BN_MIN) : bn_gu;
     /* permuted activation rows */
     if (A > 0 && !direct) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
-        launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H,
-                 TK, xg, (const int32_t *)(d.offsets + E));
+        if (peer)
+            launch_k(gather_rows_peer_kernel, dim3(blocks), dim3(256), 0, st, peer->src,
+                     peer->cap, (const int32_t *)d.perm, A, H, TK, xg,
+                     (const int32_t *)(d.offsets + E));
+        else
+            launch_k(gather_rows_kernel, dim3(blocks), dim3(256), 0, st, x, d.perm, A, H,
+                     TK, xg, (const int32_t *)(d.offsets + E));
         (*launches)++;
     }
     if (mark) mark(APUS_CUDA_STAGE_GATHER);
@@ -834,6 +902,8 @@ inline int run_prefill_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_shared = H;
     p2.perm = d.perm;
     p2.direct_tk = 0;
+    p2.peer_dst = peer ? peer->dst : nullptr;
+    p2.peer_cap = peer ? peer->cap : 0;
     p2.bn_rows = bn_dn;
     p2.sched = (dynamic & 2) ? tl.sched + 1 : nullptr;
     if (Is != I) {

@@ -112,15 +112,24 @@ class CudaOps:
 
 
 class PeerWindowBlock:
-    """The same block step with the two exchanges done by kernels that store
-    straight into the peers' memory (apus_cuda_ep_push_dev / _return_dev): no
-    collective on the data path and no host synchronisation inside a step.
-    torch.distributed is used once, to hand round the windows' IPC handles."""
+    """The same block step with the two exchanges done by kernels that load from
+    and store into the peers' memory: no collective on the data path and no host
+    synchronisation inside a step.  torch.distributed is used once, to hand
+    round the windows' IPC handles.
+
+    mode "pull" (default): a rank publishes its rows in its own window; the
+    expert ranks gather what they need from there and the down GEMM's epilogue
+    stores the outputs straight into the source's window
+    (apus_cuda_ep_publish_dev / _pull_experts_dev).
+    mode "push": exchange kernels of their own before and after the experts
+    (apus_cuda_ep_push_dev / _return_dev)."""
 
     def __init__(self, be, layer, cfg, rank, world, max_tokens, group=None,
-                 window=None, device_epoch=False):
+                 window=None, device_epoch=False, mode="pull"):
         import torch.distributed as dist
         assert cfg["experts"] % world == 0
+        assert mode in ("pull", "push")
+        self.mode = mode
         self.be, self.layer, self.cfg = be, layer, cfg
         self.rank, self.world, self.max_tokens = rank, world, max_tokens
         self.epoch = 0
@@ -180,14 +189,19 @@ class PeerWindowBlock:
         st["idx"] = torch.empty((T, TK), dtype=torch.int32, device=x.device)
         st["w"] = torch.empty((T, TK), dtype=torch.int16, device=x.device)
         st["sgl"] = torch.empty((T,), dtype=torch.int16, device=x.device)
-        st["pos"] = torch.empty((T * TK,), dtype=torch.int32, device=x.device)
+        st["pos"] = torch.empty((T * TK,), dtype=torch.int32, device=x.device) \
+            if self.mode == "push" else None
         st["sy"] = torch.empty((T, H), dtype=torch.int16, device=x.device)
         be, s = self.be, self._s()
         be.ep_route_dev(self.layer, x.data_ptr(), T, st["idx"].data_ptr(),
                         st["w"].data_ptr(), st["sgl"].data_ptr(), stream=s)
         mark("route")
-        be.ep_push_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
-                       self.epoch, st["pos"].data_ptr(), stream=s)
+        if self.mode == "push":
+            be.ep_push_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
+                           self.epoch, st["pos"].data_ptr(), stream=s)
+        else:
+            be.ep_publish_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
+                              self.epoch, stream=s)
         mark("push")
         be.ep_shared_dev(self.layer, x.data_ptr(), T, st["sy"].data_ptr(),
                          stream=s)
@@ -199,9 +213,13 @@ class PeerWindowBlock:
         be, s = self.be, self._s()
         be.ep_wait_dev(self.win, 0, self.epoch, stream=s)
         mark("wait_rows")
-        be.ep_window_experts_dev(self.win, self.layer, stream=s)
-        mark("experts")
-        be.ep_return_dev(self.win, self.epoch, stream=s)
+        if self.mode == "push":
+            be.ep_window_experts_dev(self.win, self.layer, stream=s)
+            mark("experts")
+            be.ep_return_dev(self.win, self.epoch, stream=s)
+        else:
+            be.ep_pull_experts_dev(self.win, self.layer, self.epoch, stream=s)
+            mark("experts")
         mark("return")
 
     def end(self, st, mark=None):
@@ -211,7 +229,8 @@ class PeerWindowBlock:
         out = torch.empty_like(x)
         be.ep_wait_dev(self.win, 1, self.epoch, stream=s)
         mark("wait_returns")
-        be.ep_combine_dev(self.win, self.layer, x.shape[0], st["pos"].data_ptr(),
+        be.ep_combine_dev(self.win, self.layer, x.shape[0],
+                          st["pos"].data_ptr() if st["pos"] is not None else None,
                           st["w"].data_ptr(), st["sy"].data_ptr(),
                           st["sgl"].data_ptr(), out.data_ptr(), stream=s)
         mark("combine")

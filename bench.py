@@ -801,12 +801,16 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
     x_host = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
     d_x = torch.from_numpy(x_host).cuda()
     exchange = getattr(args, "exchange", "peer")
+    window_mode = "push" if exchange == "push" else "pull"
+    if exchange == "push":
+        exchange = "peer"
     exchange_note = None
     if exchange == "peer":
         # every rank must take the same arm: agree on whether the windows came up
         ok = torch.ones(1, device="cuda")
         try:
-            blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=True)
+            blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=True,
+                                     mode=window_mode)
         except Exception as e:             # e.g. no peer access between two GPUs
             exchange_note = f"{type(e).__name__}: {e}"
             ok.zero_()
@@ -898,7 +902,9 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
     stage_ms = None
     if exchange == "peer":
         acc = np.zeros(len(EP_STAGES))
+        inner = {}
         reps = 5
+        be.stage_timing(True)
         for _ in range(reps):
             evs = [torch.cuda.Event(enable_timing=True)]
             dist.barrier()
@@ -912,11 +918,16 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
             blk.forward(d_x, mark=mark)
             torch.cuda.synchronize()
             acc += np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(len(EP_STAGES))])
+            # the library's own marks of the call that marked last: the experts
+            for k, v in be.last_stage_ms().items():
+                inner[k] = inner.get(k, 0.0) + v / reps
+        be.stage_timing(False)
         st = torch.tensor(acc / reps, device="cuda", dtype=torch.float64)
         st_max = st.clone()
         dist.all_reduce(st_max, op=dist.ReduceOp.MAX)
         stage_ms = {"max_over_ranks": dict(zip(EP_STAGES, (float(v) for v in st_max))),
                     "rank0": dict(zip(EP_STAGES, (float(v) for v in st))),
+                    "rank0_inside_experts": {k: v for k, v in inner.items() if v > 0},
                     "note": "one host-launched step bracketed by events; the two "
                             "wait stages contain the time a rank waits for its "
                             "slowest peer"}
@@ -1027,8 +1038,13 @@ def run_multi(args, cfg, config, pkg, synth, metric, unit, peaks, clock_sampler,
                          "bytes_each_way_per_step":
                              sent_rows * H * 2 if sent_rows is not None else None,
                          "requested": getattr(args, "exchange", "peer"),
-                         "collective": ("none: kernels store rows into the owner's "
-                                        "memory over NVLink (CUDA IPC windows)"
+                         "collective": (("none: the expert kernels load token rows "
+                                         "from and store outputs into the peers' "
+                                         "memory over NVLink (CUDA IPC windows)"
+                                         if window_mode == "pull" else
+                                         "none: push/return kernels store rows into "
+                                         "the peers' memory over NVLink (CUDA IPC "
+                                         "windows)")
                                         if exchange == "peer" else
                                         "all_to_all_single (NCCL), rows as bytes")},
             "block": {"device_status": status,
@@ -1102,7 +1118,7 @@ def run_config4(args, cfg, pkg, synth, be, ep, blk0, rank, world, stream, peaks,
                              stream=sp)
         layers.append(h)
         blks.append(ep.PeerWindowBlock(be, h, cfg, rank, world, T, window=win,
-                                       device_epoch=True))
+                                       device_epoch=True, mode=blk0.mode))
     x_all = synth.host_x(be, Tg, H, seed=args.seed, layer=1)
     x_loc = np.ascontiguousarray(x_all[rank * T:(rank + 1) * T]).view(np.int16)
     d_x = torch.from_numpy(x_loc).cuda()
@@ -1224,9 +1240,11 @@ def main():
     ap.add_argument("--chain", action="store_true",
                     help="with a layer stack: chain the layers through rmsnorm "
                          "and the residual add instead of one batch per layer")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="multi-GPU arm: rows exchanged by kernels that store into "
-                         "the peers' memory (default), or by NCCL all-to-all")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "push", "nccl"],
+                    help="multi-GPU arm: rows gathered from and outputs stored into "
+                         "the peers' memory by the expert kernels themselves "
+                         "(default), by push/return kernels of their own (push), or "
+                         "by NCCL all-to-all")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every step from the host instead of "
                          "replaying a captured CUDA graph")

@@ -433,6 +433,32 @@ int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer, size_t T
                              const uint16_t *d_sy, const uint16_t *d_sgl,
                              uint16_t *d_out, void *stream);
 
+/* The same step with each row crossing NVLink once per direction and no
+ * exchange kernel of its own ("pull" form; net-new as well).  A rank publishes
+ * its token rows and expert ids in its own window; the expert ranks load the
+ * rows they need straight from there while sorting them for the GEMMs, and the
+ * down GEMM's epilogue stores every output row straight into the source rank's
+ * window, where its combine reads it (d_pos NULL: flat order t * topk + j).
+ *
+ *   apus_cuda_ep_route_dev          idx, w, sgl of the rank's tokens
+ *   apus_cuda_ep_publish_dev        rows and ids into the own window, flag to peers
+ *   apus_cuda_ep_shared_dev         shared expert (overlaps the peers' publishes)
+ *   apus_cuda_ep_wait_dev(0, e)     every source has published
+ *   apus_cuda_ep_pull_experts_dev   ids read, rows gathered from the sources,
+ *                                   gate_up, down with remote stores, flag to peers
+ *   apus_cuda_ep_wait_dev(1, e)     every peer's outputs have landed here
+ *   apus_cuda_ep_combine_dev        with d_pos = NULL
+ *
+ * Same epoch rules, waits, status codes and bit-for-bit result as above.  Needs
+ * the tensor-core path (hidden, moe_inter multiples of 128).  Before capturing
+ * the step in a graph, run it once (the first call stores the peers' addresses
+ * on the device). */
+int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
+                             const int32_t *d_idx, size_t T, uint32_t epoch,
+                             void *stream);
+int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer,
+                                  uint32_t epoch, void *stream);
+
 /* ---- stages of the block, device pointers (kernel-level tests) ---------- */
 int apus_cuda_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
                         int32_t *d_idx, uint16_t *d_w, void *stream);

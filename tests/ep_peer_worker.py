@@ -15,6 +15,7 @@ from tests.conftest import load_package  # noqa: E402
 def main():
     outdir, T, steps = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
     use_graph = len(sys.argv) > 4 and sys.argv[4] == "1"
+    mode = sys.argv[5] if len(sys.argv) > 5 else "pull"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -29,7 +30,8 @@ def main():
     W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
     per = cfg["experts"] // world
     layer = be.layer_create(cfg, W, rank * per, (rank + 1) * per)
-    blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=use_graph)
+    blk = ep.PeerWindowBlock(be, layer, cfg, rank, world, T, device_epoch=use_graph,
+                             mode=mode)
     out = None
     d_x = torch.empty((T, cfg["hidden"]), dtype=torch.int16, device="cuda")
     graph = None

@@ -105,7 +105,8 @@ def test_ep_world_size_one_process_group(gpu, be, synth):
         dist.destroy_process_group()
 
 
-def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1, device_epoch=False):
+def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1, device_epoch=False,
+                    mode="push"):
     """N ranks in this process, one peer window each, attached to one another
     by pointer.  All pushes are launched before the first wait, all returns
     before the first wait for them, so no kernel ever waits on a later one."""
@@ -119,7 +120,7 @@ def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1, device_epoch=False):
             if q != r:
                 be.ep_window_attach_local(wins[r], q, wins[q])
     blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, per, window=wins[r],
-                               device_epoch=device_epoch)
+                               device_epoch=device_epoch, mode=mode)
             for r in range(N)]
     xs = [torch.from_numpy(x[r * per:(r + 1) * per].view(np.int16).copy()).cuda()
           for r in range(N)]
@@ -138,12 +139,15 @@ def emulate_windows(be, ep, torch, cfg, W, x, N, steps=1, device_epoch=False):
     return out
 
 
-@pytest.mark.parametrize("path", ["gemm", "gemv"])
+@pytest.mark.parametrize("mode,path", [("push", "gemm"), ("push", "gemv"),
+                                       ("pull", "gemm")])
 @pytest.mark.parametrize("N,T", [(2, 20), (2, 200), (4, 400), (8, 1024), (4, 2400)])
-def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, monkeypatch):
-    """The exchange through peer windows (rows stored straight into the
-    owner's memory, outputs stored straight back) gives the single-GPU block
-    bit for bit; three steps in a row reuse the windows."""
+def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, mode, monkeypatch):
+    """The exchange through peer windows gives the single-GPU block bit for
+    bit; three steps in a row reuse the windows.  push: rows stored straight
+    into the owner's memory, outputs stored straight back by kernels of their
+    own.  pull: rows gathered from the publishers' windows, outputs stored by
+    the down GEMM's epilogue (always the tensor-core kernels)."""
     import torch
     from apus_b200 import ep
     monkeypatch.setenv("APUS_CUDA_DECODE_MAX_T",
@@ -155,13 +159,35 @@ def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, monkeypatch):
         W = synth.host_weights(be, cfg, seed=13, sigma=0.05)
         x = synth.host_x(be, T, cfg["hidden"], seed=13)
         whole = be.moe_block(cfg, W, x, trace=False)["out"]
-        got = emulate_windows(be, ep, torch, cfg, W, x, N, steps=3)
+        got = emulate_windows(be, ep, torch, cfg, W, x, N, steps=3, mode=mode)
         assert np.array_equal(got, whole)
     finally:
         be.disable()
 
 
-def test_peer_window_skewed_router_one_owner(be, synth):
+@pytest.mark.parametrize("N,T", [(2, 4096), (8, 8192)])
+def test_peer_window_pull_two_sm_kernels(be, synth, N, T, monkeypatch):
+    """Enough rows per resident expert for the two-SM GEMMs (and the one-SM
+    kernels on the remainders): their down epilogues store to the sources'
+    windows too."""
+    import torch
+    from apus_b200 import ep
+    monkeypatch.setenv("APUS_CUDA_PAIR_MIN_ROWS", "64")
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        W = synth.host_weights(be, cfg, seed=29, sigma=0.05)
+        x = synth.host_x(be, T, cfg["hidden"], seed=29)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        got = emulate_windows(be, ep, torch, cfg, W, x, N, steps=2, mode="pull")
+        assert np.array_equal(got, whole)
+    finally:
+        be.disable()
+
+
+@pytest.mark.parametrize("mode", ["push", "pull"])
+def test_peer_window_skewed_router_one_owner(be, synth, mode):
     """Every assignment of every token goes to experts of rank 0: the other
     ranks receive nothing and return nothing."""
     import torch
@@ -182,14 +208,15 @@ def test_peer_window_skewed_router_one_owner(be, synth):
         x = synth.f32_to_bf16(x)
         whole = be.moe_block(cfg, W, x, trace=True)
         assert int(whole["idx"].max()) < 16
-        got = emulate_windows(be, ep, torch, cfg, W, x, 4)
+        got = emulate_windows(be, ep, torch, cfg, W, x, 4, mode=mode)
         assert np.array_equal(got, whole["out"])
     finally:
         be.disable()
 
 
+@pytest.mark.parametrize("mode", ["push", "pull"])
 @pytest.mark.parametrize("T,graph", [(24, 0), (300, 0), (300, 1)])
-def test_peer_window_two_processes(be, synth, T, graph, tmp_path):
+def test_peer_window_two_processes(be, synth, T, graph, mode, tmp_path):
     """Two real ranks, one per GPU, windows mapped through CUDA IPC: the rows
     cross NVLink by the kernels' own stores.  Three steps (graph = 1: the step
     captured once in a CUDA graph and replayed, its number kept on the device);
@@ -207,7 +234,7 @@ def test_peer_window_two_processes(be, synth, T, graph, tmp_path):
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
          "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
          "--master-port", str(port), worker, str(tmp_path), str(T), "3",
-         str(graph)],
+         str(graph), mode],
         env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     got = np.concatenate([np.load(tmp_path / f"out_{k}.npy") for k in range(2)])
@@ -223,7 +250,8 @@ def test_peer_window_two_processes(be, synth, T, graph, tmp_path):
         be.disable()
 
 
-def test_peer_window_step_number_on_the_device(be, synth):
+@pytest.mark.parametrize("mode", ["push", "pull"])
+def test_peer_window_step_number_on_the_device(be, synth, mode):
     """Epoch 0 in every call: the windows count the steps themselves (what a
     captured CUDA graph of the step needs).  Four steps, four ranks."""
     import torch
@@ -236,7 +264,7 @@ def test_peer_window_step_number_on_the_device(be, synth):
         x = synth.host_x(be, 160, cfg["hidden"], seed=21)
         whole = be.moe_block(cfg, W, x, trace=False)["out"]
         got = emulate_windows(be, ep, torch, cfg, W, x, 4, steps=4,
-                              device_epoch=True)
+                              device_epoch=True, mode=mode)
         assert np.array_equal(got, whole)
     finally:
         be.disable()
