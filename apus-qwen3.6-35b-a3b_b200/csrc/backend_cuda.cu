@@ -2108,9 +2108,9 @@ extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x
     cudaStream_t st = (cudaStream_t)stream;
     Ordered ord(c, st);
     if (ord.rc) return 1;
-    long total = (long)T * (w->l.H / 8);
+    long total = (long)T * (w->l.H / 8) * w->l.n;
     int blocks = (int)((total + 255) / 256);
-    if (blocks > c->sm_count * 4) blocks = c->sm_count * 4;
+    if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
     launch_k(epw_publish_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx, (int)T, w->topk,
              w->l, w->peers, w->me, epoch, w->counter, w->d_epoch);
     LAUNCHED();
@@ -2134,7 +2134,8 @@ extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer 
                 return fail("ep_pull_experts_dev: run one step before capturing a graph");
             unsigned long long h[2 * EPW_MAX_RANKS] = {0};
             for (int r = 0; r < w->l.n; r++) {
-                h[r] = (unsigned long long)(uintptr_t)(w->peers.base[r] + w->l.xs);
+                h[r] = (unsigned long long)(uintptr_t)(w->base + w->l.xs +
+                                                       (size_t)r * w->l.tokens * w->l.H * 2);
                 h[EPW_MAX_RANKS + r] = (unsigned long long)(uintptr_t)(w->peers.base[r] + w->l.by);
             }
             CU_OK(cudaMemcpyAsync(w->tbl, h, sizeof h, cudaMemcpyHostToDevice, st));
@@ -2144,8 +2145,9 @@ extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer 
         const long total = (long)w->l.n * w->l.cap;
         int blocks = (int)((total + 255) / 256);
         if (blocks > c->sm_count * 4) blocks = c->sm_count * 4;
-        launch_k(epw_pull_ids_kernel, dim3(blocks), dim3(256), 0, st, w->l, w->peers,
-                 (int)L->e_begin, (int)L->e_end, w->pulled);
+        launch_k(epw_pull_ids_kernel, dim3(blocks), dim3(256), 0, st,
+                 (const int32_t *)(w->base + w->l.ids), total, (int)L->e_begin,
+                 (int)L->e_end, w->pulled);
         LAUNCHED();
         /* of the n * cap slots about cap hold a resident expert */
         c->ep_rows_hint = (size_t)w->l.cap;

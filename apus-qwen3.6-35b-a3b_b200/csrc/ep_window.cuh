@@ -40,27 +40,28 @@
  * have read rx; peers write by[] for step k+1 only after this rank's push of
  * step k+1, which follows its own read of by[] in stream order.
  *
- * The second form of the step ("pull") moves each row across NVLink exactly
- * once in each direction and has no exchange kernel of its own:
+ * The second form of the step ("pull") has no exchange kernel around the
+ * experts; top-k of 8 over at most 8 ranks means nearly every rank needs
+ * nearly every token, so the token rows are all-gathered instead of sent per
+ * assignment (each row crosses a link once, not once per expert):
  *
- *   xs   [T_max][H]   BF16   this rank's token rows, published for its peers
- *   ids  [cap]        int32  their expert ids (flat t * topk + j; -1 = none)
+ *   xs   [N][T_max][H] BF16   every rank's token rows, written by their owners
+ *   ids  [N][cap]      int32  their expert ids (flat t * topk + j; -1 = none)
  *
- *   publish copy x and the ids into the own window, then fin[me] = epoch in
- *           every peer's window.
+ *   publish store x and the ids into region `me` of xs/ids of EVERY rank's
+ *           window (its own included), then fin[me] = epoch everywhere.
  *   wait    as above.
- *   experts read every source's ids (512 KB in all), keep those of the resident
- *           experts, sort; the gather kernel loads each needed token row
- *           straight from its source's xs; gate_up as on one GPU; the down
+ *   experts keep the ids of the resident experts, sort; the gather kernel reads
+ *           each needed row from the local xs; gate_up as on one GPU; the down
  *           GEMM's epilogue stores every output row straight into by[] of the
- *           source rank, at the flat position t * topk + j the source's
- *           combine reads it from; one more launch (fence, fbk[me] = epoch in
- *           every peer) follows the GEMM.
+ *           rank that owns the token, at the flat position t * topk + j its
+ *           combine reads; one more launch (fence, fbk[me] = epoch in every
+ *           peer) follows the GEMM.
  *   wait, combine as above, with no position table.
  *
- * Reuse: a rank overwrites xs/ids for step k+1 only after its combine of step
- * k, which follows every peer's fbk of step k, which follows that peer's last
- * read of xs/ids.
+ * Reuse: a rank overwrites region `me` of its peers' xs/ids for step k+1 only
+ * after its combine of step k, which follows every peer's fbk of step k, which
+ * follows that peer's last read of xs/ids.
  *
  * No kernel here waits on a kernel of the same GPU, so N windows in one process
  * on one GPU (the tests' emulation) work as long as all pushes are launched
@@ -89,8 +90,8 @@ inline EpwLayout epw_layout(int n, int cap, int H, int tokens) {
     l.fin = o; o = up(o + (size_t)n * 4);
     l.by = o;  o = up(o + (size_t)cap * H * 2);
     l.fbk = o; o = up(o + (size_t)n * 4);
-    l.xs = o;  o = up(o + (size_t)tokens * H * 2);
-    l.ids = o; o = up(o + (size_t)cap * 4);
+    l.xs = o;  o = up(o + (size_t)n * tokens * H * 2);
+    l.ids = o; o = up(o + (size_t)n * cap * 4);
     l.total = o;
     l.tokens = tokens;
     l.cap = cap;
@@ -244,40 +245,52 @@ epw_return_kernel(const uint16_t *__restrict__ y, EpwLayout l, EpwPeers peers, i
 }
 
 
-/* xs <- x [T,H]; ids <- idx [T*TK], -1 up to cap; then the push flag. */
+/* Region `me` of xs and ids in every rank's window <- x [T,H], idx [T*TK] (-1
+ * up to cap); then the push flag.  Every CTA owns one contiguous run of the
+ * (destination, 16-byte chunk) list, so all destinations are written at once. */
 __global__ void __launch_bounds__(256)
 epw_publish_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ idx, int T,
                    int TK, EpwLayout l, EpwPeers peers, int me, uint32_t epoch,
                    unsigned int *counter, uint32_t *d_epoch) {
     pdl_enter();
     if (epoch == 0) epoch = *d_epoch + 1;
-    unsigned char *mine = peers.base[me];
-    const long stride = (long)gridDim.x * blockDim.x;
-    const long first = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    __shared__ unsigned char *s_base[EPW_MAX_RANKS];
+    if (threadIdx.x < EPW_MAX_RANKS) s_base[threadIdx.x] = peers.base[threadIdx.x];
+    __syncthreads();
     const long n16 = (long)T * (l.H / 8);
-    uint4 *xs = reinterpret_cast<uint4 *>(mine + l.xs);
-    for (long i = first; i < n16; i += stride)
-        xs[i] = ldg16(x + (size_t)i * 8);
-    int32_t *ids = reinterpret_cast<int32_t *>(mine + l.ids);
-    for (long i = first; i < l.cap; i += stride) ids[i] = i < (long)T * TK ? idx[i] : -1;
+    const long total = n16 * l.n;
+    const long per = (total + gridDim.x - 1) / gridDim.x;
+    const long lo = min(total, (long)blockIdx.x * per), hi = min(total, lo + per);
+    const size_t region = (size_t)me * l.tokens * l.H * 2;
+    for (long j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        const int d = (int)(j / n16);
+        const long i = j - (long)d * n16;
+        reinterpret_cast<uint4 *>(s_base[d] + l.xs + region)[i] = ldg16(x + (size_t)i * 8);
+    }
+    const long ids_total = (long)l.cap * l.n;
+    for (long j = (long)blockIdx.x * blockDim.x + threadIdx.x; j < ids_total;
+         j += (long)gridDim.x * blockDim.x) {
+        const int d = (int)(j / l.cap);
+        const long i = j - (long)d * l.cap;
+        reinterpret_cast<int32_t *>(s_base[d] + l.ids)[(size_t)me * l.cap + i] =
+            i < (long)T * TK ? idx[i] : -1;
+    }
     if (epw_last_cta(counter) && threadIdx.x < l.n) {
         if (threadIdx.x == 0) *d_epoch = epoch;
         __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t *>(peers.base[threadIdx.x] + l.fin) + me,
-                       epoch);
+        st_release_sys(reinterpret_cast<uint32_t *>(s_base[threadIdx.x] + l.fin) + me, epoch);
     }
 }
 
-/* re[s*cap + i] = ids of source s at i if that expert is resident here, else -1 */
+/* re[i] = ids[i] (all sources, this rank's copy) if that expert is resident
+ * here, else -1 */
 __global__ void __launch_bounds__(256)
-epw_pull_ids_kernel(EpwLayout l, EpwPeers peers, int e_begin, int e_end,
+epw_pull_ids_kernel(const int32_t *__restrict__ ids, long total, int e_begin, int e_end,
                     int32_t *__restrict__ re) {
     pdl_enter();
-    const long total = (long)l.n * l.cap;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long)gridDim.x * blockDim.x) {
-        const int s = (int)(i / l.cap), k = (int)(i - (long)s * l.cap);
-        const int e = reinterpret_cast<const int32_t *>(peers.base[s] + l.ids)[k];
+        const int e = ids[i];
         re[i] = (e >= e_begin && e < e_end) ? e : -1;
     }
 }

@@ -64,7 +64,12 @@ constexpr int PP_THREADS = 64 + PP_EPI_WARPS * 32;
 constexpr int PP_TMEM_COLS = 512;
 constexpr uint32_t PP_PEER_MASK = 0xFEFFFFFFu;      /* cluster address of CTA 0's copy */
 
-inline int pp_smem_bytes() { return PP_STAGES * PP_STAGE_BYTES + 1024 + 256; }
+/* down with outputs stored into peers' memory: a 32-row x 128-byte staging tile
+ * per epilogue warp, so that a row leaves as 128 contiguous bytes */
+constexpr int PP_STAGING_BYTES = PP_EPI_WARPS * 4096;
+inline int pp_smem_bytes(bool staging = false) {
+    return PP_STAGES * PP_STAGE_BYTES + 1024 + 256 + (staging ? PP_STAGING_BYTES : 0);
+}
 
 /* token-side tensor maps: the same tensor with boxes of 32, 64, 96, 128 rows */
 struct PairMaps {
@@ -404,6 +409,48 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                     out_row = reinterpret_cast<uint16_t *>(__ldg(p.peer_dst + s)) +
                               (size_t)(orow - s * p.peer_cap) * ld;
                 }
+                if (p.peer_dst && !shared) {
+                    /* A thread owns a row, so a warp's store would touch 32 rows
+                     * with 32 bytes each: fine for local memory, where L2 merges
+                     * sectors, poor as NVLink packets.  The warp turns its 32 x 64
+                     * chunk round in shared memory (16-byte units, XOR-swizzled by
+                     * row) and stores it as 128 contiguous bytes per row, four
+                     * rows an instruction. */
+                    unsigned char *stg = smem + (size_t)STAGES * PP_STAGE_BYTES + 256 +
+                                         (size_t)(warp - 2) * 4096;
+                    const unsigned long long my_row =
+                        valid ? (unsigned long long)reinterpret_cast<uintptr_t>(out_row) : 0ull;
+                    for (int c0 = half * 128; any && c0 < half * 128 + 128; c0 += 64) {
+                        uint32_t v[32], v2[32];
+                        tmem_ld32(taddr + (uint32_t)c0, v);
+                        tmem_ld32(taddr + (uint32_t)c0 + 32u, v2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int h8 = 0; h8 < 8; h8++) {
+                            const uint32_t *f = h8 < 4 ? v + 8 * h8 : v2 + 8 * (h8 - 4);
+                            uint4 q4;
+                            q4.x = pack_bf16_rn(__uint_as_float(f[0]), __uint_as_float(f[1]));
+                            q4.y = pack_bf16_rn(__uint_as_float(f[2]), __uint_as_float(f[3]));
+                            q4.z = pack_bf16_rn(__uint_as_float(f[4]), __uint_as_float(f[5]));
+                            q4.w = pack_bf16_rn(__uint_as_float(f[6]), __uint_as_float(f[7]));
+                            *reinterpret_cast<uint4 *>(stg + lane * 128 +
+                                                       ((h8 ^ (lane & 7)) << 4)) = q4;
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int it = 0; it < 8; it++) {
+                            const int rr = it * 4 + (lane >> 3), ch = lane & 7;
+                            const unsigned long long rp = __shfl_sync(0xffffffffu, my_row, rr);
+                            const uint4 q4 = *reinterpret_cast<const uint4 *>(
+                                stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                            if (rp)
+                                *reinterpret_cast<uint4 *>(
+                                    reinterpret_cast<unsigned char *>((uintptr_t)rp) +
+                                    (size_t)(t.y * PP_BN + c0) * 2 + (ch << 4)) = q4;
+                        }
+                        __syncwarp();
+                    }
+                } else
                 for (int c0 = half * 128; any && c0 < half * 128 + 128; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld32(taddr + (uint32_t)c0, v);
@@ -628,8 +675,8 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         snprintf(g_prefill_err, sizeof g_prefill_err, "tensor maps missing");
         return 1;
     }
-    const int smem = pp_smem_bytes();
-    if (smem > smem_optin || Is != I) {
+    const int smem = pp_smem_bytes(), smem_dn = pp_smem_bytes(peer != nullptr);
+    if (smem_dn > smem_optin || Is != I) {
         snprintf(g_prefill_err, sizeof g_prefill_err,
                  "two-SM grouped GEMM: %d B shared memory, shared_inter == moe_inter", smem);
         return 1;
@@ -683,7 +730,7 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         cudaFuncSetAttribute(pair_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smem);
         cudaFuncSetAttribute(pair_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem);
+                             pp_smem_bytes(true) <= smem_optin ? pp_smem_bytes(true) : smem);
         attr_set = true;
     }
     const int grid = sm_count & ~1;
@@ -755,7 +802,7 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.gather_tk = 0;
     p2.peer_dst = peer ? peer->dst : nullptr;
     p2.peer_cap = peer ? peer->cap : 0;
-    launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem, st, m_act, m_sa, maps->w_d, maps->sh_d,
+    launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem_dn, st, m_act, m_sa, maps->w_d, maps->sh_d,
                 maps->sh_d, m_g, p2);
     (*launches)++;
     if (solo) {

@@ -217,9 +217,9 @@ gather_rows_kernel(const uint16_t *__restrict__ x,
 /* The block's rows live in other GPUs' memory (expert parallelism by peer
  * loads and stores; net-new, the reference engine is one process).  The flat
  * assignment a = s * cap + t * TK + j names slot j of token t of source rank
- * s; src[s] is the address of that rank's published token rows [tokens, H] and
- * dst[s] the address of its buffer of returned expert outputs [cap, H], both
- * mapped into this process. */
+ * s; src[s] is the address of that rank's token rows [tokens, H] (this GPU's
+ * copy of them, or the rank's own memory) and dst[s] the address of its buffer
+ * of returned expert outputs [cap, H], mapped into this process. */
 struct PeerRows {
     const unsigned long long *src;   /* device table [ranks] */
     const unsigned long long *dst;   /* device table [ranks] */
