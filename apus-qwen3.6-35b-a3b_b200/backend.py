@@ -166,7 +166,7 @@ class Backend:
         L.apus_cuda_ep_return_dev.argtypes = [vp, C.c_uint32, vp]
         L.apus_cuda_ep_shared_dev.argtypes = [vp, vp, sz, vp, vp]
         L.apus_cuda_ep_publish_dev.argtypes = [vp, vp, vp, sz, C.c_uint32, vp]
-        L.apus_cuda_ep_pull_experts_dev.argtypes = [vp, vp, C.c_uint32, vp]
+        L.apus_cuda_ep_pull_experts_dev.argtypes = [vp, vp, C.c_uint32, vp, sz, vp, vp]
         L.apus_cuda_ep_combine_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
         L.apus_cuda_resadd_dev.argtypes = [vp, vp, vp, sz, vp]
@@ -546,9 +546,10 @@ class Backend:
                                                       stream),
                     "apus_cuda_ep_publish_dev")
 
-    def ep_pull_experts_dev(self, w, layer, epoch, stream=None):
-        self._check(self.lib.apus_cuda_ep_pull_experts_dev(w, layer, epoch,
-                                                           stream),
+    def ep_pull_experts_dev(self, w, layer, epoch, d_x=None, T=0, d_sy=None,
+                            stream=None):
+        self._check(self.lib.apus_cuda_ep_pull_experts_dev(w, layer, epoch, d_x,
+                                                           T, d_sy, stream),
                     "apus_cuda_ep_pull_experts_dev")
 
     def ep_shared_dev(self, layer, d_x, T, d_sy, stream=None):

@@ -1771,8 +1771,14 @@ extern "C" int apus_cuda_ep_pack_dev(const uint16_t *d_x, const int32_t *d_idx,
 
 /* peer (expert parallelism, pull form): the rows are loaded from and the
  * outputs stored to other GPUs' memory; d_x and d_y are then unused. */
+struct SharedWork {            /* the shared expert of the rank's own tokens, in the same */
+    const uint16_t *x;         /* launches as the routed experts: x [T,H] -> y [T,H] */
+    size_t T;
+    uint16_t *y;
+};
 static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_e, size_t R,
-                        uint16_t *d_y, void *stream, const PeerRows *peer) {
+                        uint16_t *d_y, void *stream, const PeerRows *peer,
+                        const SharedWork *sh = nullptr) {
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
     Ctx *c = g_ctx;
@@ -1798,6 +1804,10 @@ static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_
         d_x = b.xg;          /* a valid local address for the unused token maps */
         d_y = b.eo;
     }
+    if (sh && (!prefill || sh->T > R)) return fail("experts: shared work needs the GEMM path");
+    const uint16_t *x_in = sh ? sh->x : d_x;
+    const int T_in = sh ? (int)sh->T : (int)R;
+    uint16_t *sy = sh ? sh->y : b.sy;
     if (prefill) {
         b.d.grp_expert = nullptr;
         b.d.grp_first = nullptr;
@@ -1810,7 +1820,7 @@ static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_
                       rows_expected >= (size_t)g_pp_min_rows * ne;
     TilePlan plan;
     memset(&plan, 0, sizeof plan);
-    if (prefill && !pair) plan = prefill_tile_plan(cx, (int)R, false, (int)R, b.tiles);
+    if (prefill && !pair) plan = prefill_tile_plan(cx, T_in, sh != nullptr, (int)R, b.tiles);
     /* stage marks (apus_cuda_stage_timing): dispatch, gather, gate_up, down */
     c->n_ev = 0;
     stage_mark(c, -1, st);
@@ -1821,19 +1831,19 @@ static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (pair) {
         const int before = c->last_block_launches;
-        if (run_pair_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x, (int)R, (int)R,
-                             peer ? (int)L->cfg.top_k : 1, false, b.d, b.xg, b.act, b.sa, d_y,
-                             b.sy, b.tiles, c->d_status, st, &c->last_block_launches, mark_cb,
-                             peer))
+        if (run_pair_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, x_in, T_in, (int)R,
+                             peer ? (int)L->cfg.top_k : 1, sh != nullptr, b.d, b.xg, b.act,
+                             b.sa, d_y, sy, b.tiles, c->d_status, st, &c->last_block_launches,
+                             mark_cb, peer))
             return fail("%s", prefill_last_error());
         c->launches += (uint64_t)(c->last_block_launches - before);
         return 0;
     }
     if (prefill) {
         const int before = c->last_block_launches;
-        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, d_x,
-                                (int)R, (int)R, peer ? (int)L->cfg.top_k : 1, false, b.d,
-                                b.xg, b.act, b.sa, d_y, b.sy, b.tiles, c->d_status, st,
+        if (run_prefill_experts(c->sm_count, c->smem_optin, L->maps, cx, 0, x_in,
+                                T_in, (int)R, peer ? (int)L->cfg.top_k : 1, sh != nullptr, b.d,
+                                b.xg, b.act, b.sa, d_y, sy, b.tiles, c->d_status, st,
                                 &c->last_block_launches, mark_cb,
                                 plan.on ? &plan : nullptr, peer))
             return fail("%s", prefill_last_error());
@@ -2118,9 +2128,11 @@ extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x
 }
 
 extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *L,
-                                             uint32_t epoch, void *stream) {
+                                             uint32_t epoch, const uint16_t *d_x, size_t T,
+                                             uint16_t *d_sy, void *stream) {
     if (epw_ready(w, "ep_pull_experts_dev")) return 1;
-    if (!L || (size_t)w->l.H != L->cfg.hidden || (size_t)w->topk != L->cfg.top_k)
+    if (!L || (size_t)w->l.H != L->cfg.hidden || (size_t)w->topk != L->cfg.top_k ||
+        (d_x && (!d_sy || !T || T > (size_t)w->l.tokens)))
         return fail("ep_pull_experts_dev: bad args");
     cudaStream_t st = (cudaStream_t)stream;
     {
@@ -2153,7 +2165,9 @@ extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer 
         c->ep_rows_hint = (size_t)w->l.cap;
     }
     PeerRows pr = {w->tbl, w->tbl + EPW_MAX_RANKS, w->l.cap};
-    if (experts_core(L, nullptr, w->pulled, (size_t)w->l.n * w->l.cap, nullptr, stream, &pr))
+    SharedWork sh = {d_x, T, d_sy};
+    if (experts_core(L, nullptr, w->pulled, (size_t)w->l.n * w->l.cap, nullptr, stream, &pr,
+                     d_x ? &sh : nullptr))
         return 1;
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     /* a plain launch: it starts only when the GEMMs before it have ended */

@@ -262,10 +262,22 @@ epw_publish_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ i
     const long per = (total + gridDim.x - 1) / gridDim.x;
     const long lo = min(total, (long)blockIdx.x * per), hi = min(total, lo + per);
     const size_t region = (size_t)me * l.tokens * l.H * 2;
-    for (long j = lo + threadIdx.x; j < hi; j += blockDim.x) {
-        const int d = (int)(j / n16);
-        const long i = j - (long)d * n16;
-        reinterpret_cast<uint4 *>(s_base[d] + l.xs + region)[i] = ldg16(x + (size_t)i * 8);
+    /* four independent loads in flight per thread before the four stores */
+    for (long j0 = lo + threadIdx.x; j0 < hi; j0 += 4L * blockDim.x) {
+        uint4 v[4];
+        int d[4];
+        long i[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const long j = j0 + (long)u * blockDim.x;
+            d[u] = j < hi ? (int)(j / n16) : -1;
+            i[u] = j - (long)(d[u] < 0 ? 0 : d[u]) * n16;
+            if (d[u] >= 0) v[u] = ldg16(x + (size_t)i[u] * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (d[u] >= 0)
+                reinterpret_cast<uint4 *>(s_base[d[u]] + l.xs + region)[i[u]] = v[u];
     }
     const long ids_total = (long)l.cap * l.n;
     for (long j = (long)blockIdx.x * blockDim.x + threadIdx.x; j < ids_total;

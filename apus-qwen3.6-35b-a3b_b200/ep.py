@@ -203,9 +203,12 @@ class PeerWindowBlock:
             be.ep_publish_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
                               self.epoch, stream=s)
         mark("push")
-        be.ep_shared_dev(self.layer, x.data_ptr(), T, st["sy"].data_ptr(),
-                         stream=s)
+        if self.mode == "push":
+            be.ep_shared_dev(self.layer, x.data_ptr(), T, st["sy"].data_ptr(),
+                             stream=s)
+        # pull: the shared expert rides in the routed experts' launches
         mark("shared")
+        self._st = st
         return st
 
     def middle(self, mark=None):
@@ -218,7 +221,10 @@ class PeerWindowBlock:
             mark("experts")
             be.ep_return_dev(self.win, self.epoch, stream=s)
         else:
-            be.ep_pull_experts_dev(self.win, self.layer, self.epoch, stream=s)
+            st = self._st
+            be.ep_pull_experts_dev(self.win, self.layer, self.epoch,
+                                   st["x"].data_ptr(), st["x"].shape[0],
+                                   st["sy"].data_ptr(), stream=s)
             mark("experts")
         mark("return")
 

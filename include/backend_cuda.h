@@ -434,18 +434,20 @@ int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer, size_t T
                              uint16_t *d_out, void *stream);
 
 /* The same step with each row crossing NVLink once per direction and no
- * exchange kernel of its own ("pull" form; net-new as well).  A rank publishes
- * its token rows and expert ids in its own window; the expert ranks load the
- * rows they need straight from there while sorting them for the GEMMs, and the
- * down GEMM's epilogue stores every output row straight into the source rank's
- * window, where its combine reads it (d_pos NULL: flat order t * topk + j).
+ * exchange kernel around the experts ("pull" form; net-new as well).  A rank
+ * stores its token rows and expert ids into every rank's window (with top-8
+ * over at most 8 ranks nearly every rank needs nearly every token); the expert
+ * ranks gather the rows they need from their own copy while sorting them for
+ * the GEMMs, and the down GEMM's epilogue stores every output row straight into
+ * the source rank's window, where its combine reads it (d_pos NULL: flat order
+ * t * topk + j).
  *
  *   apus_cuda_ep_route_dev          idx, w, sgl of the rank's tokens
- *   apus_cuda_ep_publish_dev        rows and ids into the own window, flag to peers
- *   apus_cuda_ep_shared_dev         shared expert (overlaps the peers' publishes)
+ *   apus_cuda_ep_publish_dev        rows and ids into every rank's window, flag
  *   apus_cuda_ep_wait_dev(0, e)     every source has published
- *   apus_cuda_ep_pull_experts_dev   ids read, rows gathered from the sources,
- *                                   gate_up, down with remote stores, flag to peers
+ *   apus_cuda_ep_pull_experts_dev   resident ids kept and sorted, rows gathered,
+ *                                   gate_up, down with remote stores (the shared
+ *                                   expert of the own tokens rides along), flag
  *   apus_cuda_ep_wait_dev(1, e)     every peer's outputs have landed here
  *   apus_cuda_ep_combine_dev        with d_pos = NULL
  *
@@ -456,8 +458,12 @@ int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer, size_t T
 int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
                              const int32_t *d_idx, size_t T, uint32_t epoch,
                              void *stream);
+/* d_x [T,H] (optional): the rank's own token rows; their shared expert then
+ * runs inside the same GEMM launches and lands in d_sy [T,H], instead of in a
+ * call to apus_cuda_ep_shared_dev. */
 int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer,
-                                  uint32_t epoch, void *stream);
+                                  uint32_t epoch, const uint16_t *d_x, size_t T,
+                                  uint16_t *d_sy, void *stream);
 
 /* ---- stages of the block, device pointers (kernel-level tests) ---------- */
 int apus_cuda_route_dev(ApusCudaLayer *layer, const uint16_t *d_x, size_t T,
