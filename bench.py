@@ -47,6 +47,13 @@ METRIC = "moe_layer_prefill_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0,
                       bf16_tflops_sustained=1400.0)
+# DRAM bytes per gate_up stage from ncu, keyed by (tokens, skewed router)
+NCU_TRAFFIC = {
+    (8192, True): (1715.5e6, "profiles/launch_list_t8192_zipf.md: pair_gemm_kernel<0> "
+                             "817.8 MB + grouped_gemm_kernel<0> 897.7 MB"),
+    (512, False): (1101.6e6, "profiles/launch_list_t8192_zipf.md (T = 512 table): "
+                             "grouped_gemm_kernel<0>"),
+}
 HEADLINE_T = 8192
 ZIPF_S = 1.1
 # tuned once on seed 0 so that the hottest expert takes about ten times the
@@ -322,7 +329,10 @@ def measure_layer(env, layer, x_host, T, skew, steps, warmup, sustain_s,
                 "algorithmic_bytes_per_launch": block_bytes}
     else:
         dom = max(("gate_up", "down"), key=lambda k: stage_ms.get(k, 0.0))
-        kname = f"grouped_gemm_kernel<{dom}>"
+        two_sm = be.last_block_path() == 3
+        kname = (f"pair_gemm_kernel<{dom}> + grouped_gemm_kernel<{dom}> (the stage's "
+                 "two launches: 256-row chunks on SM pairs, the rest on single SMs)"
+                 if two_sm else f"grouped_gemm_kernel<{dom}>")
         if dom == "gate_up":
             kbytes = (uniq + 1) * slab_gu + (A + T) * H * 2 + (A + T) * I * 2
             kflops = 2 * (A + T) * 2 * I * H
@@ -341,6 +351,13 @@ def measure_layer(env, layer, x_host, T, skew, steps, warmup, sustain_s,
                     "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
                     "algorithmic_bytes_per_launch": kbytes}
+    # dram__bytes_read.sum + dram__bytes_write.sum of the stage's launches, from the
+    # ncu capture of this workload summarised under profiles/ (not measured live)
+    if launches_per_step > 1 and dom == "gate_up":
+        tr = NCU_TRAFFIC.get((T, bool(skew)))
+        if tr:
+            roof["traffic"] = tr[0]
+            roof["traffic_source"] = tr[1]
     roof["peak_source"] = pk["_source"]
     roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
     res["roofline"] = roof
