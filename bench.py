@@ -47,12 +47,18 @@ METRIC = "moe_layer_prefill_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0,
                       bf16_tflops_sustained=1400.0)
-# DRAM bytes per gate_up stage from ncu, keyed by (tokens, skewed router)
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the gate_up stage's
+# launches, keyed by (tokens, skewed router).  From an ncu capture of this
+# benchmark's own command on the build of commit 20ff240 (the GEMM kernels are
+# unchanged since); the launch-list summary under profiles/ holds the table.
 NCU_TRAFFIC = {
-    (8192, True): (1715.5e6, "profiles/launch_list_t8192_zipf.md: pair_gemm_kernel<0> "
-                             "817.8 MB + grouped_gemm_kernel<0> 897.7 MB"),
-    (512, False): (1101.6e6, "profiles/launch_list_t8192_zipf.md (T = 512 table): "
-                             "grouped_gemm_kernel<0>"),
+    (8192, True): (1715.5e6, "ncu, commit 20ff240, bench.py --no-sub --no-cpu-baseline "
+                             "--sustain 0 --steps 2 --warmup 3 --no-graph: "
+                             "pair_gemm_kernel<0> 817.8 MB + grouped_gemm_kernel<0> "
+                             "897.7 MB per launch"),
+    (512, False): (1101.6e6, "ncu, commit 20ff240, bench.py --tokens 512 --uniform "
+                             "--no-cpu-baseline --sustain 0 --steps 2 --warmup 3 "
+                             "--no-graph: grouped_gemm_kernel<0> per launch"),
 }
 HEADLINE_T = 8192
 ZIPF_S = 1.1
@@ -351,8 +357,7 @@ def measure_layer(env, layer, x_host, T, skew, steps, warmup, sustain_s,
                     "achieved": kbytes / (kms * 1e-3) / 1e9 if kms else None,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None,
                     "algorithmic_bytes_per_launch": kbytes}
-    # dram__bytes_read.sum + dram__bytes_write.sum of the stage's launches, from the
-    # ncu capture of this workload summarised under profiles/ (not measured live)
+    # DRAM traffic of the stage's launches from an ncu capture (not measured live)
     if launches_per_step > 1 and dom == "gate_up":
         tr = NCU_TRAFFIC.get((T, bool(skew)))
         if tr:
