@@ -77,7 +77,8 @@ SYMBOLS = [
     "apus_cuda_ep_push_dev", "apus_cuda_ep_wait_dev",
     "apus_cuda_ep_window_experts_dev", "apus_cuda_ep_return_dev",
     "apus_cuda_ep_shared_dev", "apus_cuda_ep_combine_dev",
-    "apus_cuda_ep_publish_dev", "apus_cuda_ep_pull_experts_dev",
+    "apus_cuda_ep_publish_dev", "apus_cuda_ep_publish_rows_dev",
+    "apus_cuda_ep_pull_experts_dev",
     "apus_cuda_route_dev", "apus_cuda_dispatch_dev",
     "apus_cuda_dispatch_dev_static", "apus_cuda_rmsnorm_dev",
     "apus_cuda_resadd_dev", "apus_cuda_bf16_gemv_dev", "apus_synth_fill_host",
@@ -166,6 +167,7 @@ class Backend:
         L.apus_cuda_ep_return_dev.argtypes = [vp, C.c_uint32, vp]
         L.apus_cuda_ep_shared_dev.argtypes = [vp, vp, sz, vp, vp]
         L.apus_cuda_ep_publish_dev.argtypes = [vp, vp, vp, sz, C.c_uint32, vp]
+        L.apus_cuda_ep_publish_rows_dev.argtypes = [vp, vp, sz, vp]
         L.apus_cuda_ep_pull_experts_dev.argtypes = [vp, vp, C.c_uint32, vp, sz, vp, vp]
         L.apus_cuda_ep_combine_dev.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         L.apus_cuda_rmsnorm_dev.argtypes = [vp, vp, vp, sz, sz, vp]
@@ -545,6 +547,10 @@ class Backend:
         self._check(self.lib.apus_cuda_ep_publish_dev(w, d_x, d_idx, T, epoch,
                                                       stream),
                     "apus_cuda_ep_publish_dev")
+
+    def ep_publish_rows_dev(self, w, d_x, T, stream=None):
+        self._check(self.lib.apus_cuda_ep_publish_rows_dev(w, d_x, T, stream),
+                    "apus_cuda_ep_publish_rows_dev")
 
     def ep_pull_experts_dev(self, w, layer, epoch, d_x=None, T=0, d_sy=None,
                             stream=None):

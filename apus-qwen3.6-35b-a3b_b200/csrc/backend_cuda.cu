@@ -2105,11 +2105,31 @@ extern "C" int apus_cuda_ep_return_dev(ApusCudaEpWindow *w, uint32_t epoch,
 }
 
 /* ---- the pull form of the step (ep_window.cuh) ---- */
+/* Touches the window and d_x only (no shared workspace), so it is not ordered
+ * against the library's other calls: it may run beside the router on a second
+ * stream.  The caller orders it after its previous step's combine and before
+ * apus_cuda_ep_publish_dev(..., d_x = NULL, ...). */
+extern "C" int apus_cuda_ep_publish_rows_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
+                                             size_t T, void *stream) {
+    if (epw_ready(w, "ep_publish_rows_dev")) return 1;
+    if (!d_x || !T || T > (size_t)w->l.tokens) return fail("ep_publish_rows_dev: bad args");
+    std::lock_guard<std::recursive_mutex> lk(g_mu);
+    if (ctx_init()) return 1;
+    Ctx *c = g_ctx;
+    long total = (long)T * (w->l.H / 8) * w->l.n;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
+    epw_publish_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(d_x, (int)T, w->l,
+                                                                      w->peers, w->me);
+    LAUNCHED();
+    return 0;
+}
+
 extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
                                         const int32_t *d_idx, size_t T, uint32_t epoch,
                                         void *stream) {
     if (epw_ready(w, "ep_publish_dev")) return 1;
-    if (!d_x || !d_idx || !T || T > (size_t)w->l.tokens)
+    if (!d_idx || !T || T > (size_t)w->l.tokens)
         return fail("ep_publish_dev: bad args");
     std::lock_guard<std::recursive_mutex> lk(g_mu);
     if (ctx_init()) return 1;
@@ -2118,7 +2138,7 @@ extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x
     cudaStream_t st = (cudaStream_t)stream;
     Ordered ord(c, st);
     if (ord.rc) return 1;
-    long total = (long)T * (w->l.H / 8) * w->l.n;
+    long total = d_x ? (long)T * (w->l.H / 8) * w->l.n : (long)w->l.cap * w->l.n;
     int blocks = (int)((total + 255) / 256);
     if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
     launch_k(epw_publish_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx, (int)T, w->topk,

@@ -257,7 +257,8 @@ epw_publish_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ i
     __shared__ unsigned char *s_base[EPW_MAX_RANKS];
     if (threadIdx.x < EPW_MAX_RANKS) s_base[threadIdx.x] = peers.base[threadIdx.x];
     __syncthreads();
-    const long n16 = (long)T * (l.H / 8);
+    /* x == nullptr: the rows are there already (epw_publish_rows_kernel) */
+    const long n16 = x ? (long)T * (l.H / 8) : 0;
     const long total = n16 * l.n;
     const long per = (total + gridDim.x - 1) / gridDim.x;
     const long lo = min(total, (long)blockIdx.x * per), hi = min(total, lo + per);
@@ -291,6 +292,38 @@ epw_publish_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ i
         if (threadIdx.x == 0) *d_epoch = epoch;
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(s_base[threadIdx.x] + l.fin) + me, epoch);
+    }
+}
+
+/* The rows alone, no ids and no flag: needs nothing from the router, so it can
+ * run beside it on another stream; the publish kernel proper (x = nullptr) must
+ * follow it in device order. */
+__global__ void __launch_bounds__(256)
+epw_publish_rows_kernel(const uint16_t *__restrict__ x, int T, EpwLayout l, EpwPeers peers,
+                        int me) {
+    __shared__ unsigned char *s_base[EPW_MAX_RANKS];
+    if (threadIdx.x < EPW_MAX_RANKS) s_base[threadIdx.x] = peers.base[threadIdx.x];
+    __syncthreads();
+    const long n16 = (long)T * (l.H / 8);
+    const long total = n16 * l.n;
+    const long per = (total + gridDim.x - 1) / gridDim.x;
+    const long lo = min(total, (long)blockIdx.x * per), hi = min(total, lo + per);
+    const size_t region = (size_t)me * l.tokens * l.H * 2;
+    for (long j0 = lo + threadIdx.x; j0 < hi; j0 += 4L * blockDim.x) {
+        uint4 v[4];
+        int d[4];
+        long i[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const long j = j0 + (long)u * blockDim.x;
+            d[u] = j < hi ? (int)(j / n16) : -1;
+            i[u] = j - (long)(d[u] < 0 ? 0 : d[u]) * n16;
+            if (d[u] >= 0) v[u] = ldg16(x + (size_t)i[u] * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (d[u] >= 0)
+                reinterpret_cast<uint4 *>(s_base[d[u]] + l.xs + region)[i[u]] = v[u];
     }
 }
 

@@ -125,11 +125,15 @@ class PeerWindowBlock:
     (apus_cuda_ep_push_dev / _return_dev)."""
 
     def __init__(self, be, layer, cfg, rank, world, max_tokens, group=None,
-                 window=None, device_epoch=False, mode="pull"):
+                 window=None, device_epoch=False, mode="pull", overlap=True):
         import torch.distributed as dist
         assert cfg["experts"] % world == 0
         assert mode in ("pull", "push")
         self.mode = mode
+        # pull: the rows are stored into the peers' windows on a second stream
+        # while the router runs (they need nothing from it)
+        self.overlap = overlap and mode == "pull"
+        self._side = None
         self.be, self.layer, self.cfg = be, layer, cfg
         self.rank, self.world, self.max_tokens = rank, world, max_tokens
         self.epoch = 0
@@ -193,12 +197,23 @@ class PeerWindowBlock:
             if self.mode == "push" else None
         st["sy"] = torch.empty((T, H), dtype=torch.int16, device=x.device)
         be, s = self.be, self._s()
+        if self.overlap:
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)          # after the previous step's combine
+            be.ep_publish_rows_dev(self.win, x.data_ptr(), T,
+                                   stream=self._side.cuda_stream)
         be.ep_route_dev(self.layer, x.data_ptr(), T, st["idx"].data_ptr(),
                         st["w"].data_ptr(), st["sgl"].data_ptr(), stream=s)
         mark("route")
         if self.mode == "push":
             be.ep_push_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
                            self.epoch, st["pos"].data_ptr(), stream=s)
+        elif self.overlap:
+            main.wait_stream(self._side)          # the rows are in the windows
+            be.ep_publish_dev(self.win, None, st["idx"].data_ptr(), T,
+                              self.epoch, stream=s)
         else:
             be.ep_publish_dev(self.win, x.data_ptr(), st["idx"].data_ptr(), T,
                               self.epoch, stream=s)

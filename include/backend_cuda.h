@@ -458,6 +458,15 @@ int apus_cuda_ep_combine_dev(ApusCudaEpWindow *w, ApusCudaLayer *layer, size_t T
 int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x,
                              const int32_t *d_idx, size_t T, uint32_t epoch,
                              void *stream);
+/* The rows need nothing from the router: a caller may store them with this call
+ * on a second stream while apus_cuda_ep_route_dev runs, and then pass d_x = NULL
+ * to apus_cuda_ep_publish_dev (ids and flag only).  This call uses no shared
+ * workspace and is the one device-pointer call the library does not order
+ * against the others; the caller makes it start after its previous step's
+ * combine and end before the publish (events, or a fork and join inside a
+ * captured graph). */
+int apus_cuda_ep_publish_rows_dev(ApusCudaEpWindow *w, const uint16_t *d_x, size_t T,
+                                  void *stream);
 /* d_x [T,H] (optional): the rank's own token rows; their shared expert then
  * runs inside the same GEMM launches and lands in d_sy [T,H], instead of in a
  * call to apus_cuda_ep_shared_dev. */

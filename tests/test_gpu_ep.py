@@ -165,6 +165,52 @@ def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, mode, monkeyp
         be.disable()
 
 
+@pytest.mark.parametrize("mode,overlap", [("push", False), ("pull", True),
+                                          ("pull", False)])
+def test_peer_window_ragged_ranks(be, synth, mode, overlap):
+    """Ranks with different token counts (5, 200, 37, 128; windows sized for
+    200): the unused tail of a rank's region holds no assignment.  overlap: the
+    rows are stored on a second stream beside the router."""
+    import torch
+    from apus_b200 import ep
+    be.enable()
+    try:
+        cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128,
+                   top_k=8)
+        counts, N, cap_t = [5, 200, 37, 128], 4, 200
+        T, H, E = sum(counts), cfg["hidden"], cfg["experts"]
+        W = synth.host_weights(be, cfg, seed=31, sigma=0.05)
+        x = synth.host_x(be, T, H, seed=31)
+        whole = be.moe_block(cfg, W, x, trace=False)["out"]
+        layers = [be.layer_create(cfg, W, r * E // N, (r + 1) * E // N)
+                  for r in range(N)]
+        wins = [be.ep_window_create(cap_t, cfg["top_k"], H, E, N, r) for r in range(N)]
+        for r in range(N):
+            for q in range(N):
+                if q != r:
+                    be.ep_window_attach_local(wins[r], q, wins[q])
+        blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, cap_t, window=wins[r],
+                                   mode=mode, overlap=overlap) for r in range(N)]
+        lo = np.concatenate([[0], np.cumsum(counts)])
+        xs = [torch.from_numpy(x[lo[r]:lo[r + 1]].view(np.int16).copy()).cuda()
+              for r in range(N)]
+        for _ in range(2):
+            sts = [blks[r].begin(xs[r]) for r in range(N)]
+            for r in range(N):
+                blks[r].middle()
+            outs = [blks[r].end(sts[r]) for r in range(N)]
+        torch.cuda.synchronize()
+        assert be.last_block_status() == 0
+        got = np.concatenate([o.cpu().numpy().view(np.uint16) for o in outs])
+        assert np.array_equal(got, whole)
+        for w in wins:
+            be.ep_window_destroy(w)
+        for l in layers:
+            be.layer_destroy(l)
+    finally:
+        be.disable()
+
+
 @pytest.mark.parametrize("N,T", [(2, 4096), (8, 8192)])
 def test_peer_window_pull_two_sm_kernels(be, synth, N, T, monkeypatch):
     """Enough rows per resident expert for the two-SM GEMMs (and the one-SM
