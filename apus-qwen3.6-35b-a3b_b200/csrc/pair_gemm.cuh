@@ -540,7 +540,7 @@ build_hybrid_tiles_kernel(const int32_t *__restrict__ counts,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cnt = tid < E ? counts[tid] : 0, off = tid < E ? offsets[tid] : 0;
     const int full = cnt / (2 * PP_BM), rem = cnt - full * 2 * PP_BM;
-    const bool rem_pair = rem >= hp.solo_below;
+    const bool rem_pair = rem > 0 && rem >= hp.solo_below;   /* never a tile without rows */
     const int n_pair = full + (rem_pair ? 1 : 0);             /* 256-row chunks */
     const int solo = rem_pair ? 0 : rem;                      /* rows for the one-SM kernels */
     const int n_sg = (solo + hp.solo_bn_gu - 1) / hp.solo_bn_gu;

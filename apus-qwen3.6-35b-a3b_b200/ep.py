@@ -111,6 +111,9 @@ class CudaOps:
         return out
 
 
+_SIDE_STREAMS = {}
+
+
 class PeerWindowBlock:
     """The same block step with the two exchanges done by kernels that load from
     and store into the peers' memory: no collective on the data path and no host
@@ -199,7 +202,12 @@ class PeerWindowBlock:
         be, s = self.be, self._s()
         if self.overlap:
             if self._side is None:
-                self._side = torch.cuda.Stream()
+                # one second stream per device, shared by every block (a stack of
+                # layers forks and joins the same stream forty times per step)
+                dev = x.device.index or 0
+                if dev not in _SIDE_STREAMS:
+                    _SIDE_STREAMS[dev] = torch.cuda.Stream(device=x.device)
+                self._side = _SIDE_STREAMS[dev]
             main = torch.cuda.current_stream()
             self._side.wait_stream(main)          # after the previous step's combine
             be.ep_publish_rows_dev(self.win, x.data_ptr(), T,
