@@ -61,6 +61,10 @@ constexpr int PP_STAGE_BYTES = 2 * PP_HALF_BYTES;    /* tokens | weights */
 constexpr int PP_STAGES = 6;
 constexpr int PP_EPI_WARPS = 8;
 constexpr int PP_THREADS = 64 + PP_EPI_WARPS * 32;
+/* gate_up only: six more warps that fetch the token rows themselves, so that no
+ * permuted copy of the block input is needed */
+constexpr int PP_GATHER_WARPS = 6;    /* == PP_STAGES: warp w serves stage w */
+constexpr int PP_THREADS_GU = PP_THREADS + PP_GATHER_WARPS * 32;
 constexpr int PP_TMEM_COLS = 512;
 constexpr uint32_t PP_PEER_MASK = 0xFEFFFFFFu;      /* cluster address of CTA 0's copy */
 
@@ -68,7 +72,9 @@ constexpr uint32_t PP_PEER_MASK = 0xFEFFFFFFu;      /* cluster address of CTA 0'
  * per epilogue warp, so that a row leaves as 128 contiguous bytes */
 constexpr int PP_STAGING_BYTES = PP_EPI_WARPS * 4096;
 inline int pp_smem_bytes(bool staging = false) {
-    return PP_STAGES * PP_STAGE_BYTES + 1024 + 256 + (staging ? PP_STAGING_BYTES : 0);
+    /* after the stages and the barriers: the down epilogue's staging tiles, or
+     * the gate_up gather warps' token tables (6 x 128 ints) */
+    return PP_STAGES * PP_STAGE_BYTES + 1024 + 256 + (staging ? PP_STAGING_BYTES : 3072);
 }
 
 /* token-side tensor maps: the same tensor with boxes of 32, 64, 96, 128 rows */
@@ -100,6 +106,12 @@ struct PairParams {
      * input by index (row perm[p] / gather_tk), four rows per TMA instruction,
      * instead of from a permuted copy */
     int gather_tk;           /* 0: off */
+    /* gate_up: token rows fetched by the kernel's own gather warps with plain
+     * loads (row perm[p] / wgather_tk of x for a routed tile, row p for the shared
+     * expert) and written into the stage in the layout the TMA would have
+     * produced; the TMA producer then loads weights only.  0: off */
+    int wgather_tk;
+    const uint16_t *x;       /* [T, K] block input (wgather) */
 };
 
 __device__ __forceinline__ uint32_t pp_cta_rank() {
@@ -180,6 +192,36 @@ __device__ __forceinline__ void pp_arrive_leader(uint64_t *bar) {
         "}\n" ::"r"(smem_u32(bar))
         : "memory");
 }
+/* barrier wait that also acquires what the PEER CTA's threads wrote before
+ * their (cluster-scope release) arrivals */
+__device__ __forceinline__ bool pp_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool pp_wait_cluster(uint64_t *bar, uint32_t parity,
+                                                volatile int *abort_flag, int *status,
+                                                int code) {
+    if (*abort_flag) return false;
+    for (uint32_t i = 0; i < APUS_WAIT_LIMIT; i++) {
+        if (pp_try_wait_cluster(bar, parity)) return true;
+        if (i > 256) {
+            __nanosleep(32);
+            if (*abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    set_status(status, code);
+    return false;
+}
 /* kind::f16 instruction descriptor: D fp32, A/B BF16, both K-major, M x N */
 __device__ __forceinline__ uint32_t pp_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
@@ -196,7 +238,7 @@ __device__ __forceinline__ void st32(uint16_t *p, const uint32_t (&v)[8]) {
 
 /* MODE 0: gate_up + SwiGLU;  MODE 1: down */
 template <int MODE>
-__global__ void __launch_bounds__(PP_THREADS, 1)
+__global__ void __launch_bounds__(MODE == 0 ? PP_THREADS_GU : PP_THREADS, 1)
 pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (tokens) */
                  const __grid_constant__ PairMaps mapAs,       /* x  | sa */
                  const __grid_constant__ CUtensorMap mapB,     /* routed weights */
@@ -220,7 +262,9 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 1);
+            /* the producer's expect_tx arrival, plus the stage's gather warp of
+             * each CTA when they bring the token rows */
+            mbar_init(&full[s], 1 + (MODE == 0 && p.wgather_tk ? 2 : 0));
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; a++) {
@@ -281,6 +325,7 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
         for (int tile = pair; alive && tile < n_tiles; tile += npairs) {
             const Ops o = ops_of(__ldg(&p.tiles[tile]));
             const bool gath = MODE == 0 && p.gather_tk > 0 && !o.shared;
+            const bool wg = MODE == 0 && p.wgather_tk > 0;   /* rows come from the gather warps */
             /* lane l fetches rows 4l .. 4l+3 of this CTA's share */
             int g4[4] = {0, 0, 0, 0};
             const int ng_mine = (o.n_mine + 3) >> 2;
@@ -293,7 +338,7 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
             }
             const uint32_t bytes_all =
                 (uint32_t)(2 * PP_HALF_BYTES) +
-                (gath ? (uint32_t)(((o.n0 + 3) >> 2) + ((o.n1 + 3) >> 2)) * 4u * PP_BK * 2u
+                (wg ? 0u : gath ? (uint32_t)(((o.n0 + 3) >> 2) + ((o.n1 + 3) >> 2)) * 4u * PP_BK * 2u
                       : (uint32_t)(((o.n0 + 31) >> 5) + ((o.n1 + 31) >> 5)) * 32u * PP_BK * 2u);
             for (int kb = 0; alive && kb < num_kb; kb++, kiter++) {
                 const int s = kiter % STAGES;
@@ -309,7 +354,8 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                 unsigned char *st = smem + (size_t)s * PP_STAGE_BYTES;
                 if (lane == 0) {
                     if (rank == 0) mbar_expect_tx(&full[s], bytes_all);
-                    if (!gath && o.mine) pp_tma_load(st, o.ma, kb * PP_BK, o.arow, &full[s]);
+                    if (!gath && !wg && o.mine)
+                        pp_tma_load(st, o.ma, kb * PP_BK, o.arow, &full[s]);
                     pp_tma_load(st + PP_HALF_BYTES, o.mb, kb * PP_BK, o.brow, &full[s]);
                 }
                 if (gath && lane < ng_mine)
@@ -335,7 +381,7 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                 for (int kb = 0; kb < num_kb; kb++, kiter++) {
                     const int s = kiter % STAGES;
                     const uint32_t ph = (kiter / STAGES) & 1u;
-                    if (!pg_wait(&full[s], ph, abort_flag, p.status, ST_MBAR_TIMEOUT)) {
+                    if (!pp_wait_cluster(&full[s], ph, abort_flag, p.status, ST_MBAR_TIMEOUT)) {
                         alive = false;
                         break;
                     }
@@ -349,6 +395,67 @@ pair_gemm_kernel(const __grid_constant__ PairMaps mapA,        /* xg | act   (to
                     pp_commit_both(&empty[s]);       /* frees the stage in both CTAs */
                 }
                 if (alive) pp_commit_both(&tfull[acc]);
+            }
+        }
+    } else if (MODE == 0 && warp >= 2 + PP_EPI_WARPS) {
+        /* ---------------- gather warps (gate_up, both CTAs) ----------------
+         * Per k-block the CTA's 128 rows x 128 bytes are fetched as 16-byte
+         * units and land at (unit ^ (row & 7)) of their row — the 128-byte
+         * swizzle the MMA's descriptor expects.  Generic-proxy writes become
+         * visible to the tensor core through fence.proxy.async in the writer,
+         * before the warp's arrival on the leader CTA's full barrier. */
+        if (p.wgather_tk > 0) {
+            /* One warp per pipeline stage: warp w brings the rows of every
+             * PP_GATHER_WARPS-th k-block into stage w, so that a warp has one
+             * k-block of cp.async in flight at a time (fence.proxy.async waits
+             * for all of a thread's outstanding copies: issuing ahead within a
+             * thread buys nothing) while the CTA has six.  Eight lanes share a
+             * row (16 bytes each, one whole 128-byte line), four rows an
+             * instruction, 32 instructions a k-block. */
+            const int gw = warp - 2 - PP_EPI_WARPS, sub = lane >> 3, ch = lane & 7;
+            int *tok = reinterpret_cast<int *>(smem + (size_t)STAGES * PP_STAGE_BYTES + 256) +
+                       gw * PP_BM;
+            const int my_tiles = pair < n_tiles ? (n_tiles - pair + npairs - 1) / npairs : 0;
+            const uint32_t total = (uint32_t)my_tiles * (uint32_t)num_kb;
+            int cur = -1, n_mine = 0;
+            const uint32_t st0 = smem_u32(smem + (size_t)gw * PP_STAGE_BYTES);
+            for (uint32_t it = (uint32_t)gw; it < total; it += PP_GATHER_WARPS) {
+                const int tile_of = (int)(it / (uint32_t)num_kb),
+                          kb = (int)(it - (uint32_t)tile_of * (uint32_t)num_kb);
+                if (tile_of != cur) {
+                    cur = tile_of;
+                    const int4 t = __ldg(&p.tiles[pair + tile_of * npairs]);
+                    const int n0 = pp_rows_of(t.w, 0);
+                    n_mine = rank ? t.w - n0 : n0;
+                    __syncwarp();
+                    for (int g = lane; g < n_mine; g += 32) {
+                        const int r = t.z + (rank ? n0 : 0) + g;
+                        tok[g] = t.x == p.E ? r : __ldg(&p.perm[r]) / p.wgather_tk;
+                    }
+                    __syncwarp();
+                }
+                const uint32_t ph = (it / STAGES) & 1u;
+                int ok = 1;
+                if (lane == 0)
+                    ok = pg_wait(&empty[gw], ph ^ 1u, abort_flag, p.status, ST_MBAR_TIMEOUT) ? 1
+                                                                                             : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint16_t *col = p.x + (size_t)kb * PP_BK + ch * 8;
+#pragma unroll 8
+                for (int j = 0; j < PP_BM / 4; j++) {
+                    const int g = j * 4 + sub;
+                    if (g < n_mine)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                                         st0 + (uint32_t)(g * 128 + ((ch ^ (g & 7)) << 4))),
+                                     "l"(col + (size_t)tok[g] * p.K)
+                                     : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) pp_arrive_leader(&full[gw]);
             }
         }
     } else {
@@ -490,8 +597,12 @@ inline int g_pp_enable = 1;          /* APUS_CUDA_PAIR=0: never take this path *
 inline int g_pp_min_rows = 192;      /* mean rows per resident expert from which it is taken */
 inline int g_pp_solo_below = 160;    /* APUS_CUDA_PAIR_SOLO_BELOW: see build_hybrid_tiles_kernel
                                       * (0: every chunk to the pair kernels) */
-inline int g_pp_gather = 0;          /* APUS_CUDA_PAIR_GATHER=1: rows by TMA gather4 instead of a permuted copy
-                                      * (measured 2.4x slower: 32 four-row requests per k-block) */
+inline int g_pp_gather = 0;          /* APUS_CUDA_PAIR_GATHER: how gate_up gets its token rows.
+                                      * 0: permuted copy + TMA (fastest measured);
+                                      * 1: TMA gather4 from the block input (2.4x slower:
+                                      *    32 four-row requests per k-block);
+                                      * 2: the kernel's gather warps, cp.async into the
+                                      *    swizzled stage (gate_up 1.4x slower, no copy) */
 
 inline bool pair_supported(const ApusCudaMoeCfg &c, int sm_count, int smem_optin) {
     return g_pp_enable && prefill_supported(c) && c.hidden % PP_BN == 0 &&
@@ -605,6 +716,26 @@ build_hybrid_tiles_kernel(const int32_t *__restrict__ counts,
     }
 }
 
+/* xg rows of the one-SM lists only (the SM pairs fetch their rows themselves):
+ * every gate_up tile of weight-row tile 0 names one run of rows. */
+__global__ void __launch_bounds__(256)
+gather_solo_rows_kernel(const uint16_t *__restrict__ x, const int32_t *__restrict__ perm,
+                        const int4 *__restrict__ tiles, const int *__restrict__ n_tiles, int H,
+                        int TK, uint16_t *__restrict__ xg) {
+    pdl_enter();
+    const int n = *n_tiles, c8 = H / 8;
+    for (int i = blockIdx.x; i < n; i += gridDim.x) {
+        const int4 t = tiles[i];
+        if (t.y != 0) continue;
+        for (int j = threadIdx.x; j < t.w * c8; j += blockDim.x) {
+            const int r = t.z + j / c8, c = j % c8;
+            const int tok = perm[r] / TK;
+            reinterpret_cast<uint4 *>(xg)[(size_t)r * c8 + c] =
+                ldg16(x + (size_t)tok * H + (size_t)c * 8);
+        }
+    }
+}
+
 /* list storage inside the block's tile workspace (prefill_tiles_bytes_for) */
 inline bool hybrid_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, int A, void *ws,
                         size_t ws_bytes, HybridPlan *out) {
@@ -640,11 +771,11 @@ inline bool hybrid_plan(const ApusCudaMoeCfg &c, int T, bool do_shared, int A, v
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pair(void (*kernel)(KArgs...), int grid, size_t smem,
+inline cudaError_t launch_pair(void (*kernel)(KArgs...), int grid, int threads, size_t smem,
                                cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(PP_THREADS);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -693,8 +824,17 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     const HybridLists tl = plan.l;
     const bool solo = plan.solo_below > 0 && A > 0;
     /* the one-SM kernels read the permuted copy, so it is made whenever they run */
-    const bool gather = g_pp_gather != 0 && !solo && !peer;
-    if (A > 0 && !gather) {
+    const bool gather = g_pp_gather == 1 && !solo && !peer;
+    /* the SM pairs' gather warps read the block input themselves; a permuted
+     * copy is made of the one-SM lists' rows only */
+    const bool wgather = g_pp_gather == 2 && !peer && A > 0;
+    if (wgather && solo) {
+        launch_k(gather_solo_rows_kernel, dim3(sm_count * 4), dim3(256), 0, st, x,
+                 (const int32_t *)d.perm, (const int4 *)tl.solo_gu, (const int *)tl.n_solo_gu, H,
+                 TK, xg);
+        (*launches)++;
+    }
+    if (A > 0 && !gather && !wgather) {
         long total = (long)A * (H / 8);
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count * 16) blocks = sm_count * 16;
@@ -779,7 +919,9 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
         g1.sched = tl.sched;
     }
     p1.gather_tk = gather && A > 0 ? TK : 0;
-    launch_pair(pair_gemm_kernel<0>, grid, (size_t)smem, st, m_xg, m_x, maps->w_gu, maps->sh_g,
+    p1.wgather_tk = wgather ? TK : 0;
+    p1.x = x;
+    launch_pair(pair_gemm_kernel<0>, grid, PP_THREADS_GU, (size_t)smem, st, m_xg, m_x, maps->w_gu, maps->sh_g,
                 maps->sh_u, m_g, p1);
     (*launches)++;
     if (solo) {
@@ -800,9 +942,10 @@ inline int run_pair_experts(int sm_count, int smem_optin, PrefillMaps *maps,
     p2.ld_routed = H;
     p2.ld_shared = H;
     p2.gather_tk = 0;
+    p2.wgather_tk = 0;
     p2.peer_dst = peer ? peer->dst : nullptr;
     p2.peer_cap = peer ? peer->cap : 0;
-    launch_pair(pair_gemm_kernel<1>, grid, (size_t)smem_dn, st, m_act, m_sa, maps->w_d, maps->sh_d,
+    launch_pair(pair_gemm_kernel<1>, grid, PP_THREADS, (size_t)smem_dn, st, m_act, m_sa, maps->w_d, maps->sh_d,
                 maps->sh_d, m_g, p2);
     (*launches)++;
     if (solo) {

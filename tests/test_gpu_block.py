@@ -251,11 +251,15 @@ def test_block_few_tokens_without_gathered_rows(be, orc, synth, qwen_weights, T,
 @pytest.mark.parametrize("T,E,TK,skew", [(300, 8, 4, False), (257, 8, 4, False),
                                          (1000, 8, 4, False), (1500, 16, 8, True),
                                          (129, 4, 4, False)])
-def test_block_two_sm_gemm_path(be, orc, synth, monkeypatch, T, E, TK, skew):
+@pytest.mark.parametrize("gather", ["0", "1", "2"])
+def test_block_two_sm_gemm_path(be, orc, synth, monkeypatch, T, E, TK, skew, gather):
     """Many rows per expert: the GEMMs in which a pair of SMs shares a tile
     (tokens as the MMA's M, 256 per pair).  Checked against the CPU checker and,
     bit for bit, against the one-SM kernels on the same inputs (a row's result
-    must not depend on the tiling)."""
+    must not depend on the tiling).  gather: how the gate_up kernel gets its
+    token rows — 0 a permuted copy (default), 1 TMA gather4 from the block input,
+    2 the kernel's own gather warps (cp.async into the swizzled stage)."""
+    monkeypatch.setenv("APUS_CUDA_PAIR_GATHER", gather)
     cfg = dict(hidden=512, experts=E, moe_inter=128, shared_inter=128, top_k=TK)
     W = synth.host_weights(be, cfg, seed=60 + T, sigma=0.05)
     x = synth.host_x(be, T, cfg["hidden"], seed=60 + T)
