@@ -1826,7 +1826,8 @@ static int experts_core(ApusCudaLayer *L, const uint16_t *d_x, const int32_t *d_
     stage_mark(c, -1, st);
     g_mark_stream = st;
     if (launch_dispatch(c, d_e, (int)R, (int)ne, b.d, b.unit_hist, st,
-                        DispatchKey{(int)L->e_begin, 1}, prefill && !pair ? &plan : nullptr))
+                        DispatchKey{(int)L->e_begin, 1, peer ? (int)ne : 0},
+                        prefill && !pair ? &plan : nullptr))
         return 1;
     stage_mark(c, APUS_CUDA_STAGE_DISPATCH, st);
     if (pair) {
@@ -1920,7 +1921,6 @@ struct ApusCudaEpWindow {
     int32_t *uh;                     /* dispatch scratch */
     unsigned int *counter;           /* [2] finished-CTA counters */
     uint32_t *d_epoch;               /* step number for calls made with epoch 0 */
-    int32_t *pulled;                 /* [n*cap] ids of the resident experts, by flat slot */
     unsigned long long *tbl;         /* [2][EPW_MAX_RANKS] addresses of every rank's xs, by */
     bool tbl_ready;
 };
@@ -1942,7 +1942,7 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     w->E = (int)E;
     const size_t A = cap;
     const size_t local = n_ranks * cap * H * 2 + (n_ranks + 1) * 4 + A * 4 +
-                         n_ranks * 4 + n_ranks * cap * 4 + 2 * EPW_MAX_RANKS * 8 +
+                         n_ranks * 4 + 2 * EPW_MAX_RANKS * 8 +
                          dispatch_scratch_bytes(A, n_ranks) + 8192;
     unsigned char *loc = nullptr;
     if (cudaMalloc(&w->base, w->l.total) != cudaSuccess ||
@@ -1962,7 +1962,6 @@ extern "C" int apus_cuda_ep_window_create(size_t max_tokens, size_t topk, size_t
     w->counts = (int32_t *)(loc + o);    o = up(o + n_ranks * 4);
     w->counter = (unsigned int *)(loc + o); o = up(o + 8);
     w->d_epoch = (uint32_t *)(loc + o);  o = up(o + 4);
-    w->pulled = (int32_t *)(loc + o);    o = up(o + n_ranks * cap * 4);
     w->tbl = (unsigned long long *)(loc + o); o = up(o + 2 * EPW_MAX_RANKS * 8);
     w->uh = (int32_t *)(loc + o);
     w->peers.base[rank] = w->base;
@@ -2174,19 +2173,14 @@ extern "C" int apus_cuda_ep_pull_experts_dev(ApusCudaEpWindow *w, ApusCudaLayer 
             CU_OK(cudaStreamSynchronize(st));
             w->tbl_ready = true;
         }
-        const long total = (long)w->l.n * w->l.cap;
-        int blocks = (int)((total + 255) / 256);
-        if (blocks > c->sm_count * 4) blocks = c->sm_count * 4;
-        launch_k(epw_pull_ids_kernel, dim3(blocks), dim3(256), 0, st,
-                 (const int32_t *)(w->base + w->l.ids), total, (int)L->e_begin,
-                 (int)L->e_end, w->pulled);
-        LAUNCHED();
-        /* of the n * cap slots about cap hold a resident expert */
+        /* of the n * cap slots about cap hold a resident expert; the dispatch
+         * skips the others */
         c->ep_rows_hint = (size_t)w->l.cap;
     }
     PeerRows pr = {w->tbl, w->tbl + EPW_MAX_RANKS, w->l.cap};
     SharedWork sh = {d_x, T, d_sy};
-    if (experts_core(L, nullptr, w->pulled, (size_t)w->l.n * w->l.cap, nullptr, stream, &pr,
+    if (experts_core(L, nullptr, (const int32_t *)(w->base + w->l.ids),
+                     (size_t)w->l.n * w->l.cap, nullptr, stream, &pr,
                      d_x ? &sh : nullptr))
         return 1;
     std::lock_guard<std::recursive_mutex> lk(g_mu);

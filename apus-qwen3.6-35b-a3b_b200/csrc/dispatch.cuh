@@ -38,12 +38,15 @@ constexpr int GROUP_TOKENS = 4;         /* rows per decode token group */
 struct DispatchKey {
     int base;
     int div;
+    int lax;     /* > 0: ids outside [base, base + lax * div) are someone else's, skipped
+                  * like empty slots (a rank sorting every rank's ids for its own experts) */
 };
 /* An id of -1 is an empty slot: skipped without complaint (key -2).  Any other
- * id outside the key range is an error (key -1 or >= E). */
+ * id outside the key range is an error (key -1 or >= E) unless the key is lax. */
 __device__ __forceinline__ int dispatch_key(int raw, DispatchKey kx) {
     if (raw == -1) return -2;
     const int v = raw - kx.base;
+    if (kx.lax > 0 && (v < 0 || v / kx.div >= kx.lax)) return -2;
     return v < 0 ? -1 : v / kx.div;
 }
 

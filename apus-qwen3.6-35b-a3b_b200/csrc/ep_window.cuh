@@ -51,7 +51,8 @@
  *   publish store x and the ids into region `me` of xs/ids of EVERY rank's
  *           window (its own included), then fin[me] = epoch everywhere.
  *   wait    as above.
- *   experts keep the ids of the resident experts, sort; the gather kernel reads
+ *   experts sort the ids of the resident experts (the dispatch skips everyone
+ *           else's); the gather kernel reads
  *           each needed row from the local xs; gate_up as on one GPU; the down
  *           GEMM's epilogue stores every output row straight into by[] of the
  *           rank that owns the token, at the flat position t * topk + j its
@@ -324,19 +325,6 @@ epw_publish_rows_kernel(const uint16_t *__restrict__ x, int T, EpwLayout l, EpwP
         for (int u = 0; u < 4; u++)
             if (d[u] >= 0)
                 reinterpret_cast<uint4 *>(s_base[d[u]] + l.xs + region)[i[u]] = v[u];
-    }
-}
-
-/* re[i] = ids[i] (all sources, this rank's copy) if that expert is resident
- * here, else -1 */
-__global__ void __launch_bounds__(256)
-epw_pull_ids_kernel(const int32_t *__restrict__ ids, long total, int e_begin, int e_end,
-                    int32_t *__restrict__ re) {
-    pdl_enter();
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long)gridDim.x * blockDim.x) {
-        const int e = ids[i];
-        re[i] = (e >= e_begin && e < e_end) ? e : -1;
     }
 }
 
