@@ -165,6 +165,53 @@ def test_peer_window_ranks_equal_single_gpu(be, synth, N, T, path, mode, monkeyp
         be.disable()
 
 
+@pytest.mark.parametrize("min_rows", ["192", "32"])
+def test_peer_window_pull_real_dims(be, synth, min_rows, monkeypatch):
+    """The real layer shape (H 2048, 256 experts, top-8, I 512), two ranks of 1024
+    tokens: the one-SM GEMMs (64 rows per resident expert on average) and, with
+    the threshold lowered, the two-SM GEMMs store their outputs into the owners'
+    windows; every row equals the one-GPU block on the same weights."""
+    import torch
+    from apus_b200 import ep
+    monkeypatch.setenv("APUS_CUDA_PAIR_MIN_ROWS", min_rows)
+    be.enable()
+    try:
+        cfg = dict(synth.QWEN_CFG)
+        N, per, H, E = 2, 1024, cfg["hidden"], cfg["experts"]
+        sp = torch.cuda.current_stream().cuda_stream
+        whole = be.layer_create(cfg, None, 0, E)
+        synth.device_weights(be, whole, cfg, seed=5, stream=sp)
+        layers = []
+        for r in range(N):
+            h = be.layer_create(cfg, None, r * E // N, (r + 1) * E // N)
+            synth.device_weights(be, h, cfg, seed=5, expert_begin=r * E // N, stream=sp)
+            layers.append(h)
+        x = synth.host_x(be, N * per, H, seed=5)
+        d_x = torch.from_numpy(x.view(np.int16).copy()).cuda()
+        d_ref = torch.empty_like(d_x)
+        be.moe_block_dev(whole, d_x.data_ptr(), d_ref.data_ptr(), N * per, stream=sp)
+        wins = [be.ep_window_create(per, cfg["top_k"], H, E, N, r) for r in range(N)]
+        for r in range(N):
+            be.ep_window_attach_local(wins[r], 1 - r, wins[1 - r])
+        blks = [ep.PeerWindowBlock(be, layers[r], cfg, r, N, per, window=wins[r])
+                for r in range(N)]
+        xs = [d_x[r * per:(r + 1) * per].contiguous() for r in range(N)]
+        for _ in range(2):
+            sts = [blks[r].begin(xs[r]) for r in range(N)]
+            for r in range(N):
+                blks[r].middle()
+            outs = [blks[r].end(sts[r]) for r in range(N)]
+        torch.cuda.synchronize()
+        assert be.last_block_status() == 0
+        assert torch.equal(torch.cat(outs), d_ref)
+        for w in wins:
+            be.ep_window_destroy(w)
+        for l in layers + [whole]:
+            be.layer_destroy(l)
+    finally:
+        be.disable()
+
+
 @pytest.mark.parametrize("mode,overlap", [("push", False), ("pull", True),
                                           ("pull", False)])
 def test_peer_window_ragged_ranks(be, synth, mode, overlap):
