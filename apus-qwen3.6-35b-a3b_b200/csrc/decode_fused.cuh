@@ -208,24 +208,60 @@ __device__ __forceinline__ void df_rmsnorm_to_smem(const FusedArgs &a, uint16_t 
     __syncthreads();
     if (warp < T) {
         uint16_t *row = xs + (size_t)warp * H;
+        /* the gains are asked for before the chain starts, so that their trip
+         * from L2 hides behind it: 16 bytes a lane and round, H / 256 rounds */
+        const int nj = H / 256;
+        const bool vec = H % 256 == 0 && nj <= 8;
+        uint4 lw[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            lw[j] = (vec && a.ln_w && j < nj) ? ldg16(a.ln_w + (size_t)(lane + 32 * j) * 8)
+                                              : make_uint4(0, 0, 0, 0);
         float ss = 0.0f;
         if (lane == 0) {
             const uint4 *r4 = reinterpret_cast<const uint4 *>(row);
-#pragma unroll 2
+            /* four rows of eight ahead: the shared-memory loads and the squares
+             * stay off the chain of dependent adds */
+#pragma unroll 4
             for (int i = 0; i < H / 8; i++) {
                 const uint4 v = r4[i];
                 const float f[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
                                     bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+                float q[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+                for (int j = 0; j < 8; j++) q[j] = __fmul_rn(f[j], f[j]);
+#pragma unroll
+                for (int j = 0; j < 8; j++) ss = __fadd_rn(ss, q[j]);
             }
         }
         ss = __shfl_sync(0xffffffffu, ss, 0);
         const float rs =
             __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), 1e-6f)));
-        for (int i = lane; i < H; i += 32) {
-            const float g = __fadd_rn(1.0f, a.ln_w ? bf16_f32(__ldg(a.ln_w + i)) : 0.0f);
-            row[i] = bf16_bits(__fmul_rn(__fmul_rn(bf16_f32(row[i]), rs), g));
+        if (vec) {
+            uint4 *r4 = reinterpret_cast<uint4 *>(row);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (j < nj) {
+                    const uint4 v = r4[lane + 32 * j];
+                    const uint32_t xw[4] = {v.x, v.y, v.z, v.w};
+                    const uint32_t gw[4] = {lw[j].x, lw[j].y, lw[j].z, lw[j].w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float g0 = __fadd_rn(1.0f, bf16lo(gw[q])),
+                                    g1 = __fadd_rn(1.0f, bf16hi(gw[q]));
+                        const float y0 = __fmul_rn(__fmul_rn(bf16lo(xw[q]), rs), g0),
+                                    y1 = __fmul_rn(__fmul_rn(bf16hi(xw[q]), rs), g1);
+                        o[q] = (uint32_t)bf16_bits(y0) | ((uint32_t)bf16_bits(y1) << 16);
+                    }
+                    r4[lane + 32 * j] = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) {
+                const float g = __fadd_rn(1.0f, a.ln_w ? bf16_f32(__ldg(a.ln_w + i)) : 0.0f);
+                row[i] = bf16_bits(__fmul_rn(__fmul_rn(bf16_f32(row[i]), rs), g));
+            }
         }
     }
     __syncthreads();
