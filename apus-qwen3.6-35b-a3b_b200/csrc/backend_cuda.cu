@@ -2140,6 +2140,9 @@ extern "C" int apus_cuda_ep_publish_dev(ApusCudaEpWindow *w, const uint16_t *d_x
     long total = d_x ? (long)T * (w->l.H / 8) * w->l.n : (long)w->l.cap * w->l.n;
     int blocks = (int)((total + 255) / 256);
     if (blocks > c->sm_count * 2) blocks = c->sm_count * 2;
+    /* ids only: a few hundred KB; every CTA ends with a system-scope fence and a
+     * turn at one counter, so a handful of CTAs is quicker than hundreds */
+    if (!d_x && blocks > 4 * w->l.n) blocks = 4 * w->l.n;
     launch_k(epw_publish_kernel, dim3(blocks), dim3(256), 0, st, d_x, d_idx, (int)T, w->topk,
              w->l, w->peers, w->me, epoch, w->counter, w->d_epoch);
     LAUNCHED();
