@@ -107,6 +107,11 @@ struct Ctx {
     int last_block_path = 0;
     bool hooks_filled = false;
     size_t ep_rows_hint = 0;     /* rows the next experts_dev call expects (0: its R) */
+    /* host-pointer block call with many tokens: two halves, the second half's
+     * upload and the first half's download beside the other half's kernels */
+    long host_split_t = 4096;    /* APUS_CUDA_HOST_SPLIT_T: from this many tokens (0: never) */
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_io[5] = {};   /* start, in[2], done[2] */
     /* ordering of calls that arrive on different streams */
     cudaStream_t cur_stream = nullptr, last_stream = nullptr;
     cudaEvent_t last_ev = nullptr;
@@ -216,6 +221,7 @@ static int ctx_init() {
     g_pp_min_rows = (int)env_long("APUS_CUDA_PAIR_MIN_ROWS", 192);
     g_pp_gather = (int)env_long("APUS_CUDA_PAIR_GATHER", 0);
     g_pp_solo_below = (int)env_long("APUS_CUDA_PAIR_SOLO_BELOW", 160);
+    c->host_split_t = env_long("APUS_CUDA_HOST_SPLIT_T", 4096);
     g_ctx = c;
     return 0;
 }
@@ -387,6 +393,10 @@ extern "C" void apus_cuda_disable(void) {
     if (c->d_df_sa) cudaFree(c->d_df_sa);
     if (c->d_router_logits) cudaFree(c->d_router_logits);
     if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->s_in) cudaStreamDestroy(c->s_in);
+    if (c->s_out) cudaStreamDestroy(c->s_out);
+    for (auto &e : c->ev_io)
+        if (e) cudaEventDestroy(e);
     g_ctx = nullptr;
     delete c;
 }
@@ -1622,24 +1632,71 @@ extern "C" int apus_cuda_moe_block(const ApusCudaMoeCfg *cfg,
         if (tr->moe_routed) dtr.moe_routed = (uint16_t *)c->io.take(T * H * 2);
         if (tr->moe_shared) dtr.moe_shared = (uint16_t *)c->io.take(T * H * 2);
     }
-    CU_OK(cudaMemcpyAsync(dx, ln2, T * H * 2, cudaMemcpyHostToDevice, c->stream));
-    if (apus_cuda_moe_block_dev(L, dx, dout, T, tr ? &dtr : nullptr, c->stream))
-        return 1;
-    CU_OK(cudaMemcpyAsync(moe_out, dout, T * H * 2, cudaMemcpyDeviceToHost,
-                          c->stream));
-    if (tr) {
+    /* rows [r0, r0 + n) of the call: upload on s_up, block on the library's
+     * stream, download on s_dn (all three the same stream for a small call) */
+    auto download = [&](size_t r0, size_t n, cudaStream_t s_dn) -> int {
+        CU_OK(cudaMemcpyAsync(moe_out + r0 * H, dout + r0 * H, n * H * 2,
+                              cudaMemcpyDeviceToHost, s_dn));
+        if (!tr) return 0;
         if (tr->rtr_idx)
-            CU_OK(cudaMemcpyAsync(tr->rtr_idx, dtr.rtr_idx, T * TK * 4,
-                                  cudaMemcpyDeviceToHost, c->stream));
+            CU_OK(cudaMemcpyAsync(tr->rtr_idx + r0 * TK, dtr.rtr_idx + r0 * TK, n * TK * 4,
+                                  cudaMemcpyDeviceToHost, s_dn));
         if (tr->rtr_w)
-            CU_OK(cudaMemcpyAsync(tr->rtr_w, dtr.rtr_w, T * TK * 2,
-                                  cudaMemcpyDeviceToHost, c->stream));
+            CU_OK(cudaMemcpyAsync(tr->rtr_w + r0 * TK, dtr.rtr_w + r0 * TK, n * TK * 2,
+                                  cudaMemcpyDeviceToHost, s_dn));
         if (tr->moe_routed)
-            CU_OK(cudaMemcpyAsync(tr->moe_routed, dtr.moe_routed, T * H * 2,
-                                  cudaMemcpyDeviceToHost, c->stream));
+            CU_OK(cudaMemcpyAsync(tr->moe_routed + r0 * H, dtr.moe_routed + r0 * H,
+                                  n * H * 2, cudaMemcpyDeviceToHost, s_dn));
         if (tr->moe_shared)
-            CU_OK(cudaMemcpyAsync(tr->moe_shared, dtr.moe_shared, T * H * 2,
-                                  cudaMemcpyDeviceToHost, c->stream));
+            CU_OK(cudaMemcpyAsync(tr->moe_shared + r0 * H, dtr.moe_shared + r0 * H,
+                                  n * H * 2, cudaMemcpyDeviceToHost, s_dn));
+        return 0;
+    };
+    auto part_trace = [&](size_t r0) {
+        ApusCudaMoeTrace t = dtr;
+        if (t.rtr_idx) t.rtr_idx += r0 * TK;
+        if (t.rtr_w) t.rtr_w += r0 * TK;
+        if (t.moe_routed) t.moe_routed += r0 * H;
+        if (t.moe_shared) t.moe_shared += r0 * H;
+        return t;
+    };
+    const bool split = c->host_split_t > 0 && T >= (size_t)c->host_split_t;
+    if (!split) {
+        CU_OK(cudaMemcpyAsync(dx, ln2, T * H * 2, cudaMemcpyHostToDevice, c->stream));
+        if (apus_cuda_moe_block_dev(L, dx, dout, T, tr ? &dtr : nullptr, c->stream))
+            return 1;
+        if (download(0, T, c->stream)) return 1;
+    } else {
+        /* A token's result does not depend on which other tokens share the call,
+         * so two half calls give the same bits; the PCIe copies of one half run
+         * beside the kernels of the other. */
+        if (!c->s_in) {
+            CU_OK(cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking));
+            CU_OK(cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking));
+            for (auto &e : c->ev_io) CU_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        }
+        const size_t r1 = T / 2, cut[3] = {0, r1, T};
+        CU_OK(cudaEventRecord(c->ev_io[0], c->stream));       /* earlier work owns dx, dout */
+        CU_OK(cudaStreamWaitEvent(c->s_in, c->ev_io[0], 0));
+        CU_OK(cudaStreamWaitEvent(c->s_out, c->ev_io[0], 0));
+        for (int k = 0; k < 2; k++) {
+            CU_OK(cudaMemcpyAsync(dx + cut[k] * H, ln2 + cut[k] * H,
+                                  (cut[k + 1] - cut[k]) * H * 2, cudaMemcpyHostToDevice,
+                                  c->s_in));
+            CU_OK(cudaEventRecord(c->ev_io[1 + k], c->s_in));
+        }
+        for (int k = 0; k < 2; k++) {
+            const size_t r0 = cut[k], n = cut[k + 1] - cut[k];
+            CU_OK(cudaStreamWaitEvent(c->stream, c->ev_io[1 + k], 0));
+            ApusCudaMoeTrace tk = part_trace(r0);
+            if (apus_cuda_moe_block_dev(L, dx + r0 * H, dout + r0 * H, n, tr ? &tk : nullptr,
+                                        c->stream))
+                return 1;
+            CU_OK(cudaEventRecord(c->ev_io[3 + k], c->stream));
+            CU_OK(cudaStreamWaitEvent(c->s_out, c->ev_io[3 + k], 0));
+            if (download(r0, n, c->s_out)) return 1;
+        }
+        CU_OK(cudaStreamSynchronize(c->s_out));
     }
     int st = 0;
     CU_OK(cudaMemcpyAsync(&st, c->d_status, 4, cudaMemcpyDeviceToHost, c->stream));

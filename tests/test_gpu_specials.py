@@ -206,3 +206,24 @@ def test_graph_survives_workspace_growth(gpu, be, synth):
             pass                      # an empty capture may itself be refused
         torch.cuda.synchronize()
         assert "apus_cuda_reserve" in msg
+
+
+def test_host_call_in_two_halves_gives_the_same_bits(be, synth, monkeypatch):
+    """From 4096 tokens the host-pointer call runs as two half calls whose PCIe
+    copies overlap the other half's kernels (APUS_CUDA_HOST_SPLIT_T): every
+    output and trace array equals the single call bit for bit, odd token count
+    included."""
+    cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128, top_k=8)
+    W = synth.host_weights(be, cfg, seed=41, sigma=0.05)
+    x = synth.host_x(be, 4101, cfg["hidden"], seed=41)
+    res = {}
+    for split in ("0", "4096"):
+        monkeypatch.setenv("APUS_CUDA_HOST_SPLIT_T", split)
+        be.enable()
+        try:
+            res[split] = be.moe_block(cfg, W, x)
+            assert be.last_block_status() == 0
+        finally:
+            be.disable()
+    for k in ("idx", "w", "shared", "routed", "out"):
+        assert np.array_equal(res["0"][k], res["4096"][k]), k
