@@ -437,8 +437,14 @@ decode_fused_kernel(FusedArgs a) {
     }
     __syncthreads();
     {
-        const int lo = (int)((long)Is * blockIdx.x / G);
-        const int hi = (int)((long)Is * (blockIdx.x + 1) / G);
+        /* The shared expert's rows go to the CTAs that have no router chains to
+         * walk (they would otherwise idle until the logits arrive); a router CTA
+         * that also took a share reached the selection 2-3 us after everyone
+         * else and held up the grid barrier by as much. */
+        const bool spare = G > nR;
+        const int Gs = spare ? G - nR : G, bs = spare ? (int)blockIdx.x - nR : (int)blockIdx.x;
+        const int lo = bs < 0 ? 0 : (int)((long)Is * bs / Gs);
+        const int hi = bs < 0 ? 0 : (int)((long)Is * (bs + 1) / Gs);
         const int n_my = (lo + warp < hi) ? (hi - lo - warp + DF_WARPS - 1) / DF_WARPS : 0;
         if (lane == 0)
             for (; ring.issued < n_my && ring.issued < a.stages; ring.issued++) {
