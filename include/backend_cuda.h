@@ -149,7 +149,11 @@ typedef struct {
  * on first sight of w->rtr_w (the residency key) and stay in HBM until
  * apus_cuda_disable (exp_gu / exp_d may be NULL for a layer registered with
  * apus_cuda_register_layer_slabs).  Synchronous: moe_out and the trace rows are complete on
- * return.  Returns 0, or nonzero with apus_cuda_last_error() set. */
+ * return.  T == 0 writes nothing and succeeds, as the engine's loops over T do.
+ * From APUS_CUDA_HOST_SPLIT_T tokens (default 4096; 0: never) the call runs as
+ * two half calls whose PCIe copies overlap the other half's kernels: the same
+ * bits, since a token's result does not depend on its neighbours.
+ * Returns 0, or nonzero with apus_cuda_last_error() set. */
 int apus_cuda_moe_block(const ApusCudaMoeCfg *c, const ApusCudaMoeW *w,
                         const uint16_t *ln2, uint16_t *moe_out, size_t T,
                         const ApusCudaMoeTrace *tr);

@@ -227,3 +227,22 @@ def test_host_call_in_two_halves_gives_the_same_bits(be, synth, monkeypatch):
             be.disable()
     for k in ("idx", "w", "shared", "routed", "out"):
         assert np.array_equal(res["0"][k], res["4096"][k]), k
+
+
+def test_no_token_is_a_successful_no_op(gpu, be, synth):
+    """T = 0: the engine's loops run zero times (c/layer.h:589); the block call
+    returns success and writes nothing, host and device entry points alike."""
+    import ctypes as C
+    import torch
+    cfg = dict(hidden=512, experts=64, moe_inter=128, shared_inter=128, top_k=8)
+    W = synth.host_weights(be, cfg, seed=43, sigma=0.05)
+    layer = gpu.layer_create(cfg, W)
+    d = torch.full((4, cfg["hidden"]), 0x1234, dtype=torch.int16, device="cuda")
+    rc = gpu.lib.apus_cuda_moe_block_dev(layer, d.data_ptr(), d.data_ptr(), 0, None, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int((d != 0x1234).sum()) == 0
+    gpu.layer_destroy(layer)
+    x = synth.host_x(be, 1, cfg["hidden"], seed=43)
+    res = gpu.moe_block(cfg, W, x[:0])              # host pointers, T = 0
+    assert res["out"].shape == (0, cfg["hidden"]) and res["idx"].shape == (0, 8)
